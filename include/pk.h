@@ -1,0 +1,238 @@
+/*
+ * pk.h -- C ABI of libpk, the sm_100a kernel library behind the microtorch
+ * tape (activation-checkpointed transformer-block training step).
+ *
+ * Conventions
+ *   - every entry returns an int status (PK_OK == 0); none throws, exits,
+ *     traps the device or allocates device memory unless its name says so
+ *     (pk_malloc / pk_free / pk_host_alloc).
+ *   - every pointer is a DEVICE pointer unless the parameter name ends in _h.
+ *   - `stream` is a cudaStream_t passed as void*; work is asynchronous on it.
+ *   - matrices are row-major; `ld*` are row strides in ELEMENTS.
+ *   - `dtype` is PK_F32 or PK_BF16 and names the storage type of activations;
+ *     all arithmetic is fp32 (fp64 where the reference sums in double).
+ *   - scratch buffers are caller-provided; the matching *_scratch_bytes()
+ *     call gives the size. Results never depend on scratch contents on entry.
+ *   - all kernels are deterministic: the same call on the same inputs gives
+ *     the same bits, which is what makes a recomputed activation identical to
+ *     the one the forward pass produced.
+ *
+ * Each group cites the interface of the reference (paperkiln / microtorch,
+ * paths relative to its repository root) that the entries stand in for.
+ */
+#ifndef PK_H_
+#define PK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PK_ABI_VERSION 1
+
+enum pk_dtype { PK_F32 = 0, PK_BF16 = 1 };
+
+enum pk_status {
+    PK_OK = 0,
+    PK_ERR_INVALID = 1,     /* bad argument (shape, alignment, null pointer) */
+    PK_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed; see pk_last_error */
+    PK_ERR_UNSUPPORTED = 3, /* valid request this build has no kernel for */
+    PK_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up */
+    PK_ERR_INDEX = 5        /* an id / target was out of range (device status word) */
+};
+
+/* ---- library / runtime ----------------------------------------------------
+ * Stands in for the process-global device switch and CUDA error convention of
+ * include/microtorch/device.hpp:20-33 and src/cuda_ops.cu:34-38 (exceptions
+ * there, status codes here). */
+int pk_abi_version(void);
+const char* pk_last_error(void);           /* message of the last failing call on this thread */
+int pk_device_count(int* count_h);
+int pk_set_device(int device);
+int pk_device_name(int device, char* name_h, size_t cap);
+int pk_mem_info(size_t* free_h, size_t* total_h);
+int pk_malloc(void** ptr_h, size_t bytes);
+int pk_free(void* ptr);
+int pk_host_alloc(void** ptr_h, size_t bytes); /* pinned host memory */
+int pk_host_free(void* ptr_h);
+int pk_memcpy_h2d(void* dst, const void* src_h, size_t bytes, void* stream);
+int pk_memcpy_d2h(void* dst_h, const void* src, size_t bytes, void* stream);
+int pk_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream);
+int pk_memset(void* dst, int value, size_t bytes, void* stream);
+int pk_stream_create(void** stream_h);
+int pk_stream_destroy(void* stream);
+int pk_stream_sync(void* stream);
+int pk_device_sync(void);
+/* Device status word: kernels that detect an out-of-range id or a wait that
+ * ran out OR a code into *status (int32 on the device) instead of trapping. */
+
+/* ---- GEMM ------------------------------------------------------------------
+ * C[M,N] (+)= op(A) . op(B) (+ bias) (+ residual), fp32 accumulation.
+ * Replaces device::gemm(A, devA, tA, B, devB, tB) -- include/microtorch/
+ * device_cache.hpp:63-71, call sites src/ops.cpp:45,50-55 -- and the kernels
+ * gemm_tiled / gemm_tiled_ops in src/cuda_resident.cu:53-76,141-171.
+ *   ab_dtype : storage type of A and B (PK_F32 or PK_BF16)
+ *   c_dtype  : storage type of C and of `residual`
+ *   trans_a  : 0 -> A is [M,K] (lda >= K); 1 -> A is stored [K,M] (lda >= M)
+ *   trans_b  : 0 -> B is [K,N] (ldb >= N); 1 -> B is stored [N,K] (ldb >= K)
+ *   accumulate: 0 -> C = ..., 1 -> C += ... (C read-modify-write, fixed order)
+ *   bias     : fp32 [N] or NULL; residual: [M,N] with row stride ldr or NULL
+ * bf16 inputs take the tcgen05 tensor-core kernel when M,N,K and the leading
+ * dimensions meet its alignment (multiples of 8 elements, 16-byte aligned
+ * bases); other shapes take a SIMT kernel. pk_gemm_last_path() tells which
+ * one the last call on this thread used (0 SIMT fp32, 1 SIMT bf16, 2 tcgen05). */
+int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b,
+            int64_t M, int64_t N, int64_t K,
+            const void* A, int64_t lda, const void* B, int64_t ldb,
+            void* C, int64_t ldc, int accumulate,
+            const float* bias, const void* residual, int64_t ldr);
+int pk_gemm_last_path(void);
+/* Status word of the tensor-core kernel: non-zero (PK_ERR_TIMEOUT) when one of its
+ * bounded mbarrier waits gave up. Synchronises the device; clear != 0 resets it. */
+int pk_gemm_tc_status(int* status_h, int clear);
+/* Force the SIMT kernels (1) or restore automatic selection (0); used by the
+ * parity tests to compare the tensor-core kernel with the SIMT one. */
+int pk_gemm_force_simt(int on);
+
+/* ---- normalisation ----------------------------------------------------------
+ * RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w; rinv[R] is saved for backward.
+ * Replaces ops::rmsnorm (src/ops.cpp:426-479), devops::rmsnorm_fwd/bwd
+ * (include/microtorch/device_cache.hpp:122-126) and k_rmsnorm_* in
+ * src/cuda_ops.cu:321-381. w and dw are fp32 [C]. dw is ACCUMULATED (+=).
+ * dx and dw may each be NULL to skip. */
+int pk_rmsnorm_fwd(void* stream, int dtype, const void* x, const float* w, void* y,
+                   float* rinv, int64_t R, int64_t C, float eps);
+size_t pk_rmsnorm_bwd_scratch_bytes(int64_t R, int64_t C);
+int pk_rmsnorm_bwd(void* stream, int dtype, const void* dy, const void* x, const float* w,
+                   const float* rinv, void* dx, float* dw, void* scratch,
+                   int64_t R, int64_t C);
+/* LayerNorm (biased variance). Saves mean[R] and rstd[R] instead of the
+ * reference's xhat [R,C]. Replaces ops::layernorm (src/ops.cpp:248-327),
+ * devops::layernorm_fwd/bwd and k_layernorm_* / k_colsum_dgb in
+ * src/cuda_ops.cu:221-318. dgamma/dbeta are ACCUMULATED. */
+int pk_layernorm_fwd(void* stream, int dtype, const void* x, const float* gamma,
+                     const float* beta, void* y, float* mean, float* rstd,
+                     int64_t R, int64_t C, float eps);
+size_t pk_layernorm_bwd_scratch_bytes(int64_t R, int64_t C);
+int pk_layernorm_bwd(void* stream, int dtype, const void* dy, const void* x,
+                     const float* gamma, const float* mean, const float* rstd,
+                     void* dx, float* dgamma, float* dbeta, void* scratch,
+                     int64_t R, int64_t C);
+
+/* ---- rotary embedding -------------------------------------------------------
+ * In-place interleaved-pair rotation (x[2j], x[2j+1]) of `n_heads` heads of
+ * width head_dim starting at column col0 of a [R, ld] buffer. The angle table
+ * cos_sin is fp32 [n_pos, head_dim/2, 2] built on the host with the reference's
+ * float expressions; pos is int32 [R]. inverse != 0 rotates by -theta (the
+ * backward). Replaces ops::apply_rope (src/ops.cpp:481-537), which rotates
+ * ONE head of q and one of k: call with n_heads = 1 for that behaviour. */
+int pk_rope(void* stream, int dtype, void* x, int64_t ld, int64_t col0, int n_heads,
+            int head_dim, const int32_t* pos, const float* cos_sin, int64_t n_pos,
+            int64_t R, int inverse);
+
+/* ---- activations / elementwise ---------------------------------------------
+ * SwiGLU y = silu(g) * u and its backward: ops::silu + ops::mul
+ * (src/ops.cpp:404-424, 76-83). GELU (tanh form, correct derivative):
+ * ops::gelu (src/ops.cpp:106-138), k_gelu_fwd/bwd (src/cuda_ops.cu:125-150).
+ * ReLU: ops::relu (src/ops.cpp:788-801). n = element count. */
+int pk_swiglu_fwd(void* stream, int dtype, const void* g, const void* u, void* y, int64_t n);
+int pk_swiglu_bwd(void* stream, int dtype, const void* dy, const void* g, const void* u,
+                  void* dg, void* du, int64_t n);
+int pk_silu_fwd(void* stream, int dtype, const void* x, void* y, int64_t n);
+int pk_silu_bwd(void* stream, int dtype, const void* dy, const void* x, void* dx, int64_t n);
+int pk_gelu_fwd(void* stream, int dtype, const void* x, void* y, int64_t n);
+int pk_gelu_bwd(void* stream, int dtype, const void* dy, const void* x, void* dx, int64_t n);
+int pk_relu_fwd(void* stream, int dtype, const void* x, void* y, int64_t n);
+int pk_relu_bwd(void* stream, int dtype, const void* dy, const void* x, void* dx, int64_t n);
+/* y = a (op) b, op: 0 add, 1 sub, 2 mul. ops::add/sub/mul (src/ops.cpp:60-83),
+ * devops::add/sub/mul (device_cache.hpp:99-101). */
+int pk_binary(void* stream, int dtype, int op, const void* a, const void* b, void* y, int64_t n);
+/* y = alpha * x (ops::scale, src/ops.cpp:184-190); y may alias x. */
+int pk_scale(void* stream, int dtype, const void* x, float alpha, void* y, int64_t n);
+/* y += alpha * x, the gradient-accumulate shape (devops::axpy; Variable::accumulate,
+ * src/autograd.cpp:16-24). x has dtype x_dtype, y has dtype y_dtype. */
+int pk_axpy(void* stream, int y_dtype, void* y, int x_dtype, const void* x, float alpha, int64_t n);
+int pk_cast(void* stream, int src_dtype, const void* src, int dst_dtype, void* dst, int64_t n);
+/* y[R,C] = x[R,C] + b[C] (ops::add_bias, src/ops.cpp:85-104); b fp32. */
+int pk_add_bias(void* stream, int dtype, const void* x, const float* b, void* y, int64_t R, int64_t C);
+/* out[C] += column sums of x[R,C] (the db of add_bias), fp32 out, deterministic. */
+size_t pk_colsum_scratch_bytes(int64_t R, int64_t C);
+int pk_colsum(void* stream, int dtype, const void* x, float* out, void* scratch, int64_t R, int64_t C);
+/* dst[r, dcol0 + j] (+)= src[r, scol0 + j], j < ncols: ops::slice_cols /
+ * ops::concat_cols and their backward scatters (src/ops.cpp:200-246). */
+int pk_copy_cols(void* stream, int dtype, const void* src, int64_t lds, int64_t scol0,
+                 void* dst, int64_t ldd, int64_t dcol0, int64_t R, int64_t ncols, int accumulate);
+/* y[C,R] = x[R,C]^T (ops::transpose, src/ops.cpp:192-198). */
+int pk_transpose(void* stream, int dtype, const void* x, void* y, int64_t R, int64_t C);
+
+/* ---- attention ---------------------------------------------------------------
+ * Causal (or bidirectional) softmax attention over B stacked sequences of
+ * length S, all heads in one call, never materialising the score matrix.
+ * q is [B*S, Hq*dk] with row stride ldq, k/v are [B*S, Hkv*dk]; query head h
+ * reads kv head h / (Hq/Hkv). out has q's shape (row stride ldo); lse is fp32
+ * [B*S, Hq] (log-sum-exp of the scaled scores), saved for backward.
+ * Replaces the per-head slice_cols + ops::fused_attention loop
+ * (src/llama.cpp:44-52, src/nn.cpp:144-150; op at src/ops.cpp:863-934). A
+ * row attends keys [sequence start, i] when causal, the whole sequence
+ * otherwise; rows of different sequences never see each other. */
+int pk_attn_fwd(void* stream, int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk,
+                const void* v, int64_t ldv, void* out, int64_t ldo, float* lse,
+                int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale, int causal);
+/* delta is fp32 scratch [B*S, Hq]. dq/dk/dv are overwritten (row strides lddq, lddk, lddv). */
+size_t pk_attn_bwd_scratch_bytes(int64_t B, int64_t S, int Hq);
+int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk,
+                const void* v, int64_t ldv, const void* out, int64_t ldo, const float* lse,
+                const void* dout, int64_t lddo, void* dq, int64_t lddq, void* dk_, int64_t lddk,
+                void* dv, int64_t lddv, void* scratch,
+                int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale, int causal);
+/* 0 = SIMT fp32-math kernel, 1 = tensor-core kernel (last call on this thread). */
+int pk_attn_last_path(void);
+int pk_attn_force_simt(int on);
+
+/* ---- embedding / loss --------------------------------------------------------
+ * Row gather out[i,:] = table[ids[i],:] (pure copy; table has the out dtype).
+ * ops::embedding forward (src/ops.cpp:329-337). An id outside [0,V) ORs
+ * PK_ERR_INDEX into *status (int32, device) and writes zeros. */
+int pk_embedding_fwd(void* stream, int dtype, const void* table, const int32_t* ids, void* out,
+                     int64_t R, int64_t d, int64_t V, int32_t* status);
+/* dtable[uniq[u],:] += sum over p in order[seg[u]..seg[u+1]) of dy[p,:], summed in
+ * ascending position order (the order the reference's scatter-add loop uses,
+ * src/ops.cpp:338-347). order/seg/uniq are built on the host from the ids. */
+int pk_embedding_bwd(void* stream, int dtype, const void* dy, const int32_t* order,
+                     const int32_t* seg, const int32_t* uniq, int64_t n_uniq, float* dtable,
+                     int64_t d);
+/* Cross entropy over rows of logits [R,V]: row_loss[i] = -log(max(softmax_i[t_i], 1e-12)).
+ * When want_grad != 0 the logits are OVERWRITTEN with (softmax - onehot) * grad_scale.
+ * ops::cross_entropy (src/ops.cpp:350-376). A target outside [0,V) sets *status. */
+int pk_cross_entropy(void* stream, int dtype, void* logits, int64_t ld, const int32_t* targets,
+                     float* row_loss, int64_t R, int64_t V, float grad_scale, int want_grad,
+                     int32_t* status);
+/* out[0] (double) = sum of x[0..n) in a fixed tree order, accumulated in fp64
+ * (the reference sums the NLL and the grad norm in double). square != 0 sums x^2.
+ * add != 0 adds to out[0] instead of overwriting. scratch: pk_reduce_scratch_bytes(). */
+size_t pk_reduce_scratch_bytes(void);
+int pk_reduce_sum_f64(void* stream, const float* x, int64_t n, int square, int add, double* out,
+                      void* scratch);
+
+/* ---- optimizer ---------------------------------------------------------------
+ * AdamW::step (src/nn.cpp:301-321) over a flat fp32 buffer: m,v EMA, bias
+ * correction c1 = 1-b1^t, c2 = 1-b2^t computed by the caller in float,
+ * p -= lr * ((m/c1)/(sqrt(v/c2)+eps) + wd*p). p_bf16 (nullable) receives the
+ * rounded copy of the new p in the same pass. */
+int pk_adamw(void* stream, float* p, const float* g, float* m, float* v, int64_t n,
+             float lr, float b1, float b2, float eps, float wd, float c1, float c2,
+             void* p_bf16);
+/* Q8_0: blocks of 32 along a row of W[rows, cols] (cols % 32 == 0), int8 values and an
+ * fp16 scale = fp16(absmax/127) (1.0 for an all-zero block); q = round-half-away(clamp(x/s)).
+ * quantize_int8 / dequantize (src/quant.cpp:11-48) with block 32 and the scale stored as fp16.
+ * Dequantisation is one fp32 multiply float(q) * float(scale), then a cast to out_dtype. */
+int pk_q8_quantize(void* stream, const float* W, int8_t* q, uint16_t* scales, int64_t rows, int64_t cols);
+int pk_q8_dequantize(void* stream, const int8_t* q, const uint16_t* scales, int out_dtype, void* out,
+                     int64_t rows, int64_t cols);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PK_H_ */

@@ -1,0 +1,122 @@
+// Runtime entries of libpk: device selection, memory, copies, streams and the
+// per-thread error message. See include/pk.h for the contract of each call.
+#include <cstdarg>
+#include <cstring>
+
+#include "pk_common.cuh"
+
+namespace pk {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1;
+    static thread_local int cached = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return cached;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
+            cached = n;
+            cached_dev = dev;
+        }
+    }
+    return cached;
+}
+
+}  // namespace pk
+
+extern "C" {
+
+int pk_abi_version(void) { return PK_ABI_VERSION; }
+const char* pk_last_error(void) { return pk::g_err; }
+
+int pk_device_count(int* count_h) {
+    PK_REQUIRE(count_h != nullptr, "null output");
+    PK_CHECK_CUDA(cudaGetDeviceCount(count_h));
+    return PK_OK;
+}
+int pk_set_device(int device) {
+    PK_CHECK_CUDA(cudaSetDevice(device));
+    return PK_OK;
+}
+int pk_device_name(int device, char* name_h, size_t cap) {
+    PK_REQUIRE(name_h != nullptr && cap > 0, "null output");
+    cudaDeviceProp p;
+    PK_CHECK_CUDA(cudaGetDeviceProperties(&p, device));
+    snprintf(name_h, cap, "%s sm_%d%d", p.name, p.major, p.minor);
+    return PK_OK;
+}
+int pk_mem_info(size_t* free_h, size_t* total_h) {
+    PK_REQUIRE(free_h && total_h, "null output");
+    PK_CHECK_CUDA(cudaMemGetInfo(free_h, total_h));
+    return PK_OK;
+}
+int pk_malloc(void** ptr_h, size_t bytes) {
+    PK_REQUIRE(ptr_h != nullptr, "null output");
+    *ptr_h = nullptr;
+    if (bytes == 0) return PK_OK;
+    PK_CHECK_CUDA(cudaMalloc(ptr_h, bytes));
+    return PK_OK;
+}
+int pk_free(void* ptr) {
+    if (ptr) PK_CHECK_CUDA(cudaFree(ptr));
+    return PK_OK;
+}
+int pk_host_alloc(void** ptr_h, size_t bytes) {
+    PK_REQUIRE(ptr_h != nullptr, "null output");
+    PK_CHECK_CUDA(cudaMallocHost(ptr_h, bytes ? bytes : 1));
+    return PK_OK;
+}
+int pk_host_free(void* ptr_h) {
+    if (ptr_h) PK_CHECK_CUDA(cudaFreeHost(ptr_h));
+    return PK_OK;
+}
+int pk_memcpy_h2d(void* dst, const void* src_h, size_t bytes, void* stream) {
+    if (bytes == 0) return PK_OK;
+    PK_CHECK_CUDA(cudaMemcpyAsync(dst, src_h, bytes, cudaMemcpyHostToDevice, pk::as_stream(stream)));
+    return PK_OK;
+}
+int pk_memcpy_d2h(void* dst_h, const void* src, size_t bytes, void* stream) {
+    if (bytes == 0) return PK_OK;
+    PK_CHECK_CUDA(cudaMemcpyAsync(dst_h, src, bytes, cudaMemcpyDeviceToHost, pk::as_stream(stream)));
+    return PK_OK;
+}
+int pk_memcpy_d2d(void* dst, const void* src, size_t bytes, void* stream) {
+    if (bytes == 0) return PK_OK;
+    PK_CHECK_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, pk::as_stream(stream)));
+    return PK_OK;
+}
+int pk_memset(void* dst, int value, size_t bytes, void* stream) {
+    if (bytes == 0) return PK_OK;
+    PK_CHECK_CUDA(cudaMemsetAsync(dst, value, bytes, pk::as_stream(stream)));
+    return PK_OK;
+}
+int pk_stream_create(void** stream_h) {
+    PK_REQUIRE(stream_h != nullptr, "null output");
+    cudaStream_t s;
+    PK_CHECK_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *stream_h = s;
+    return PK_OK;
+}
+int pk_stream_destroy(void* stream) {
+    if (stream) PK_CHECK_CUDA(cudaStreamDestroy(pk::as_stream(stream)));
+    return PK_OK;
+}
+int pk_stream_sync(void* stream) {
+    PK_CHECK_CUDA(cudaStreamSynchronize(pk::as_stream(stream)));
+    return PK_OK;
+}
+int pk_device_sync(void) {
+    PK_CHECK_CUDA(cudaDeviceSynchronize());
+    return PK_OK;
+}
+
+}  // extern "C"
