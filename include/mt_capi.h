@@ -1,0 +1,87 @@
+/*
+ * mt_capi.h -- C driver entry points of libmicrotorch, the C++ host library that
+ * holds the tape (microtorch::backward / checkpoint), the ops, the layers and the
+ * model families. They let a host language without a C++ binding (the Python
+ * benchmark and test drivers use ctypes) build a model, run the checkpointed
+ * training step and read results back. Every call returns 0 on success; on failure
+ * the message is available from mt_last_error(). Pointers ending in _h are host
+ * pointers.
+ *
+ * The step these entries drive is the reference's own loop -- zero_grad, forward,
+ * ops::cross_entropy, backward, clip, AdamW::step -- as written in its
+ * tests/test_checkpointing.cpp:45-58 and tools/mtstudio.cpp:456-480.
+ */
+#ifndef MT_CAPI_H_
+#define MT_CAPI_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* mt_last_error(void);
+
+/* Selects GPU `device`, sets the compute dtype (0 = fp32, 1 = bf16 activations and
+ * GEMM operands with fp32 master weights, gradients of parameters and accumulation). */
+int mt_init(int device, int dtype);
+/* Run all work on this cudaStream_t (NULL: the library's own stream). */
+int mt_set_stream(void* cuda_stream);
+int mt_sync(void);
+
+/* spec: "key=value;key=value;..." with keys
+ *   family   llama | gpt2 | flex
+ *   vocab d layers heads kv_heads dff nctx theta tie rope_all qlora rank alpha seed
+ *   norm (layernorm|rmsnorm)  act (gelu|relu|swiglu)  pos (learned|sinusoidal)   [flex]
+ *   ckpt (0|1: per-block activation checkpointing)
+ *   pack (0|1, default 1: parameters, gradients and bf16 shadows in flat buffers)
+ * Unknown keys are an error. */
+int mt_model_create(const char* spec, void** model_h);
+int mt_model_destroy(void* model);
+int mt_model_set_checkpoint(void* model, int on);
+
+int mt_model_num_params(void* model, int64_t* n_h);
+int mt_model_param_info(void* model, int64_t index, char* name_h, size_t cap, int64_t* rows_h, int64_t* cols_h);
+int mt_model_param_get(void* model, int64_t index, float* out_h);
+int mt_model_param_set(void* model, int64_t index, const float* in_h);
+/* *has_grad_h = 0 when the parameter never received a gradient (out_h untouched). */
+int mt_model_grad_get(void* model, int64_t index, float* out_h, int* has_grad_h);
+
+/* One pass: zero_grad, forward over `n` token ids (B sequences of seq_len stacked;
+ * seq_len = 0 means one sequence), mean cross entropy against targets, scaled by
+ * loss_scale, and -- when do_backward != 0 -- the reverse pass. *loss_h receives the
+ * UNSCALED mean loss (read back after the backward was enqueued). */
+int mt_model_step(void* model, const int32_t* ids_h, const int32_t* targets_h, int64_t n, int64_t seq_len,
+                  float loss_scale, int do_backward, float* loss_h);
+/* Variables alive between forward and backward of the last mt_model_step (the
+ * reference's memory receipt for checkpointing, include/microtorch/autograd.hpp:61-64). */
+int mt_model_live_after_forward(void* model, int64_t* n_h);
+
+/* AdamW with the reference's defaults unless set (lr 1e-3, betas 0.9/0.999, eps 1e-8, wd 0.01). */
+int mt_model_set_adamw(void* model, float lr, float beta1, float beta2, float eps, float weight_decay);
+int mt_model_optimizer_step(void* model);
+int mt_model_clip_grad_norm(void* model, float max_norm, float* norm_h);
+
+/* Gradient ranges for data parallelism: bucket i < n-1 is the contiguous fp32 gradient
+ * range of transformer block i; the last bucket holds everything else (embeddings,
+ * final norm, head). Needs pack=1. */
+int mt_model_num_buckets(void* model, int64_t* n_h);
+int mt_model_bucket(void* model, int64_t index, void** ptr_h, int64_t* count_h);
+/* cb(k, user) runs on the calling thread right after the backward of the k-th
+ * checkpointed segment finished being enqueued (k counts from 0 per step, in reverse
+ * block order: k = 0 is the last block). NULL removes the hook. */
+typedef void (*mt_segment_cb)(int, void*);
+int mt_set_segment_hook(mt_segment_cb cb, void* user);
+
+/* out_h[0..5] = activation bytes in use, activation peak, persistent in use, persistent
+ * peak, bytes reserved from the driver, number of driver allocations. */
+int mt_mem_stats(uint64_t* out_h);
+int mt_reset_peak(void);
+int mt_empty_cache(void);
+int mt_live_variables(int64_t* n_h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MT_CAPI_H_ */

@@ -216,6 +216,12 @@ size_t pk_reduce_scratch_bytes(void);
 int pk_reduce_sum_f64(void* stream, const float* x, int64_t n, int square, int add, double* out,
                       void* scratch);
 
+/* out[0] = float(sum[0] / denom): turns the fp64 NLL sum into the mean loss without a
+ * host round trip (ops::cross_entropy, src/ops.cpp:368: out = float(nll / R)). */
+int pk_sum_to_mean(void* stream, const double* sum, double denom, float* out);
+/* dst[0..n) = value (devops::fill, include/microtorch/device_cache.hpp:104). */
+int pk_fill(void* stream, int dtype, void* dst, float value, int64_t n);
+
 /* ---- optimizer ---------------------------------------------------------------
  * AdamW::step (src/nn.cpp:301-321) over a flat fp32 buffer: m,v EMA, bias
  * correction c1 = 1-b1^t, c2 = 1-b2^t computed by the caller in float,

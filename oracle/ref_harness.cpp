@@ -332,6 +332,26 @@ struct CkptFlexLM {
     }
 };
 
+// Frozen tensors of the QLoRA harness (dequantized Q8_0 bases, embedding): written next
+// to the parameters so that a checker can rebuild the model without the C++ generator.
+template <class Model>
+void dump_frozen(const Model&, const std::string&) {}
+void dump_frozen(const GQALlama& m, const std::string& out) {
+    if (!m.cfg.qlora) return;
+    write_matrix(out, "frozen.embed_tokens.weight", m.embed_m);
+    for (size_t i = 0; i < m.blocks.size(); ++i) {
+        const std::string pre = "frozen.layers." + std::to_string(i) + ".";
+        const GQABlock& b = *m.blocks[i];
+        write_matrix(out, pre + "self_attn.q_proj.weight", b.q_proj->Wdq);
+        write_matrix(out, pre + "self_attn.k_proj.weight", b.k_proj->Wdq);
+        write_matrix(out, pre + "self_attn.v_proj.weight", b.v_proj->Wdq);
+        write_matrix(out, pre + "self_attn.o_proj.weight", b.o_proj->Wdq);
+        write_matrix(out, pre + "mlp.gate_proj.weight", b.gate_proj->Wdq);
+        write_matrix(out, pre + "mlp.up_proj.weight", b.up_proj->Wdq);
+        write_matrix(out, pre + "mlp.down_proj.weight", b.down_proj->Wdq);
+    }
+}
+
 // ---------------------------------------------------------------- step driver
 struct StepResult {
     double fwd_s = 0, bwd_s = 0, opt_s = 0;
@@ -365,6 +385,7 @@ StepResult run_steps(Model& model, const Args& a, const std::string& out) {
             names << n << " " << p->data.rows() << " " << p->data.cols() << "\n";
             write_matrix(out, "param." + n, p->data);
         }
+        dump_frozen(model, out);
     }
 
     nn::AdamW opt(params, static_cast<float>(a.getf("lr", 1e-3)));
@@ -627,18 +648,18 @@ void dump_quant(const std::string& out) {
     dumpq("q.ref64", t64);
     dumpq("q.q8_0", t32);
     // QLoRA linear: forward/backward with the harness layer (Q8_0 base + LoRA)
-    HLinear lin(96, 24, 5, 2, 4, 8.0f, 9);
-    Matrix x = filled_uniform(10, 96, 2, -1.0f, 1.0f), up = filled_uniform(10, 24, 3, -1.0f, 1.0f);
+    HLinear lin(96, 64, 5, 2, 4, 8.0f, 9);
+    Matrix x = filled_uniform(10, 96, 2, -1.0f, 1.0f), up = filled_uniform(10, 64, 3, -1.0f, 1.0f);
     write_matrix(out, "ql.x", x);
     write_matrix(out, "ql.up", up);
-    write_matrix(out, "ql.W0", filled_normal(96, 24, 5 * 7919u + 1u, 0.02f));
+    write_matrix(out, "ql.W0", filled_normal(96, 64, 5 * 7919u + 1u, 0.02f));
     write_matrix(out, "ql.Wdq", lin.Wdq);
     write_matrix(out, "ql.A", lin.A->data);
     write_matrix(out, "ql.B", lin.B->data);
     Var vx = make_var(x, true);
     Var y = lin.forward(vx);
     write_matrix(out, "ql.y", y->data);
-    Var loss = ops::scale(ops::mean(ops::mul(y, make_var(up))), 240.0f);
+    Var loss = ops::scale(ops::mean(ops::mul(y, make_var(up))), 640.0f);
     backward(loss);
     write_matrix(out, "ql.dx", vx->grad);
     write_matrix(out, "ql.dA", lin.A->grad);

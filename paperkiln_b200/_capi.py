@@ -23,6 +23,7 @@ _SCALARS = {
     "float": ctypes.c_float,
     "double": ctypes.c_double,
     "long": ctypes.c_long,
+    "mt_segment_cb": ctypes.c_void_p,  # function pointer typedef in mt_capi.h
 }
 
 _PROTO = re.compile(r"^\s*((?:const\s+)?[A-Za-z_][A-Za-z0-9_]*\s*\**)\s*\b((?:pk|mt)_[a-z0-9_]+)\s*\(([^;{]*)\)\s*;",

@@ -140,6 +140,18 @@ __global__ void reduce_stage2(const double* __restrict__ partial, int nparts, in
     out[0] = add ? out[0] + t : t;
 }
 
+__global__ void sum_to_mean_kernel(const double* sum, double denom, float* out) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) out[0] = static_cast<float>(sum[0] / denom);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) fill_kernel(T* p, float v, int64_t n) {
+    const T tv = from_f32<T>(v);
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * 256)
+        p[i] = tv;
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -221,6 +233,28 @@ int pk_reduce_sum_f64(void* stream, const float* x, int64_t n, int square, int a
     reduce_stage1<<<blocks, 256, 0, as_stream(stream)>>>(x, n, square, partial);
     PK_LAUNCH_CHECK();
     reduce_stage2<<<1, 32, 0, as_stream(stream)>>>(partial, blocks, add, out);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+int pk_sum_to_mean(void* stream, const double* sum, double denom, float* out) {
+    PK_REQUIRE(sum && out && denom != 0.0, "bad argument");
+    sum_to_mean_kernel<<<1, 32, 0, as_stream(stream)>>>(sum, denom, out);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+int pk_fill(void* stream, int dtype, void* dst, float value, int64_t n) {
+    PK_REQUIRE(valid_dtype(dtype) && n >= 0, "bad argument");
+    if (n == 0) return PK_OK;
+    PK_REQUIRE(dst != nullptr, "null pointer");
+    int64_t blocks = (n + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    if (dtype == PK_F32)
+        fill_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(static_cast<float*>(dst), value, n);
+    else
+        fill_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(static_cast<bf16*>(dst), value, n);
     PK_LAUNCH_CHECK();
     return PK_OK;
 }

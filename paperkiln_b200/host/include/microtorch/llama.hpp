@@ -1,0 +1,76 @@
+#pragma once
+// Llama-family model: RMSNorm, rotary embedding, SwiGLU, no biases; parameter names
+// follow HF LlamaForCausalLM ("layers.N.self_attn.q_proj.weight", ...).
+//
+// Reference: include/microtorch/llama.hpp:14-51 and src/llama.cpp:9-89. LlamaConfig
+// keeps the reference's fields and adds, with defaults that reproduce the reference:
+//   n_kv_heads      grouped-query attention (0 = n_heads, the reference's layout)
+//   rope_all_heads  false = the reference's behaviour, which rotates only the first
+//                   head of q and of k (src/ops.cpp:495-511 applied to the fused
+//                   [T,3d] layout); true = every head is rotated
+//   qlora           frozen Q8_0 base weights (embedding and norm gains frozen too)
+//                   with trainable LoRA adapters on q_proj and v_proj
+// The block is written against the fused ops: one attention node for all heads,
+// in-place rotary on the projection outputs, residual adds in the GEMM epilogues.
+#include "microtorch/nn.hpp"
+#include "microtorch/quant.hpp"
+
+namespace microtorch {
+namespace nn {
+
+struct LlamaConfig {
+    size_t vocab = 4096, d = 128, n_layers = 2, n_heads = 4;
+    size_t d_ff = 512;
+    size_t n_ctx = 256;
+    float rms_eps = 1e-6f;  // unused, as in the reference: ops::rmsnorm fixes eps = 1e-5
+    float rope_theta = 10000.0f;
+    bool tie_embeddings = true;
+    size_t n_kv_heads = 0;
+    bool rope_all_heads = false;
+    bool qlora = false;
+    size_t lora_rank = 16;
+    float lora_alpha = 32.0f;
+};
+
+// A projection that is either a trainable dense Linear or a frozen Q8_0 weight with an
+// optional LoRA side path (QLoRA mode).
+class Projection : public Module {
+public:
+    Projection(size_t in, size_t out, unsigned seed, bool quantized, bool lora, size_t rank, float alpha);
+    Var forward(const Var& x) const;
+    Var forward_residual(const Var& x, const Var& residual) const;
+    Var W;     // dense mode
+    Var A, B;  // LoRA (QLoRA mode, q/v projections)
+    std::shared_ptr<Q8Weight> Wq;
+    float scaling = 0.0f;
+};
+
+class LlamaBlock : public Module {
+public:
+    LlamaBlock(const LlamaConfig& cfg, unsigned seed);
+    Var forward(const Var& x, const std::vector<int>& positions, size_t seq_len = 0) const;
+
+    Var ln1_w, ln2_w;
+    std::shared_ptr<Projection> q_proj, k_proj, v_proj, o_proj;
+    std::shared_ptr<Projection> gate_proj, up_proj, down_proj;
+    size_t H, Hkv, dk;
+    float rope_theta_, rms_eps_;
+    bool rope_all_;
+};
+
+class Llama : public Module {
+public:
+    explicit Llama(const LlamaConfig& cfg, unsigned seed = 0);
+    Var forward(const std::vector<int>& ids, size_t seq_len = 0) const;
+
+    LlamaConfig cfg;
+    bool checkpoint_blocks = false;
+    std::shared_ptr<Embedding> embed_tokens;  // dense mode
+    Var embed_frozen;                          // QLoRA mode: not a registered parameter
+    std::vector<std::shared_ptr<LlamaBlock>> blocks;
+    Var norm_w;
+    std::shared_ptr<Linear> lm_head;  // null when tied
+};
+
+}  // namespace nn
+}  // namespace microtorch

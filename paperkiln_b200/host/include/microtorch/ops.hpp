@@ -1,0 +1,60 @@
+#pragma once
+// Tape ops: forward on the GPU through libpk + a backward closure per op.
+//
+// The first group keeps the names, argument meaning and error behaviour of the
+// reference's op set (include/microtorch/ops.hpp:12-163; formulas in src/ops.cpp),
+// restricted to the ops the transformer-block training step uses. The second group
+// are the fused forms the models in this library are written against; each one is
+// mathematically the composition named in its comment.
+#include <vector>
+
+#include "microtorch/autograd.hpp"
+
+namespace microtorch {
+namespace ops {
+
+// ---- reference op set (hot-path subset) ---------------------------------------
+Var matmul(const Var& a, const Var& b);      // [m,k]x[k,n]; dA = dC B^T, dB = A^T dC
+Var add(const Var& a, const Var& b);
+Var sub(const Var& a, const Var& b);
+Var mul(const Var& a, const Var& b);         // hadamard
+Var add_bias(const Var& x, const Var& b);    // b [1,n]; db = column sum
+Var gelu(const Var& x);                      // tanh form, exact derivative
+Var relu(const Var& x);
+Var silu(const Var& x);
+Var mean(const Var& x);                      // -> [1,1]
+Var scale(const Var& x, float s);
+Var transpose(const Var& x);
+Var slice_cols(const Var& x, size_t j0, size_t j1);
+Var concat_cols(const std::vector<Var>& xs);
+Var layernorm(const Var& x, const Var& gamma, const Var& beta, float eps = 1e-5f);
+Var rmsnorm(const Var& x, const Var& w);     // eps fixed at 1e-5 like the reference (src/ops.cpp:435)
+Var embedding(const Var& table, const std::vector<int>& ids);
+Var cross_entropy(const Var& logits, const std::vector<int>& targets);
+// qk is the fused [T, 3d] q|k|v layout. Like the reference (src/ops.cpp:495-511) this
+// rotates the first head_dim columns of q and of k only.
+Var apply_rope(const Var& qk, const std::vector<int>& pos, float theta_base, size_t head_dim);
+// One head: Y = softmax(scale Q K^T + block-causal mask) V as one tape node.
+Var fused_attention(const Var& q, const Var& k, const Var& v, float scale, size_t seq_len, bool causal);
+float clip_grad_norm(const std::vector<Var>& params, float max_norm);
+Matrix attention_mask(size_t rows, size_t seq_len, bool causal);
+
+// ---- fused forms ------------------------------------------------------------------
+// y = x W (+ bias) (+ residual): matmul + add_bias + add in one GEMM epilogue.
+// W is [in, out] (transposed_w = false) or [out, in] (true: y = x W^T, the tied head).
+Var linear(const Var& x, const Var& W, const Var& bias = nullptr, const Var& residual = nullptr,
+           bool transposed_w = false);
+// All heads at once on the [T, H*dk] layout (q: Hq heads; k, v: Hkv heads, Hq % Hkv == 0).
+// Equals the per-head slice_cols + fused_attention + concat_cols loop of the
+// reference's blocks (src/llama.cpp:44-52, src/nn.cpp:144-150).
+Var attention(const Var& q, const Var& k, const Var& v, size_t n_heads, size_t n_kv_heads, size_t seq_len,
+              bool causal);
+// Rotates the first `n_rot` heads (width head_dim) of x [T, H*head_dim] IN PLACE and
+// returns a node that shares x's buffer. x must have no other consumer and must be the
+// output of an op whose backward does not read its own output (a linear / matmul).
+Var rope_(const Var& x, const std::vector<int>& pos, float theta_base, size_t head_dim, size_t n_rot);
+// silu(gate) .* up in one pass (ops::mul(ops::silu(g), u)).
+Var swiglu(const Var& gate, const Var& up);
+
+}  // namespace ops
+}  // namespace microtorch

@@ -1,0 +1,28 @@
+#pragma once
+// Building blocks shared by the translation units that define tape ops (ops.cpp,
+// quant.cpp). Not part of the public surface.
+#include <functional>
+#include <vector>
+
+#include "microtorch/autograd.hpp"
+
+namespace microtorch {
+namespace ops {
+namespace detail {
+
+// Tape node around `result` unless grad is off or no parent requires it. Null parents
+// are dropped. `bw` reads self->grad and accumulates into self->parents.
+Var record_node(Tensor result, std::vector<Var> parents, std::function<void(Variable*)> bw);
+// Upstream gradient of a node as a tensor in the compute dtype.
+Tensor upstream(Variable* self);
+// C (+)= op(A).op(B) (+ bias) (+ residual) through pk_gemm.
+void gemm_raw(const Tensor& A, bool ta, const Tensor& B, bool tb, Tensor& C, bool accumulate,
+              const float* bias = nullptr, const Tensor* residual = nullptr);
+// target.grad += op(A).op(B), in the GEMM epilogue when the gradient buffer exists.
+void gemm_into_grad(const Var& target, const Tensor& A, bool ta, const Tensor& B, bool tb);
+// grad(b) += column sums of g
+void colsum_into_grad(const Var& b, const Tensor& g);
+
+}  // namespace detail
+}  // namespace ops
+}  // namespace microtorch

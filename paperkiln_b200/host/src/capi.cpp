@@ -1,0 +1,361 @@
+// C driver entry points (include/mt_capi.h) over the C++ host library.
+#include "mt_capi.h"
+
+#include <cstring>
+#include <map>
+#include <sstream>
+#include <stdexcept>
+#include <string>
+
+#include "microtorch/flex.hpp"
+#include "microtorch/llama.hpp"
+#include "microtorch/nn.hpp"
+
+using namespace microtorch;
+
+namespace {
+
+thread_local std::string g_err;
+
+struct Model {
+    std::string family;
+    std::shared_ptr<nn::Llama> llama;
+    std::shared_ptr<nn::GPT2> gpt2;
+    std::shared_ptr<parity::FlexLM> flex;
+    std::vector<std::pair<std::string, Var>> named;   // registration order
+    std::vector<Var> params;                          // packed order (blocks first)
+    std::vector<std::pair<size_t, size_t>> buckets;   // [first, last] index into params
+    nn::ParamPack pack;
+    bool packed = false;
+    std::unique_ptr<nn::AdamW> opt;
+    float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, wd = 0.01f;
+    int64_t live_after_fwd = 0;
+
+    Var forward(const std::vector<int>& ids, size_t seq_len) const {
+        if (llama) return llama->forward(ids, seq_len);
+        if (gpt2) return gpt2->forward(ids, seq_len);
+        return flex->forward(ids, seq_len);
+    }
+    void set_ckpt(bool on) {
+        if (llama) llama->checkpoint_blocks = on;
+        if (gpt2) gpt2->checkpoint_blocks = on;
+        if (flex) flex->checkpoint_blocks = on;
+    }
+};
+
+std::map<std::string, std::string> parse_spec(const char* spec) {
+    std::map<std::string, std::string> kv;
+    std::stringstream ss(spec ? spec : "");
+    std::string item;
+    while (std::getline(ss, item, ';')) {
+        if (item.empty()) continue;
+        const size_t eq = item.find('=');
+        if (eq == std::string::npos) throw std::runtime_error("model spec: expected key=value, got '" + item + "'");
+        kv[item.substr(0, eq)] = item.substr(eq + 1);
+    }
+    return kv;
+}
+
+struct SpecReader {
+    std::map<std::string, std::string> kv;
+    std::map<std::string, bool> used;
+    std::string str(const std::string& k, const std::string& d) {
+        used[k] = true;
+        auto it = kv.find(k);
+        return it == kv.end() ? d : it->second;
+    }
+    long num(const std::string& k, long d) {
+        used[k] = true;
+        auto it = kv.find(k);
+        return it == kv.end() ? d : std::stol(it->second);
+    }
+    double real(const std::string& k, double d) {
+        used[k] = true;
+        auto it = kv.find(k);
+        return it == kv.end() ? d : std::stod(it->second);
+    }
+    void finish() {
+        for (auto& e : kv)
+            if (!used.count(e.first)) throw std::runtime_error("model spec: unknown key '" + e.first + "'");
+    }
+};
+
+// Index of the transformer block a parameter belongs to, or -1.
+long block_of(const std::string& name) {
+    for (const char* prefix : {"layers.", "h."}) {
+        const size_t n = std::strlen(prefix);
+        if (name.compare(0, n, prefix) == 0) {
+            size_t end = n;
+            while (end < name.size() && std::isdigit(static_cast<unsigned char>(name[end]))) ++end;
+            if (end > n && end < name.size() && name[end] == '.') return std::stol(name.substr(n, end - n));
+        }
+    }
+    return -1;
+}
+
+template <typename F>
+int guard(F f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return 1;
+    } catch (...) {
+        g_err = "unknown exception";
+        return 1;
+    }
+}
+
+Model* M(void* h) {
+    if (!h) throw std::runtime_error("null model handle");
+    return static_cast<Model*>(h);
+}
+
+mt_segment_cb g_cb = nullptr;
+void* g_cb_user = nullptr;
+
+}  // namespace
+
+extern "C" {
+
+const char* mt_last_error(void) { return g_err.c_str(); }
+
+int mt_init(int dev, int dtype) {
+    return guard([&] {
+        if (dtype != 0 && dtype != 1) throw std::runtime_error("mt_init: dtype must be 0 (fp32) or 1 (bf16)");
+        device::init(dev);
+        device::set_compute_dtype(dtype == 1 ? DType::BF16 : DType::F32);
+    });
+}
+int mt_set_stream(void* s) {
+    return guard([&] { device::set_stream(s); });
+}
+int mt_sync(void) {
+    return guard([&] { device::synchronize(); });
+}
+
+int mt_model_create(const char* spec, void** out) {
+    return guard([&] {
+        if (!out) throw std::runtime_error("null output");
+        SpecReader r{parse_spec(spec), {}};
+        auto m = std::make_unique<Model>();
+        m->family = r.str("family", "llama");
+        const unsigned seed = static_cast<unsigned>(r.num("seed", 0));
+        const bool ckpt = r.num("ckpt", 0) != 0;
+        const bool pack = r.num("pack", 1) != 0;
+        if (m->family == "llama") {
+            nn::LlamaConfig c;
+            c.vocab = r.num("vocab", 4096);
+            c.d = r.num("d", 128);
+            c.n_layers = r.num("layers", 2);
+            c.n_heads = r.num("heads", 4);
+            c.n_kv_heads = r.num("kv_heads", 0);
+            c.d_ff = r.num("dff", 512);
+            c.n_ctx = r.num("nctx", 256);
+            c.rope_theta = static_cast<float>(r.real("theta", 10000.0));
+            c.tie_embeddings = r.num("tie", 1) != 0;
+            c.rope_all_heads = r.num("rope_all", 0) != 0;
+            c.qlora = r.num("qlora", 0) != 0;
+            c.lora_rank = r.num("rank", 16);
+            c.lora_alpha = static_cast<float>(r.real("alpha", 32.0));
+            r.finish();
+            m->llama = std::make_shared<nn::Llama>(c, seed);
+            m->named = m->llama->named_parameters();
+        } else if (m->family == "gpt2") {
+            nn::GPT2Config c;
+            c.vocab = r.num("vocab", 50257);
+            c.n_ctx = r.num("nctx", 1024);
+            c.d = r.num("d", 768);
+            c.n_layers = r.num("layers", 12);
+            c.n_heads = r.num("heads", 12);
+            r.finish();
+            m->gpt2 = std::make_shared<nn::GPT2>(c, seed);
+            m->named = m->gpt2->named_parameters();
+        } else if (m->family == "flex") {
+            parity::FlexConfig c;
+            c.vocab = r.num("vocab", 97);
+            c.d = r.num("d", 128);
+            c.n_layers = r.num("layers", 2);
+            c.n_heads = r.num("heads", 4);
+            c.d_ff = r.num("dff", 512);
+            c.n_ctx = r.num("nctx", 128);
+            c.norm = r.str("norm", "layernorm");
+            c.act = r.str("act", "gelu");
+            c.pos = r.str("pos", "learned");
+            r.finish();
+            m->flex = std::make_shared<parity::FlexLM>(c, seed);
+            m->named = m->flex->named_parameters();
+        } else {
+            throw std::runtime_error("model spec: family must be llama, gpt2 or flex");
+        }
+        m->set_ckpt(ckpt);
+        // Packed order: block 0, block 1, ..., then everything else.
+        long n_blocks = 0;
+        for (auto& np : m->named) n_blocks = std::max(n_blocks, block_of(np.first) + 1);
+        for (long b = 0; b < n_blocks; ++b) {
+            const size_t first = m->params.size();
+            for (auto& np : m->named)
+                if (block_of(np.first) == b) m->params.push_back(np.second);
+            if (m->params.size() > first) m->buckets.emplace_back(first, m->params.size() - 1);
+        }
+        const size_t first = m->params.size();
+        for (auto& np : m->named)
+            if (block_of(np.first) < 0) m->params.push_back(np.second);
+        if (m->params.size() > first) m->buckets.emplace_back(first, m->params.size() - 1);
+        if (pack) {
+            m->pack = nn::pack_parameters(m->params);
+            m->packed = true;
+        }
+        *out = m.release();
+    });
+}
+
+int mt_model_destroy(void* h) {
+    return guard([&] { delete static_cast<Model*>(h); });
+}
+int mt_model_set_checkpoint(void* h, int on) {
+    return guard([&] { M(h)->set_ckpt(on != 0); });
+}
+int mt_model_num_params(void* h, int64_t* n) {
+    return guard([&] { *n = static_cast<int64_t>(M(h)->named.size()); });
+}
+int mt_model_param_info(void* h, int64_t i, char* name, size_t cap, int64_t* rows, int64_t* cols) {
+    return guard([&] {
+        Model* m = M(h);
+        if (i < 0 || static_cast<size_t>(i) >= m->named.size()) throw std::runtime_error("parameter index out of range");
+        if (name && cap) std::snprintf(name, cap, "%s", m->named[i].first.c_str());
+        if (rows) *rows = static_cast<int64_t>(m->named[i].second->data.rows());
+        if (cols) *cols = static_cast<int64_t>(m->named[i].second->data.cols());
+    });
+}
+int mt_model_param_get(void* h, int64_t i, float* out) {
+    return guard([&] {
+        Model* m = M(h);
+        if (i < 0 || static_cast<size_t>(i) >= m->named.size()) throw std::runtime_error("parameter index out of range");
+        const Matrix& v = m->named[i].second->data.host();
+        std::memcpy(out, v.data(), v.size() * sizeof(float));
+    });
+}
+int mt_model_param_set(void* h, int64_t i, const float* in) {
+    return guard([&] {
+        Model* m = M(h);
+        if (i < 0 || static_cast<size_t>(i) >= m->named.size()) throw std::runtime_error("parameter index out of range");
+        Var& p = m->named[i].second;
+        Matrix v(p->data.rows(), p->data.cols());
+        std::memcpy(v.data(), in, v.size() * sizeof(float));
+        p->data = v;
+    });
+}
+int mt_model_grad_get(void* h, int64_t i, float* out, int* has) {
+    return guard([&] {
+        Model* m = M(h);
+        if (i < 0 || static_cast<size_t>(i) >= m->named.size()) throw std::runtime_error("parameter index out of range");
+        Var& p = m->named[i].second;
+        if (p->grad.empty()) {
+            if (has) *has = 0;
+            return;
+        }
+        if (has) *has = 1;
+        const Matrix& v = p->grad.host();
+        std::memcpy(out, v.data(), v.size() * sizeof(float));
+    });
+}
+
+int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64_t n, int64_t seq_len,
+                  float loss_scale, int do_backward, float* loss_h) {
+    return guard([&] {
+        Model* m = M(h);
+        if (n < 0 || seq_len < 0) throw std::runtime_error("negative size");
+        std::vector<int> ids(ids_h, ids_h + n), targets(targets_h, targets_h + n);
+        device::step_begin();
+        float loss_value = 0.0f;
+        if (do_backward) {
+            zero_grad(m->params);
+            const size_t live0 = live_variables();
+            Var logits = m->forward(ids, static_cast<size_t>(seq_len));
+            Var loss = ops::cross_entropy(logits, targets);
+            logits.reset();
+            m->live_after_fwd = static_cast<int64_t>(live_variables() - live0);
+            Var root = loss_scale == 1.0f ? loss : ops::scale(loss, loss_scale);
+            backward(root);
+            loss_value = loss->data(0, 0);
+        } else {
+            NoGrad ng;
+            Var logits = m->forward(ids, static_cast<size_t>(seq_len));
+            Var loss = ops::cross_entropy(logits, targets);
+            loss_value = loss->data(0, 0);
+        }
+        device::step_end();
+        if (loss_h) *loss_h = loss_value;
+    });
+}
+
+int mt_model_live_after_forward(void* h, int64_t* n) {
+    return guard([&] { *n = M(h)->live_after_fwd; });
+}
+
+int mt_model_set_adamw(void* h, float lr, float b1, float b2, float eps, float wd) {
+    return guard([&] {
+        Model* m = M(h);
+        if (m->opt) throw std::runtime_error("optimizer already created; set hyper-parameters before the first step");
+        m->lr = lr; m->b1 = b1; m->b2 = b2; m->eps = eps; m->wd = wd;
+    });
+}
+int mt_model_optimizer_step(void* h) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!m->opt) m->opt = std::make_unique<nn::AdamW>(m->params, m->lr, m->b1, m->b2, m->eps, m->wd);
+        m->opt->step();
+    });
+}
+int mt_model_clip_grad_norm(void* h, float max_norm, float* norm) {
+    return guard([&] {
+        const float n = ops::clip_grad_norm(M(h)->params, max_norm);
+        if (norm) *norm = n;
+    });
+}
+
+int mt_model_num_buckets(void* h, int64_t* n) {
+    return guard([&] { *n = static_cast<int64_t>(M(h)->buckets.size()); });
+}
+int mt_model_bucket(void* h, int64_t i, void** ptr, int64_t* count) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!m->packed) throw std::runtime_error("gradient buckets need a packed model (pack=1)");
+        if (i < 0 || static_cast<size_t>(i) >= m->buckets.size()) throw std::runtime_error("bucket index out of range");
+        const size_t first = m->buckets[i].first, last = m->buckets[i].second;
+        const size_t begin = m->pack.offset[first];
+        const size_t end = last + 1 < m->pack.offset.size() ? m->pack.offset[last + 1] : m->pack.total;
+        *ptr = m->pack.grad.f32() + begin;
+        *count = static_cast<int64_t>(end - begin);
+    });
+}
+
+int mt_set_segment_hook(mt_segment_cb cb, void* user) {
+    return guard([&] {
+        g_cb = cb;
+        g_cb_user = user;
+        if (cb) autograd::set_segment_hook([](int k) { if (g_cb) g_cb(k, g_cb_user); });
+        else autograd::set_segment_hook(nullptr);
+    });
+}
+
+int mt_mem_stats(uint64_t* out) {
+    return guard([&] {
+        const device::MemStats s = device::mem_stats();
+        out[0] = s.in_use[0]; out[1] = s.peak[0]; out[2] = s.in_use[1]; out[3] = s.peak[1];
+        out[4] = s.reserved; out[5] = s.driver_allocs;
+    });
+}
+int mt_reset_peak(void) {
+    return guard([&] { device::reset_peak(); });
+}
+int mt_empty_cache(void) {
+    return guard([&] { device::empty_cache(); });
+}
+int mt_live_variables(int64_t* n) {
+    return guard([&] { *n = static_cast<int64_t>(live_variables()); });
+}
+
+}  // extern "C"

@@ -1,0 +1,109 @@
+// Llama-family model. Behavioural reference: src/llama.cpp of paperkiln
+// (LlamaBlock 9-60, Llama 62-89).
+#include "microtorch/llama.hpp"
+
+#include <cmath>
+#include <stdexcept>
+
+namespace microtorch {
+namespace nn {
+
+Projection::Projection(size_t in, size_t out, unsigned seed, bool quantized, bool lora, size_t rank, float alpha) {
+    // Same generator and seed as nn::Linear, so dense mode owns the reference's weights.
+    Matrix W0 = randn(in, out, seed * 7919u + 1u, 0.02f);
+    if (!quantized) {
+        W = reg("weight", std::move(W0));
+        return;
+    }
+    Wq = std::make_shared<Q8Weight>(Q8Weight::from_matrix(W0));
+    if (lora) {
+        A = reg("lora_A", randn(in, rank, seed * 31u + 5u, 0.02f));
+        B = reg("lora_B", randn(rank, out, seed * 31u + 6u, 0.01f));
+        scaling = alpha / static_cast<float>(rank);
+    }
+}
+
+Var Projection::forward(const Var& x) const { return forward_residual(x, nullptr); }
+
+Var Projection::forward_residual(const Var& x, const Var& residual) const {
+    if (W) return ops::linear(x, W, nullptr, residual);
+    Var base = ops::q8_linear(x, Wq, nullptr, residual);
+    if (!A) return base;
+    Var xa = ops::scale(ops::matmul(x, A), scaling);
+    return ops::linear(xa, B, nullptr, base);
+}
+
+LlamaBlock::LlamaBlock(const LlamaConfig& cfg, unsigned seed)
+    : H(cfg.n_heads), Hkv(cfg.n_kv_heads ? cfg.n_kv_heads : cfg.n_heads), dk(cfg.d / cfg.n_heads),
+      rope_theta_(cfg.rope_theta), rms_eps_(cfg.rms_eps), rope_all_(cfg.rope_all_heads) {
+    if (cfg.d % cfg.n_heads != 0) throw std::runtime_error("llama: d must divide by n_heads");
+    if (H % Hkv != 0) throw std::runtime_error("llama: n_heads must be a multiple of n_kv_heads");
+    const bool q = cfg.qlora;
+    if (q) {  // frozen gains: plain leaves, not registered
+        ln1_w = make_var(Matrix(1, cfg.d, 1.0f), false);
+        ln2_w = make_var(Matrix(1, cfg.d, 1.0f), false);
+    } else {
+        ln1_w = reg("input_layernorm.weight", Matrix(1, cfg.d, 1.0f));
+        ln2_w = reg("post_attention_layernorm.weight", Matrix(1, cfg.d, 1.0f));
+    }
+    const size_t r = cfg.lora_rank;
+    const float a = cfg.lora_alpha;
+    q_proj = mod<Projection>("self_attn.q_proj", cfg.d, H * dk, seed + 1, q, q, r, a);
+    k_proj = mod<Projection>("self_attn.k_proj", cfg.d, Hkv * dk, seed + 2, q, false, r, a);
+    v_proj = mod<Projection>("self_attn.v_proj", cfg.d, Hkv * dk, seed + 3, q, q, r, a);
+    o_proj = mod<Projection>("self_attn.o_proj", H * dk, cfg.d, seed + 4, q, false, r, a);
+    gate_proj = mod<Projection>("mlp.gate_proj", cfg.d, cfg.d_ff, seed + 5, q, false, r, a);
+    up_proj = mod<Projection>("mlp.up_proj", cfg.d, cfg.d_ff, seed + 6, q, false, r, a);
+    down_proj = mod<Projection>("mlp.down_proj", cfg.d_ff, cfg.d, seed + 7, q, false, r, a);
+}
+
+Var LlamaBlock::forward(const Var& x, const std::vector<int>& pos, size_t seq_len) const {
+    // ---- attention sublayer (pre-RMSNorm)
+    Var h = ops::rmsnorm(x, ln1_w);
+    Var q = q_proj->forward(h);
+    Var k = k_proj->forward(h);
+    Var v = v_proj->forward(h);
+    q = ops::rope_(q, pos, rope_theta_, dk, rope_all_ ? H : 1);
+    k = ops::rope_(k, pos, rope_theta_, dk, rope_all_ ? Hkv : 1);
+    Var a = ops::attention(q, k, v, H, Hkv, seq_len, /*causal=*/true);
+    Var x1 = o_proj->forward_residual(a, x);  // x + attn
+    // ---- SwiGLU FFN sublayer
+    Var h2 = ops::rmsnorm(x1, ln2_w);
+    Var f = ops::swiglu(gate_proj->forward(h2), up_proj->forward(h2));
+    return down_proj->forward_residual(f, x1);  // x1 + ffn
+}
+
+Llama::Llama(const LlamaConfig& cfg_, unsigned seed) : cfg(cfg_) {
+    if (cfg.qlora) {
+        embed_frozen = make_var(randn(cfg.vocab, cfg.d, (seed + 11) * 104729u + 3u, 0.02f), false);
+    } else {
+        embed_tokens = mod<Embedding>("embed_tokens", cfg.vocab, cfg.d, seed + 11);
+    }
+    for (size_t i = 0; i < cfg.n_layers; ++i)
+        blocks.push_back(mod<LlamaBlock>("layers." + std::to_string(i), cfg, seed + 100 * static_cast<unsigned>(i + 1)));
+    if (cfg.qlora) norm_w = make_var(Matrix(1, cfg.d, 1.0f), false);
+    else norm_w = reg("norm.weight", Matrix(1, cfg.d, 1.0f));
+    if (!cfg.tie_embeddings && !cfg.qlora) lm_head = mod<Linear>("lm_head", cfg.d, cfg.vocab, false, seed + 12);
+}
+
+Var Llama::forward(const std::vector<int>& ids, size_t seq_len) const {
+    const size_t sl = seq_len == 0 ? ids.size() : seq_len;
+    if (sl == 0 || ids.size() % sl != 0) throw std::runtime_error("ids not a multiple of seq_len");
+    std::vector<int> pos(ids.size());
+    for (size_t i = 0; i < pos.size(); ++i) pos[i] = static_cast<int>(i % sl);
+    const Var& table = cfg.qlora ? embed_frozen : embed_tokens->weight;
+    Var h = ops::embedding(table, ids);
+    for (const auto& b : blocks) {
+        h = checkpoint_blocks && grad_enabled()
+                ? checkpoint([b, pos, seq_len](const Var& in) { return b->forward(in, pos, seq_len); }, h)
+                : b->forward(h, pos, seq_len);
+    }
+    h = ops::rmsnorm(h, norm_w);
+    if (lm_head) return lm_head->forward(h);
+    // Tied head: logits = h E^T; the embedding receives gradient from the gather and
+    // from this GEMM (src/llama.cpp:85-88). No transposed copy of E is made.
+    return ops::linear(h, table, nullptr, nullptr, /*transposed_w=*/true);
+}
+
+}  // namespace nn
+}  // namespace microtorch

@@ -15,3 +15,18 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+import pytest
+
+
+@pytest.fixture(autouse=True)
+def _release_scratch():
+    yield
+    try:
+        from tests import pkt
+        import torch
+        if pkt._live and torch.cuda.is_available():
+            pkt.release()
+    except ImportError:
+        pass

@@ -24,9 +24,21 @@ def stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+_live = []
+
+
 def scratch(nbytes: int) -> torch.Tensor:
-    # filled with garbage on purpose: results must not depend on scratch contents
-    return torch.full((max(int(nbytes), 16),), 0x5A, dtype=torch.uint8, device="cuda")
+    # filled with garbage on purpose: results must not depend on scratch contents.
+    # The tensor stays referenced (until release()) so that its memory cannot be handed
+    # to another allocation while a kernel still uses it.
+    t = torch.full((max(int(nbytes), 16),), 0x5A, dtype=torch.uint8, device="cuda")
+    _live.append(t)
+    return t
+
+
+def release():
+    torch.cuda.synchronize()
+    _live.clear()
 
 
 def gemm(A, B, *, ta=False, tb=False, out_dtype=None, C=None, accumulate=False, bias=None,

@@ -397,8 +397,10 @@ def test_embedding_and_cross_entropy(pk, dtype):
     uniq, counts = np.unique(ids_h, return_counts=True)
     seg = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
     dtab = torch.zeros(V, d, device="cuda")
-    pkt.check(pk.pk_embedding_bwd(stream(), dt(dy), ptr(dy), ptr(torch.from_numpy(order).cuda()),
-                                  ptr(torch.from_numpy(seg).cuda()), ptr(torch.from_numpy(uniq.astype(np.int32)).cuda()),
+    # keep the index tensors referenced until the kernel has run
+    order_d, seg_d = torch.from_numpy(order).cuda(), torch.from_numpy(seg).cuda()
+    uniq_d = torch.from_numpy(uniq.astype(np.int32)).cuda()
+    pkt.check(pk.pk_embedding_bwd(stream(), dt(dy), ptr(dy), ptr(order_d), ptr(seg_d), ptr(uniq_d),
                                   len(uniq), ptr(dtab), d))
     ref = np.zeros((V, d), dtype=np.float32)
     dyh = dy.float().cpu().numpy()
@@ -411,7 +413,8 @@ def test_embedding_and_cross_entropy(pk, dtype):
         tg = torch.randint(0, Vv, (Rr,), generator=g, dtype=torch.int32).cuda()
         lf = logits.float()
         P = torch.softmax(lf, dim=1)
-        ref_rows = -torch.log(torch.clamp(P[torch.arange(Rr), tg.long()], min=1e-12))
+        ar = torch.arange(Rr, device="cuda")
+        ref_rows = -torch.log(torch.clamp(P[ar, tg.long()], min=1e-12))
         work = logits.clone()
         rows = torch.empty(Rr, device="cuda")
         status.zero_()
@@ -419,7 +422,7 @@ def test_embedding_and_cross_entropy(pk, dtype):
                                       ptr(status)))
         close(rows, ref_rows, 2e-5, 1e-5)
         dref = P.clone()
-        dref[torch.arange(Rr), tg.long()] -= 1.0
+        dref[ar, tg.long()] -= 1.0
         tol = 1e-6 if dtype == torch.float32 else 1e-3
         close(work, dref / Rr, tol, 0 if dtype == torch.float32 else 2 ** -7)
         total = torch.zeros(1, dtype=torch.float64, device="cuda")
