@@ -1,0 +1,439 @@
+#!/usr/bin/env python
+"""Benchmark of the activation-checkpointed transformer training step.
+
+    python bench.py --gpus N --steps K --warmup W [--workload c4] [--impl reference]
+
+One "step" = zero_grad + forward + cross entropy + backward with per-block recompute +
+(N > 1: fp32 gradient all-reduce overlapped with the backward) + AdamW, on one batch of
+synthetic token ids. Prints ONE JSON line (rank 0). Workloads are the configurations of
+the task's baseline file:
+  c1  tiny Llama fp32 (4 layers, d 128, batch 8 x 256)            -- the CPU-parity case
+  c2  GPT-2-small shape, bf16, batch 16 x 1024
+  c3  Qwen2.5-0.5B-shape QLoRA (Q8_0 frozen base, LoRA r=16), bf16, batch 8 x 2048
+  c4  Llama-1B shape, bf16, global batch 64 x 4096 (default; sharded by batch over N GPUs)
+Keys of the JSON line: metric/value (tokens/s, whole job, inputs resident on the device),
+e2e (same through the public step API with host token buffers), roofline (tcgen05 GEMM:
+achieved TFLOP/s from CUDA events around every launch in the timed region), cpu_baseline
+(the unmodified reference's CPU path on a bounded sample, rank 0 at N=1), clocks, peak
+activation memory with and without checkpointing (reported in `config`).
+
+`--impl reference` times the reference's own CPU implementation (oracle/_ref/ref_harness,
+built by oracle/Makefile from the reference's sources) on a bounded sample of the same
+workload and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    "c1": dict(family="llama", dtype="fp32", vocab=4096, d=128, layers=4, heads=4, kv_heads=0, dff=512, nctx=256,
+               theta=10000.0, rope_all=0, qlora=0, batch=8, seq=256,
+               name="tiny Llama fp32 (4L d128 H4 dff512 V4096), batch 8 x 256"),
+    "c2": dict(family="gpt2", dtype="bf16", vocab=50257, d=768, layers=12, heads=12, nctx=1024, batch=16, seq=1024,
+               name="GPT-2-small shape (12L d768 H12 dff3072 V50257), bf16, batch 16 x 1024"),
+    "c3": dict(family="llama", dtype="bf16", vocab=151936, d=896, layers=24, heads=14, kv_heads=2, dff=4864,
+               nctx=2048, theta=1e6, rope_all=1, qlora=1, rank=16, alpha=32, batch=8, seq=2048,
+               name="Qwen2.5-0.5B-shape QLoRA (24L d896 Hq14/Hkv2 dff4864 V151936, Q8_0 base, LoRA r16 q/v), "
+                    "bf16, batch 8 x 2048"),
+    "c4": dict(family="llama", dtype="bf16", vocab=32000, d=2048, layers=16, heads=32, kv_heads=8, dff=8192,
+               nctx=4096, theta=500000.0, rope_all=1, qlora=0, batch=64, seq=4096,
+               name="Llama-1B shape (16L d2048 Hq32/Hkv8 dff8192 V32000), bf16 + fp32 master/AdamW, "
+                    "global batch 64 x 4096"),
+}
+
+
+def model_spec(w, ckpt):
+    if w["family"] == "gpt2":
+        return dict(family="gpt2", vocab=w["vocab"], d=w["d"], layers=w["layers"], heads=w["heads"], nctx=w["nctx"],
+                    seed=0, ckpt=int(ckpt))
+    s = dict(family="llama", vocab=w["vocab"], d=w["d"], layers=w["layers"], heads=w["heads"],
+             kv_heads=w["kv_heads"], dff=w["dff"], nctx=w["nctx"], theta=w["theta"], rope_all=w["rope_all"], tie=1,
+             seed=0, ckpt=int(ckpt))
+    if w.get("qlora"):
+        s.update(qlora=1, rank=w["rank"], alpha=w["alpha"])
+    return s
+
+
+def flops_per_token(w):
+    """Algorithmic dense FLOPs per token: forward block, attention (causal average), head."""
+    d, L, V, S = w["d"], w["layers"], w["vocab"], w["seq"]
+    H = w["heads"]
+    Hkv = w.get("kv_heads") or H
+    dk = d // H
+    dq, dkv = H * dk, Hkv * dk
+    if w["family"] == "gpt2":
+        f_blk = 2 * (d * 3 * d + d * d + 2 * d * 4 * d)
+    else:
+        f_blk = 2 * (d * dq + 2 * d * dkv + dq * d + 3 * d * w["dff"])
+    f_attn = 4 * (S / 2) * dq
+    f_head = 2 * d * V
+    return f_blk, f_attn, f_head
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        # the first samples precede the load; the median over the region is what counts
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def ref_harness_args(w, sample_tokens):
+    fam = {"gpt2": "gpt2"}.get(w["family"], "llama")
+    a = {"family": fam, "vocab": w["vocab"], "d": w["d"], "layers": w["layers"], "heads": w["heads"],
+         "batch": 1, "seq": sample_tokens, "seed": 0, "data-seed": 0, "ckpt": 1, "adamw": 1}
+    if fam == "gpt2":
+        a["nctx"] = w["nctx"]
+    else:
+        a["dff"] = w["dff"]
+        a["theta"] = w["theta"]
+        if w.get("qlora"):
+            a.update(family="qlora", rank=w["rank"], alpha=w["alpha"])
+            a["kv-heads"] = w["kv_heads"]
+        elif w.get("kv_heads"):
+            a["family"] = "llamagqa"
+            a["kv-heads"] = w["kv_heads"]
+    return a
+
+
+def run_reference(w, steps, warmup, sample_tokens):
+    """Times the unmodified reference's CPU path on a bounded sample of the workload."""
+    harness = ROOT / "oracle" / "_ref" / "ref_harness"
+    if not harness.exists():
+        return None, f"{harness} missing (built by `make -C oracle` from the reference's sources)"
+    args = ref_harness_args(w, sample_tokens)
+    argv = [str(harness), "bench"]
+    for k, v in args.items():
+        argv += [f"--{k}", str(v)]
+    argv += ["--steps", str(steps + warmup), "--warmup", str(warmup)]
+    t0 = time.time()
+    res = subprocess.run(argv, capture_output=True, text=True)
+    if res.returncode != 0:
+        return None, f"reference harness failed: {res.stderr[-300:]}"
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    out = json.loads(line)
+    out["wall_s_total"] = time.time() - t0
+    out["sample"] = (f"{steps} timed step(s) of {sample_tokens} tokens (1 sequence) of the same model, reference "
+                     f"CPU fp32 path with per-block checkpointing + AdamW")
+    return out, None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=os.environ.get("PK_BENCH_WORKLOAD", "c4"), choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="override the global batch (sequences)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=0)
+    ap.add_argument("--skip-nockpt", action="store_true", help="do not measure the un-checkpointed step")
+    args = ap.parse_args()
+
+    w = dict(WORKLOADS[args.workload])
+    if args.batch:
+        w["batch"] = args.batch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    sample_tokens = args.cpu_sample_tokens or {"c1": 2048, "c2": 64, "c3": 64, "c4": 16}[args.workload]
+    if args.workload == "c1":
+        sample_tokens = 256  # per sequence; the harness batches 8 of them below
+
+    base = {"metric": "train tokens/s with per-block activation recompute", "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": f"{args.workload}: {w['name']}", "global_batch": w["batch"], "seq_len": w["seq"],
+                       "parallelism": f"dp{args.gpus}", "l2": "inputs and activations exceed L2 (126 MB)"}}
+
+    # ------------------------------------------------------------------ reference arm
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        out, err = run_reference(w, args.steps, max(args.warmup, 0), sample_tokens)
+        if out is None:
+            print(json.dumps({"impl": "reference", "unavailable": err}))
+            return 0
+        line = dict(base)
+        line.update({"impl": "reference", "value": out["tokens_per_s"], "ms_per_step": out["step_s"] * 1e3,
+                     "dtype": "f32", "gpu_launches": 0,
+                     "cpu_baseline": {"value": out["tokens_per_s"], "unit": "tokens/s", "cores": 1, "kind": "reference",
+                                      "sample": out["sample"], "host_threads": os.cpu_count(),
+                                      "note": "the reference's GEMM (~95% of its step) is single-threaded by "
+                                              "construction; OpenMP covers elementwise ops only"},
+                     "e2e": {"value": out["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
+                             "d2h_bytes_per_step": 0}})
+        print(json.dumps(line))
+        return 0
+
+    # ------------------------------------------------------------------ our arm
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU execution path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from paperkiln_b200 import model as mt
+    from paperkiln_b200._capi import libpk
+
+    pk = libpk()
+    mt.init(local_rank, mt.BF16 if w["dtype"] == "bf16" else mt.FP32)
+    stream = torch.cuda.current_stream()
+    mt.set_stream(stream.cuda_stream)
+
+    B, S = w["batch"], w["seq"]
+    if B % world:
+        raise SystemExit(f"global batch {B} does not divide over {world} ranks")
+    Bl = B // world
+    n_local = Bl * S
+    tokens_global = B * S
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # synthetic token stream: ids = rng % vocab, targets = ids shifted by one; rank r takes
+    # sequences [r*B/g, (r+1)*B/g) of every global batch
+    n_batches = args.warmup + args.steps + 1
+    rng = np.random.RandomState(1234)
+    host_ids, host_tg = [], []
+    for _ in range(n_batches):
+        stream_ids = rng.randint(0, w["vocab"], size=tokens_global + 1).astype(np.int32)
+        lo = rank * n_local
+        ids = torch.from_numpy(stream_ids[lo:lo + n_local].copy()).pin_memory()
+        tg = torch.from_numpy(stream_ids[lo + 1:lo + n_local + 1].copy()).pin_memory()
+        host_ids.append(ids)
+        host_tg.append(tg)
+
+    def build(ckpt):
+        m = mt.Model(**model_spec(w, ckpt))
+        m.set_adamw()
+        return m
+
+    class _Buf:
+        def __init__(self, ptr, n):
+            self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+    def make_step(m):
+        buckets = [torch.as_tensor(_Buf(p, n), device="cuda") for (p, n) in m.buckets()] if world > 1 else []
+        pending = []
+        n_blocks = len(buckets) - 1
+
+        def hook(k):  # block (n_blocks-1-k) finished its backward: start its all-reduce
+            i = n_blocks - 1 - k
+            if 0 <= i < n_blocks:
+                pending.append(dist.all_reduce(buckets[i], op=dist.ReduceOp.SUM, async_op=True))
+
+        if world > 1:
+            mt.set_segment_hook(hook)
+
+        def step(i):
+            loss = m.step_ptr(host_ids[i].data_ptr(), host_tg[i].data_ptr(), n_local, S, loss_scale=1.0 / world)
+            if world > 1:
+                pending.append(dist.all_reduce(buckets[-1], op=dist.ReduceOp.SUM, async_op=True))
+                for h in pending:
+                    h.wait()
+                pending.clear()
+            m.optimizer_step()
+            return loss
+        return step
+
+    def timed(step_fn, indices):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        loss = None
+        for i in indices:
+            loss = step_fn(i)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, loss
+
+    # ---- checkpointed model: warm-up, then the two timed regions
+    m = build(ckpt=True)
+    step_fn = make_step(m)
+    for i in range(args.warmup):
+        step_fn(i)
+    barrier()
+    mt.reset_peak()
+    # (1) e2e: a fresh host batch every step (H2D of ids and targets inside the region, loss read back)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    pk.pk_prof_reset()
+    pk.pk_prof_enable(1)
+    e2e_ms, loss = timed(step_fn, range(args.warmup, args.warmup + args.steps))
+    pk.pk_prof_enable(0)
+    clocks = sampler.stop()
+    peak_ckpt = mt.mem_stats()["activation_peak"]
+    import ctypes
+    prof = {}
+    for kind, name in ((0, "gemm_tc"), (1, "gemm_simt"), (2, "attn_fwd"), (3, "attn_bwd")):
+        ms_, work_, n_ = ctypes.c_double(0), ctypes.c_double(0), ctypes.c_int64(0)
+        pk.pk_prof_summary(kind, ctypes.byref(ms_), ctypes.byref(work_), ctypes.byref(n_))
+        prof[name] = {"ms": ms_.value, "flops": work_.value, "launches": n_.value}
+    # (2) value: the same batch every step -- its ids/targets are already on the device
+    # (the library caches uploaded index arrays by content), so no input crosses PCIe
+    last = args.warmup + args.steps
+    step_fn(last)
+    res_ms, _ = timed(step_fn, [last] * args.steps)
+    stats = mt.mem_stats()
+    m.close()
+    mt.set_segment_hook(None)
+
+    # ---- the same step without checkpointing, for the activation-memory comparison
+    peak_plain, plain_ms = None, None
+    if not args.skip_nockpt:
+        try:
+            mt.empty_cache()
+            m2 = build(ckpt=False)
+            step2 = make_step(m2)
+            step2(0)
+            barrier()
+            mt.reset_peak()
+            plain_ms, _ = timed(step2, [1, 2])
+            plain_ms /= 2
+            peak_plain = mt.mem_stats()["activation_peak"]
+            m2.close()
+            mt.set_segment_hook(None)
+        except Exception as e:  # does not fit without checkpointing at this size
+            peak_plain = f"unavailable: {str(e)[:120]}"
+            mt.empty_cache()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+    peak_src = "measured (MEASURED_PEAKS.json, sustained cuBLAS bf16)" if peaks else "fallback 1.4 PFLOP/s"
+    g = prof["gemm_tc"]
+    achieved = g["flops"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else 0.0
+    f_blk, f_attn, f_head = flops_per_token(w)
+    L = w["layers"]
+    step_flops = (L * 4 * (f_blk + f_attn) + 3 * f_head) * tokens_global
+    model_flops = 3 * (L * (f_blk + f_attn) + f_head) * tokens_global
+    launches = sum(p["launches"] for p in prof.values())
+    line = dict(base)
+    line["value"] = tokens_global / (res_ms / args.steps * 1e-3)
+    line["ms_per_step"] = res_ms / args.steps
+    line["e2e"] = {"value": tokens_global / (e2e_ms / args.steps * 1e-3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": 2 * n_local * 4 * world, "d2h_bytes_per_step": 4 * world,
+                   "ms_per_step": e2e_ms / args.steps}
+    line["loss"] = loss
+    line["clocks"] = clocks
+    line["gpu_launches"] = int(launches)
+    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM)", "achieved": achieved,
+                        "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf if peak_tf else None,
+                        "peak_source": peak_src, "traffic": None,
+                        "share_of_step": g["ms"] / e2e_ms if e2e_ms else None, "launches_timed": g["launches"]}
+    line["kernels"] = {k: {"ms_per_step": v["ms"] / args.steps,
+                           "tflops": (v["flops"] / (v["ms"] * 1e-3) / 1e12) if v["ms"] > 0 else None,
+                           "launches_per_step": v["launches"] / args.steps} for k, v in prof.items()}
+    line["step_tflops_executed"] = step_flops / (res_ms / args.steps * 1e-3) / 1e12 / args.gpus
+    line["mfu_model_flops"] = model_flops / (res_ms / args.steps * 1e-3) / 1e12 / args.gpus / (peaks.get("bf16_tflops", 1676.5))
+    line["config"].update({
+        "peak_activation_gib_checkpointed": peak_ckpt / 2 ** 30,
+        "peak_activation_gib_plain": (peak_plain / 2 ** 30) if isinstance(peak_plain, int) else peak_plain,
+        "ms_per_step_plain": plain_ms,
+        "persistent_gib": stats["persistent_peak"] / 2 ** 30,
+    })
+    if not args.no_cpu_baseline and world == 1:
+        hw = dict(w)
+        if args.workload == "c1":
+            out, err = run_reference_c1(hw)
+        else:
+            out, err = run_reference(hw, 1, 0, sample_tokens)
+        if out is not None:
+            line["cpu_baseline"] = {"value": out["tokens_per_s"], "unit": "tokens/s", "cores": 1, "kind": "reference",
+                                    "sample": out["sample"], "host_threads": os.cpu_count()}
+        else:
+            line["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 1, "kind": "reference", "sample": err}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_reference_c1(w):
+    """Config 1 is the reference's own CPU-runnable case: one full-size step (8 x 256 tokens)."""
+    harness = ROOT / "oracle" / "_ref" / "ref_harness"
+    if not harness.exists():
+        return None, f"{harness} missing"
+    argv = [str(harness), "bench", "--family", "llama", "--vocab", "4096", "--d", "128", "--layers", "4", "--heads", "4",
+            "--dff", "512", "--nctx", "256", "--batch", "8", "--seq", "256", "--ckpt", "1", "--steps", "1"]
+    res = subprocess.run(argv, capture_output=True, text=True)
+    if res.returncode != 0:
+        return None, res.stderr[-300:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    out["sample"] = "1 full-size step (8 x 256 tokens), reference CPU fp32 path with checkpointing + AdamW"
+    return out, None
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -68,6 +68,17 @@ int pk_device_sync(void);
 /* Device status word: kernels that detect an out-of-range id or a wait that
  * ran out OR a code into *status (int32 on the device) instead of trapping. */
 
+/* ---- per-kernel-class timing -------------------------------------------------
+ * With profiling enabled every launch of a timed class is bracketed by CUDA events on
+ * its own stream. pk_prof_summary(kind) synchronises the device and returns the summed
+ * duration (ms), the summed algorithmic work (FLOPs) and the launch count since the last
+ * pk_prof_reset. kind: 0 tcgen05 GEMM, 1 SIMT GEMM, 2 attention forward, 3 attention
+ * backward. (The reference prints per-call timings under MATMUL_PROFILE,
+ * third_party/transformer_cpp/src/cuda/matrix_ops.cu:173-181.) */
+int pk_prof_enable(int on);
+int pk_prof_reset(void);
+int pk_prof_summary(int kind, double* ms_h, double* work_h, int64_t* launches_h);
+
 /* ---- GEMM ------------------------------------------------------------------
  * C[M,N] (+)= op(A) . op(B) (+ bias) (+ residual), fp32 accumulation.
  * Replaces device::gemm(A, devA, tA, B, devB, tB) -- include/microtorch/

@@ -420,9 +420,11 @@ StepResult run_steps(Model& model, const Args& a, const std::string& out) {
         auto t3 = std::chrono::steady_clock::now();
         if (do_opt) opt.step();
         auto t4 = std::chrono::steady_clock::now();
-        r.fwd_s += std::chrono::duration<double>(t1 - t0).count();
-        r.bwd_s += std::chrono::duration<double>(t2 - t1).count();
-        r.opt_s += std::chrono::duration<double>(t4 - t3).count();
+        if (s >= static_cast<int>(a.geti("warmup", 0))) {  // warm-up steps run but are not timed
+            r.fwd_s += std::chrono::duration<double>(t1 - t0).count();
+            r.bwd_s += std::chrono::duration<double>(t2 - t1).count();
+            r.opt_s += std::chrono::duration<double>(t4 - t3).count();
+        }
     }
     if (!out.empty()) {
         Matrix lm(1, losses.size());
@@ -698,7 +700,7 @@ int main(int argc, char** argv) {
         auto t1 = std::chrono::steady_clock::now();
         const double secs = std::chrono::duration<double>(t1 - t0).count();
         const double step_s = r.fwd_s + r.bwd_s + r.opt_s;
-        const long steps = a.geti("steps", 1);
+        const long steps = a.geti("steps", 1) - a.geti("warmup", 0);  // timed steps
         const double tokens = static_cast<double>(a.geti("batch", 1)) * a.geti("seq", 16) * steps;
         std::printf("{\"tokens_per_s\": %.4f, \"step_s\": %.5f, \"wall_s\": %.4f, \"loss\": %.9g, \"steps\": %ld}\n",
                     tokens / step_s, step_s / steps, secs, r.loss, steps);

@@ -70,15 +70,19 @@ def build_libpk(verbose: bool = False, force: bool = False, ptxas_info: bool = F
     nvcc = _nvcc()
     cxx = _host_cxx()
     headers = list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
-    objs = []
+    objs, jobs = [], []
     for src in sorted(CSRC.glob("*.cu")):
         obj = OBJ / (src.stem + ".o")
         if force or not _newer(obj, [src, *headers]):
             cmd = [nvcc, "-ccbin", cxx, *NVCC_FLAGS, "-c", src, "-o", obj]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
-            _run(cmd, verbose or ptxas_info)
+            jobs.append(cmd)
         objs.append(obj)
+    if jobs:  # translation units are independent: compile them side by side
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as pool:
+            list(pool.map(lambda c: _run(c, verbose or ptxas_info), jobs))
     lib = PKG / "libpk.so"
     if force or not _newer(lib, objs):
         # cudart is linked statically (nvcc default) and the driver API is reached through

@@ -338,6 +338,8 @@ int pk_attn_fwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.ldo = ldo;
     a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.scale = scale; a.causal = causal;
     g_attn_last_path = 0;
+    // causal attention touches half of the score matrix: 2 GEMMs x 2 flops x S^2/2 x dk
+    ProfScope prof(PROF_ATTN_FWD, (causal ? 2.0 : 4.0) * B * S * S * Hq * dk, as_stream(stream));
     if (dtype == PK_F32) return attn_dispatch<float>(as_stream(stream), a, dk, false);
     return attn_dispatch<bf16>(as_stream(stream), a, dk, false);
 }
@@ -362,6 +364,8 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.ldo = ldo; a.lddo = lddo; a.lddq = lddq; a.lddk = lddk; a.lddv = lddv;
     a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.scale = scale; a.causal = causal;
     g_attn_last_path = 0;
+    // backward = 5 GEMM-shaped products on the visible half: 2.5 x the forward
+    ProfScope prof(PROF_ATTN_BWD, (causal ? 5.0 : 10.0) * B * S * S * Hq * dk, as_stream(stream));
     if (dtype == PK_F32) return attn_dispatch<float>(as_stream(stream), a, dk, true);
     return attn_dispatch<bf16>(as_stream(stream), a, dk, true);
 }

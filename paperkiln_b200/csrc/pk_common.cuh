@@ -44,6 +44,17 @@ inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s
 inline size_t dtype_size(int dt) { return dt == PK_BF16 ? 2 : 4; }
 inline bool valid_dtype(int dt) { return dt == PK_F32 || dt == PK_BF16; }
 
+// Optional per-kernel-class timing with CUDA events on the launching stream (off by
+// default). A ProfScope placed around a launch records the pair of events; the totals
+// are read with pk_prof_summary().
+enum ProfKind { PROF_GEMM_TC = 0, PROF_GEMM_SIMT = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_KINDS = 4 };
+struct ProfScope {
+    ProfScope(int kind, double work, cudaStream_t st);
+    ~ProfScope();
+    int slot;
+    cudaStream_t st;
+};
+
 // Number of SMs of the current device (cached); grids of the bandwidth-bound
 // kernels are sized in multiples of it.
 int sm_count();

@@ -152,9 +152,11 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
     if (ab_dtype == PK_BF16 && !g_force_simt &&
         gemm_tc_supported(c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, residual, ldr)) {
         g_last_path = 2;
+        ProfScope prof(PROF_GEMM_TC, 2.0 * M * N * K, st);
         return gemm_tc_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate,
                               bias, residual, ldr);
     }
+    ProfScope prof(PROF_GEMM_SIMT, 2.0 * M * N * K, st);
     if (ab_dtype == PK_F32) {
         g_last_path = 0;
         return launch_simt<float, float>(st, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate,

@@ -2,6 +2,7 @@
 // per-thread error message. See include/pk.h for the contract of each call.
 #include <cstdarg>
 #include <cstring>
+#include <vector>
 
 #include "pk_common.cuh"
 
@@ -31,9 +32,64 @@ int sm_count() {
     return cached;
 }
 
+// ---- event-based profiling --------------------------------------------------------
+namespace {
+struct ProfRec {
+    cudaEvent_t a, b;
+    int kind;
+    double work;
+};
+bool g_prof_on = false;
+std::vector<ProfRec> g_prof;
+size_t g_prof_used = 0;
+}  // namespace
+
+ProfScope::ProfScope(int kind, double work, cudaStream_t st_) : slot(-1), st(st_) {
+    if (!g_prof_on) return;
+    if (g_prof_used == g_prof.size()) {
+        ProfRec r{};
+        if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+        g_prof.push_back(r);
+    }
+    slot = static_cast<int>(g_prof_used++);
+    g_prof[slot].kind = kind;
+    g_prof[slot].work = work;
+    cudaEventRecord(g_prof[slot].a, st);
+}
+ProfScope::~ProfScope() {
+    if (slot >= 0) cudaEventRecord(g_prof[slot].b, st);
+}
+
 }  // namespace pk
 
 extern "C" {
+
+int pk_prof_enable(int on) {
+    pk::g_prof_on = on != 0;
+    return PK_OK;
+}
+int pk_prof_reset(void) {
+    pk::g_prof_used = 0;
+    return PK_OK;
+}
+int pk_prof_summary(int kind, double* ms_h, double* work_h, int64_t* launches_h) {
+    PK_REQUIRE(kind >= 0 && kind < pk::PROF_KINDS && ms_h && work_h && launches_h, "bad argument");
+    PK_CHECK_CUDA(cudaDeviceSynchronize());
+    double ms = 0.0, work = 0.0;
+    int64_t n = 0;
+    for (size_t i = 0; i < pk::g_prof_used; ++i) {
+        if (pk::g_prof[i].kind != kind) continue;
+        float t = 0.0f;
+        PK_CHECK_CUDA(cudaEventElapsedTime(&t, pk::g_prof[i].a, pk::g_prof[i].b));
+        ms += t;
+        work += pk::g_prof[i].work;
+        ++n;
+    }
+    *ms_h = ms;
+    *work_h = work;
+    *launches_h = n;
+    return PK_OK;
+}
 
 int pk_abi_version(void) { return PK_ABI_VERSION; }
 const char* pk_last_error(void) { return pk::g_err; }
