@@ -198,8 +198,12 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
                 const void* dout, int64_t lddo, void* dq, int64_t lddq, void* dk_, int64_t lddk,
                 void* dv, int64_t lddv, void* scratch,
                 int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale, int causal);
-/* 0 = SIMT fp32-math kernel, 1 = tensor-core kernel (last call on this thread). */
+/* 0 = SIMT fp32-math kernel, 1 = tensor-core kernel (last call on this thread). bf16 with
+ * head_dim 64 or 128 and 16-byte aligned rows takes the tcgen05 kernels. */
 int pk_attn_last_path(void);
+/* Status word of the tensor-core attention kernels (PK_ERR_TIMEOUT when a bounded wait
+ * gave up). Synchronises the device; clear != 0 resets it. */
+int pk_attn_tc_status(int* status_h, int clear);
 int pk_attn_force_simt(int on);
 
 /* ---- embedding / loss --------------------------------------------------------

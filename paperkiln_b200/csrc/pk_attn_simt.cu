@@ -249,6 +249,13 @@ attn_bwd_dkv_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ 
 static thread_local int g_attn_last_path = -1;
 static int g_attn_force_simt = 0;
 
+// tensor-core kernels (pk_attn_tc.cu)
+int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                      int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S);
+int attn_tc_fwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
+                int causal);
+
 struct AttnArgs {
     const void *q, *k, *v, *out, *dout;
     void *o_w, *dq, *dk, *dv;
@@ -337,9 +344,13 @@ int pk_attn_fwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     a.q = q; a.k = k; a.v = v; a.o_w = out; a.lse_w = lse;
     a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.ldo = ldo;
     a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.scale = scale; a.causal = causal;
-    g_attn_last_path = 0;
     // causal attention touches half of the score matrix: 2 GEMMs x 2 flops x S^2/2 x dk
     ProfScope prof(PROF_ATTN_FWD, (causal ? 2.0 : 4.0) * B * S * S * Hq * dk, as_stream(stream));
+    if (!g_attn_force_simt && attn_tc_supported(dtype, dk, q, ldq, k, ldk, v, ldv, out, ldo, B, S)) {
+        g_attn_last_path = 1;
+        return attn_tc_fwd(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
+    }
+    g_attn_last_path = 0;
     if (dtype == PK_F32) return attn_dispatch<float>(as_stream(stream), a, dk, false);
     return attn_dispatch<bf16>(as_stream(stream), a, dk, false);
 }

@@ -1,0 +1,359 @@
+// Flash attention on the tcgen05 tensor cores (bf16 operands, fp32 accumulation in tensor
+// memory), head_dim 64 or 128, causal or full, grouped-query head mapping, B stacked
+// sequences. The score matrix lives only in tensor memory and registers.
+//
+// Forward, one CTA of 128 threads per (128-query tile, head, sequence); thread t owns query
+// row t (= tensor-memory lane t). Per 128-key tile:
+//     S = Q K^T                tcgen05.mma, operands TMA-loaded into swizzled smem
+//     p = exp2(S*c - m)        each thread reads its row of S from tensor memory (two sweeps:
+//                              max, then exponentials), writes P as bf16 into smem in the
+//                              operand layout of the next MMA
+//     O_tile = P V             tcgen05.mma (V read as an MN-major operand, no transpose)
+//     o = o*corr + O_tile      running output kept in registers, rescaled per tile
+// Two CTAs fit one SM (shared memory, tensor-memory columns), so one CTA's softmax overlaps
+// the other's MMAs. Every mbarrier wait is bounded (status word, no trap).
+//
+// Semantics: ops::fused_attention of the reference (src/ops.cpp:863-934) applied per head.
+#include "pk_tc.cuh"
+
+#include <mutex>
+
+namespace pk {
+
+__device__ int g_attn_tc_status = 0;
+
+namespace tc {
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, []() {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+int make_tensor_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner,
+                    int box_outer) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        set_error("cuTensorMapEncodeTiled is not available from the driver");
+        return PK_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+        return PK_ERR_CUDA;
+    }
+    return PK_OK;
+}
+
+}  // namespace tc
+
+using namespace tc;
+
+constexpr int AT_BM = 128;  // queries per CTA
+constexpr int AT_BN = 128;  // keys per tile
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct FwdParams {
+    bf16* out;
+    int64_t ldo;
+    float* lse;
+    int64_t S;
+    int Hq, Hkv;
+    float scale_log2;  // scale * log2(e)
+    int causal;
+};
+
+template <int DK>
+struct FwdSmem {
+    static constexpr int NCH = DK / 64;                       // 64-wide chunks per Q/K/V tile
+    static constexpr int TILE = NCH * (int)CHUNK_BYTES;       // bytes of one Q/K/V tile
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = TILE;                        // 2 stages
+    static constexpr int OFF_V = 3 * TILE;                    // 1 stage
+    static constexpr int OFF_P = 4 * TILE;                    // 2 chunks (128 keys)
+    static constexpr int OFF_BAR = 4 * TILE + 2 * (int)CHUNK_BYTES;
+    static constexpr int BYTES = OFF_BAR + 128 + 1024;        // + alignment slack
+};
+
+template <int DK>
+__global__ void __launch_bounds__(128, DK == 64 ? 2 : 1)
+attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
+    using L = FwdSmem<DK>;
+    constexpr int NCH = L::NCH;
+    constexpr uint32_t TMEM_COLS = 256;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+    uint64_t* bar_q = bars;
+    uint64_t* bar_k = bars + 1;  // [2]
+    uint64_t* bar_v = bars + 3;
+    uint64_t* bar_s = bars + 4;
+    uint64_t* bar_o = bars + 5;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int64_t seq0 = static_cast<int64_t>(b) * p.S;
+    const int64_t q0 = static_cast<int64_t>(qt) * AT_BM;
+    const int64_t qi = q0 + tid;
+    int nkv = static_cast<int>((p.S + AT_BN - 1) / AT_BN);
+    if (p.causal && qt + 1 < nkv) nkv = qt + 1;
+
+    if (tid == 0) {
+        mbar_init(smem_u32(bar_q), 1);
+        mbar_init(smem_u32(&bar_k[0]), 1);
+        mbar_init(smem_u32(&bar_k[1]), 1);
+        mbar_init(smem_u32(bar_v), 1);
+        mbar_init(smem_u32(bar_s), 1);
+        mbar_init(smem_u32(bar_o), 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t t_s = tmem;          // S: 128 columns
+    const uint32_t t_o = tmem + 128;    // O_tile: DK columns
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t sQ = smem_u32(smem + L::OFF_Q), sK0 = smem_u32(smem + L::OFF_K), sV = smem_u32(smem + L::OFF_V);
+    const uint32_t sP = smem_u32(smem + L::OFF_P);
+    uint8_t* pP = smem + L::OFF_P;
+
+    if (tid == 0) {
+        mbar_expect_tx(smem_u32(bar_q), L::TILE);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+            tma_load_2d(sQ + c * CHUNK_BYTES, &map_q, h * DK + c * 64, static_cast<int32_t>(seq0 + q0), smem_u32(bar_q));
+        mbar_expect_tx(smem_u32(&bar_k[0]), L::TILE);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+            tma_load_2d(sK0 + c * CHUNK_BYTES, &map_k, hk * DK + c * 64, static_cast<int32_t>(seq0), smem_u32(&bar_k[0]));
+    }
+    const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
+    const uint32_t idesc_o = idesc_bf16(DK, 0, 1);
+
+    float o[DK];
+#pragma unroll
+    for (int i = 0; i < DK; ++i) o[i] = 0.0f;
+    float m = -INFINITY, l = 0.0f;
+    bool ok = true;
+
+    for (int j = 0; j < nkv && ok; ++j) {
+        const int st = j & 1;
+        const int64_t kv0 = static_cast<int64_t>(j) * AT_BN;
+        if (tid == 0) {
+            // V_j: the single V buffer is free, P.V of the previous tile was waited for below
+            mbar_expect_tx(smem_u32(bar_v), L::TILE);
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+                tma_load_2d(sV + c * CHUNK_BYTES, &map_v, hk * DK + c * 64, static_cast<int32_t>(seq0 + kv0), smem_u32(bar_v));
+            if (j == 0) ok = mbar_wait(smem_u32(bar_q), 0, abort_flag, &g_attn_tc_status);
+            if (ok) ok = mbar_wait(smem_u32(&bar_k[st]), (j >> 1) & 1, abort_flag, &g_attn_tc_status);
+            if (ok) {
+                fence_after();
+                const uint32_t sK = sK0 + st * L::TILE;
+#pragma unroll
+                for (int k = 0; k < DK / 16; ++k)
+                    mma_bf16(t_s, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
+                commit(smem_u32(bar_s));
+                if (j + 1 < nkv) {  // prefetch K_{j+1}; its buffer was last read by S of tile j-1
+                    const uint32_t sKn = sK0 + (st ^ 1) * L::TILE;
+                    mbar_expect_tx(smem_u32(&bar_k[st ^ 1]), L::TILE);
+#pragma unroll
+                    for (int c = 0; c < NCH; ++c)
+                        tma_load_2d(sKn + c * CHUNK_BYTES, &map_k, hk * DK + c * 64,
+                                    static_cast<int32_t>(seq0 + kv0 + AT_BN), smem_u32(&bar_k[st ^ 1]));
+                }
+            }
+        }
+        if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        fence_after();
+        const bool need_mask = (p.causal && kv0 + AT_BN - 1 > q0) || (kv0 + AT_BN > p.S);
+        // ---- sweep 1: row maximum of the raw scores
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(t_s + lane_off + ch * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                float s = __uint_as_float(r[e]);
+                if (need_mask) {
+                    const int64_t key = kv0 + ch * 32 + e;
+                    if (key >= p.S || (p.causal && key > qi)) s = -INFINITY;
+                }
+                mx = fmaxf(mx, s);
+            }
+        }
+        const float m_new = fmaxf(m, mx * p.scale_log2);
+        const float corr = m == -INFINITY ? 0.0f : exp2f(m - m_new);
+        l *= corr;
+        // ---- sweep 2: exponentials, row sum, P -> smem (bf16, operand layout)
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(t_s + lane_off + ch * 32, r);
+            tmem_wait_ld();
+            float pv[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                float s = __uint_as_float(r[e]);
+                bool vis = true;
+                if (need_mask) {
+                    const int64_t key = kv0 + ch * 32 + e;
+                    vis = key < p.S && (!p.causal || key <= qi);
+                }
+                const float pe = vis ? exp2f(s * p.scale_log2 - m_new) : 0.0f;
+                pv[e] = pe;
+                l += pe;
+            }
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int unit = ch * 4 + g;  // 16 units of 8 keys
+                uint4 v;
+                v.x = pack_bf16(pv[g * 8 + 0], pv[g * 8 + 1]);
+                v.y = pack_bf16(pv[g * 8 + 2], pv[g * 8 + 3]);
+                v.z = pack_bf16(pv[g * 8 + 4], pv[g * 8 + 5]);
+                v.w = pack_bf16(pv[g * 8 + 6], pv[g * 8 + 7]);
+                st_swizzled(pP + (unit >> 3) * CHUNK_BYTES, tid, unit & 7, v);
+            }
+        }
+        fence_async_smem();
+        fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            ok = mbar_wait(smem_u32(bar_v), j & 1, abort_flag, &g_attn_tc_status);
+            if (ok) {
+                fence_after();
+#pragma unroll
+                for (int k = 0; k < AT_BN / 16; ++k)
+                    mma_bf16(t_o, desc_kmajor(sP, k), desc_mnmajor(sV, k), idesc_o, k > 0 ? 1u : 0u);
+                commit(smem_u32(bar_o));
+            }
+        }
+        if (!mbar_wait(smem_u32(bar_o), j & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        fence_after();
+#pragma unroll
+        for (int ch = 0; ch < DK / 32; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(t_o + lane_off + ch * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[ch * 32 + e] = o[ch * 32 + e] * corr + __uint_as_float(r[e]);
+        }
+        m = m_new;
+    }
+
+    if (ok && qi < p.S) {
+        const float inv = 1.0f / l;
+        bf16* dst = p.out + (seq0 + qi) * p.ldo + h * DK;
+#pragma unroll
+        for (int g = 0; g < DK / 8; ++g) {
+            uint4 v;
+            v.x = pack_bf16(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
+            v.y = pack_bf16(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
+            v.z = pack_bf16(o[g * 8 + 4] * inv, o[g * 8 + 5] * inv);
+            v.w = pack_bf16(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
+            *reinterpret_cast<uint4*>(dst + g * 8) = v;
+        }
+        p.lse[(seq0 + qi) * p.Hq + h] = (m + log2f(l)) * LN2;
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+template <int DK>
+static int launch_fwd(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                      const FwdParams& p, int64_t B) {
+    using L = FwdSmem<DK>;
+    auto kern = attn_fwd_tc_kernel<DK>;
+    static bool attr = false;
+    if (!attr) {
+        PK_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
+        attr = true;
+    }
+    dim3 grid(static_cast<unsigned>((p.S + AT_BM - 1) / AT_BM), p.Hq, static_cast<unsigned>(B));
+    kern<<<grid, 128, L::BYTES, st>>>(mq, mk, mv, p);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+// ---- entry points used by the dispatcher in pk_attn_simt.cu ------------------------------
+int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                      int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S) {
+    if (dtype != PK_BF16 || (dk != 64 && dk != 128)) return 0;
+    if (ldq % 8 || ldk % 8 || ldv % 8 || ldo % 8) return 0;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return 0;
+    if (B * S >= (int64_t(1) << 31)) return 0;
+    return 1;
+}
+
+int attn_tc_fwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
+                int causal) {
+    CUtensorMap mq, mk, mv;
+    const int64_t R = B * S;
+    int rc = make_tensor_map(&mq, q, static_cast<int64_t>(Hq) * dk, R, ldq, 64, AT_BM);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mk, k, static_cast<int64_t>(Hkv) * dk, R, ldk, 64, AT_BN);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mv, v, static_cast<int64_t>(Hkv) * dk, R, ldv, 64, AT_BN);
+    if (rc != PK_OK) return rc;
+    FwdParams p;
+    p.out = static_cast<bf16*>(out);
+    p.ldo = ldo;
+    p.lse = lse;
+    p.S = S;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.scale_log2 = scale * LOG2E;
+    p.causal = causal;
+    return dk == 64 ? launch_fwd<64>(st, mq, mk, mv, p, B) : launch_fwd<128>(st, mq, mk, mv, p, B);
+}
+
+}  // namespace pk
+
+extern "C" {
+
+int pk_attn_tc_status(int* status_h, int clear) {
+    PK_REQUIRE(status_h != nullptr, "null output");
+    PK_CHECK_CUDA(cudaDeviceSynchronize());
+    PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, pk::g_attn_tc_status, sizeof(int)));
+    if (clear) {
+        const int zero = 0;
+        PK_CHECK_CUDA(cudaMemcpyToSymbol(pk::g_attn_tc_status, &zero, sizeof(int)));
+    }
+    return PK_OK;
+}
+
+}  // extern "C"

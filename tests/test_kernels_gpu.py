@@ -323,7 +323,8 @@ def attn_ref(q, k, v, B, S, Hq, Hkv, dk, scale, causal):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("cfg", [(3, 20, 1, 1, 8, True), (2, 100, 4, 2, 32, True), (2, 67, 2, 2, 64, False),
-                                 (1, 130, 2, 1, 128, True)])
+                                 (1, 130, 2, 1, 128, True), (2, 300, 4, 2, 64, True), (1, 513, 2, 2, 128, True),
+                                 (2, 256, 2, 1, 64, False), (1, 1024, 8, 2, 64, True)])
 def test_attention(pk, dtype, cfg):
     B, S, Hq, Hkv, dk, causal = cfg
     R = B * S
@@ -336,8 +337,23 @@ def test_attention(pk, dtype, cfg):
     lse = torch.empty(R, Hq, device="cuda")
     pkt.check(pk.pk_attn_fwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
                              Hq * dk, ptr(lse), B, S, Hq, Hkv, dk, scale, int(causal)))
+    if dtype == torch.bfloat16 and dk in (64, 128):
+        assert pk.pk_attn_last_path() == 1, "tensor-core attention was not selected"
+        st = ctypes.c_int(0)
+        pkt.check(pk.pk_attn_tc_status(ctypes.byref(st), 1))
+        assert st.value == 0, "tensor-core attention reported a wait that gave up"
+        out2 = torch.empty_like(q)
+        lse2 = torch.empty(R, Hq, device="cuda")
+        pkt.check(pk.pk_attn_fwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out2),
+                                 Hq * dk, ptr(lse2), B, S, Hq, Hkv, dk, scale, int(causal)))
+        assert torch.equal(out, out2) and torch.equal(lse, lse2), "attention forward is not reproducible"
     qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
     ref = attn_ref(qf, kf, vf, B, S, Hq, Hkv, dk, scale, causal)
+    sref = (qf.view(B, S, Hq, dk).transpose(1, 2) @
+            kf.view(B, S, Hkv, dk).transpose(1, 2).repeat_interleave(Hq // Hkv, dim=1).transpose(-1, -2)) * scale
+    if causal:
+        sref = sref.masked_fill(~torch.ones(S, S, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    close(lse, torch.logsumexp(sref, dim=-1).transpose(1, 2).reshape(R, Hq).detach(), 1e-4 if dtype == torch.float32 else 2e-2)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     close(out, ref, tol)
     ref.backward(do.float())
