@@ -255,6 +255,10 @@ int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void*
 int attn_tc_fwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                 void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
                 int causal);
+int attn_tc_bwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                const float* lse, const float* delta, const void* dout, int64_t lddo, void* dq, int64_t lddq,
+                void* dk_, int64_t lddk, void* dv, int64_t lddv, int64_t B, int64_t S, int Hq, int Hkv, int dk,
+                float scale, int causal);
 
 struct AttnArgs {
     const void *q, *k, *v, *out, *dout;
@@ -374,9 +378,19 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     a.dq = dq; a.dk = dk_; a.dv = dv; a.delta = static_cast<float*>(scratch);
     a.ldq = ldq; a.ldk = ldk; a.ldv = ldv; a.ldo = ldo; a.lddo = lddo; a.lddq = lddq; a.lddk = lddk; a.lddv = lddv;
     a.B = B; a.S = S; a.Hq = Hq; a.Hkv = Hkv; a.scale = scale; a.causal = causal;
-    g_attn_last_path = 0;
     // backward = 5 GEMM-shaped products on the visible half: 2.5 x the forward
     ProfScope prof(PROF_ATTN_BWD, (causal ? 5.0 : 10.0) * B * S * S * Hq * dk, as_stream(stream));
+    if (!g_attn_force_simt && attn_tc_supported(dtype, dk, q, ldq, k, ldk, v, ldv, out, ldo, B, S) &&
+        attn_tc_supported(dtype, dk, dout, lddo, dk_, lddk, dv, lddv, dq, lddq, B, S)) {
+        g_attn_last_path = 1;
+        const int64_t R = B * S;
+        attn_delta_kernel<bf16><<<static_cast<unsigned>((R * Hq + 7) / 8), 256, 0, as_stream(stream)>>>(
+            static_cast<const bf16*>(out), ldo, static_cast<const bf16*>(dout), lddo, a.delta, R, Hq, dk);
+        PK_LAUNCH_CHECK();
+        return attn_tc_bwd(as_stream(stream), q, ldq, k, ldk, v, ldv, lse, a.delta, dout, lddo, dq, lddq, dk_, lddk,
+                           dv, lddv, B, S, Hq, Hkv, dk, scale, causal);
+    }
+    g_attn_last_path = 0;
     if (dtype == PK_F32) return attn_dispatch<float>(as_stream(stream), a, dk, true);
     return attn_dispatch<bf16>(as_stream(stream), a, dk, true);
 }

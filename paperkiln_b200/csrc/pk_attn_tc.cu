@@ -308,6 +308,468 @@ static int launch_fwd(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap&
     return PK_OK;
 }
 
+// ================================================================================ backward
+// Two kernels, no atomics: gradients are owned by one CTA each and summed in a fixed order.
+//   dQ kernel     one CTA per (128-query tile, head, sequence), loops over key tiles:
+//                 S = Q K^T, dP = dO V^T (tensor memory); dS = P (dP - delta) scale as bf16
+//                 in smem; dQ += dS K with K read as an MN-major operand
+//   dK/dV kernel  one CTA per (128-key tile, kv head, sequence), loops over the query heads
+//                 of the group and their query tiles: S and dP as above, P and dS written as
+//                 bf16 [query, key]; dV += P^T dO and dK += dS^T Q take P / dS as MN-major A
+//                 operands (the transpose is a descriptor bit), dO / Q as MN-major B operands
+// P is recomputed from the saved log-sum-exp: p = exp2(s*c - lse*log2 e).
+struct BwdParams {
+    bf16* dq;
+    int64_t lddq;
+    bf16* dk;
+    int64_t lddk;
+    bf16* dv;
+    int64_t lddv;
+    const float* lse;
+    const float* delta;
+    int64_t S;
+    int Hq, Hkv;
+    float scale, scale_log2;
+    int causal;
+};
+
+template <int DK>
+__device__ __forceinline__ void load_tile_tma(uint32_t dst, const CUtensorMap* map, int col0, int64_t row, uint32_t bar) {
+#pragma unroll
+    for (int c = 0; c < DK / 64; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, col0 + c * 64, static_cast<int32_t>(row), bar);
+}
+
+// Reads one 32-column chunk of S and dP for this thread's query row and produces p and ds.
+__device__ __forceinline__ void softmax_grad_chunk(uint32_t t_s, uint32_t t_dp, int ch, int64_t key0, int64_t qi, int64_t S,
+                                                   bool causal, bool row_ok, float scale, float scale_log2, float lse2,
+                                                   float delta, float (&pv)[32], float (&dsv)[32]) {
+    uint32_t rs[32], rd[32];
+    tmem_ld32(t_s + ch * 32, rs);
+    tmem_ld32(t_dp + ch * 32, rd);
+    tmem_wait_ld();
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+        const int64_t key = key0 + ch * 32 + e;
+        const bool vis = row_ok && key < S && (!causal || key <= qi);
+        const float pe = vis ? exp2f(__uint_as_float(rs[e]) * scale_log2 - lse2) : 0.0f;
+        pv[e] = pe;
+        dsv[e] = pe * (__uint_as_float(rd[e]) - delta) * scale;
+    }
+}
+__device__ __forceinline__ void store_chunk_bf16(uint8_t* tile, int row, int ch, const float (&v)[32]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int unit = ch * 4 + g;
+        uint4 w;
+        w.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
+        w.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
+        w.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
+        w.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
+        st_swizzled(tile + (unit >> 3) * CHUNK_BYTES, row, unit & 7, w);
+    }
+}
+
+template <int DK>
+struct DqSmem {
+    static constexpr int TILE = (DK / 64) * (int)CHUNK_BYTES;
+    static constexpr int NST = DK == 64 ? 2 : 1;  // K/V stages
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_DO = TILE;
+    static constexpr int OFF_K = 2 * TILE;               // NST stages
+    static constexpr int OFF_V = 2 * TILE + NST * TILE;  // NST stages
+    static constexpr int OFF_DS = 2 * TILE + 2 * NST * TILE;
+    static constexpr int OFF_BAR = OFF_DS + 2 * (int)CHUNK_BYTES;
+    static constexpr int BYTES = OFF_BAR + 128 + 1024;
+};
+
+template <int DK>
+__global__ void __launch_bounds__(128, 1)
+attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                      const BwdParams p) {
+    using L = DqSmem<DK>;
+    constexpr int NST = L::NST;
+    constexpr uint32_t TMEM_COLS = 512;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+    uint64_t* bar_q = bars;
+    uint64_t* bar_kv = bars + 1;  // [2]
+    uint64_t* bar_s = bars + 3;
+    uint64_t* bar_d = bars + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int64_t seq0 = static_cast<int64_t>(b) * p.S;
+    const int64_t q0 = static_cast<int64_t>(qt) * AT_BM;
+    const int64_t qi = q0 + tid;
+    const bool row_ok = qi < p.S;
+    int nkv = static_cast<int>((p.S + AT_BN - 1) / AT_BN);
+    if (p.causal && qt + 1 < nkv) nkv = qt + 1;
+
+    if (tid == 0) {
+        mbar_init(smem_u32(bar_q), 1);
+        mbar_init(smem_u32(&bar_kv[0]), 1);
+        mbar_init(smem_u32(&bar_kv[1]), 1);
+        mbar_init(smem_u32(bar_s), 1);
+        mbar_init(smem_u32(bar_d), 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t t_s = tmem + lane_off, t_dp = tmem + 128 + lane_off, t_dq = tmem + 256;
+    const uint32_t sQ = smem_u32(smem + L::OFF_Q), sDO = smem_u32(smem + L::OFF_DO);
+    const uint32_t sK0 = smem_u32(smem + L::OFF_K), sV0 = smem_u32(smem + L::OFF_V), sDS = smem_u32(smem + L::OFF_DS);
+    uint8_t* pDS = smem + L::OFF_DS;
+
+    if (tid == 0) {
+        mbar_expect_tx(smem_u32(bar_q), 2 * L::TILE);
+        load_tile_tma<DK>(sQ, &map_q, h * DK, seq0 + q0, smem_u32(bar_q));
+        load_tile_tma<DK>(sDO, &map_do, h * DK, seq0 + q0, smem_u32(bar_q));
+        mbar_expect_tx(smem_u32(&bar_kv[0]), 2 * L::TILE);
+        load_tile_tma<DK>(sK0, &map_k, hk * DK, seq0, smem_u32(&bar_kv[0]));
+        load_tile_tma<DK>(sV0, &map_v, hk * DK, seq0, smem_u32(&bar_kv[0]));
+    }
+    const float lse2 = row_ok ? p.lse[(seq0 + qi) * p.Hq + h] * LOG2E : 0.0f;
+    const float delta = row_ok ? p.delta[(seq0 + qi) * p.Hq + h] : 0.0f;
+    const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
+    const uint32_t idesc_q = idesc_bf16(DK, 0, 1);
+    bool ok = true;
+
+    for (int j = 0; j < nkv && ok; ++j) {
+        const int st = NST == 2 ? (j & 1) : 0;
+        const uint32_t kv_phase = NST == 2 ? ((j >> 1) & 1) : (j & 1);
+        const int64_t kv0 = static_cast<int64_t>(j) * AT_BN;
+        if (tid == 0) {
+            if (NST == 1 && j > 0) {  // the single K/V stage is free once dQ of tile j-1 is done
+                ok = mbar_wait(smem_u32(bar_d), (j - 1) & 1, abort_flag, &g_attn_tc_status);
+                if (ok) {
+                    mbar_expect_tx(smem_u32(&bar_kv[0]), 2 * L::TILE);
+                    load_tile_tma<DK>(sK0, &map_k, hk * DK, seq0 + kv0, smem_u32(&bar_kv[0]));
+                    load_tile_tma<DK>(sV0, &map_v, hk * DK, seq0 + kv0, smem_u32(&bar_kv[0]));
+                }
+            }
+            if (ok && j == 0) ok = mbar_wait(smem_u32(bar_q), 0, abort_flag, &g_attn_tc_status);
+            if (ok) ok = mbar_wait(smem_u32(&bar_kv[st]), kv_phase, abort_flag, &g_attn_tc_status);
+            if (ok) {
+                fence_after();
+                const uint32_t sK = sK0 + st * L::TILE, sV = sV0 + st * L::TILE;
+#pragma unroll
+                for (int k = 0; k < DK / 16; ++k)
+                    mma_bf16(tmem, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < DK / 16; ++k)
+                    mma_bf16(tmem + 128, desc_kmajor(sDO, k), desc_kmajor(sV, k), idesc_s, k > 0 ? 1u : 0u);
+                commit(smem_u32(bar_s));
+            }
+        }
+        if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        // S_j complete implies dQ of tile j-1 (issued earlier on the same pipe) is complete:
+        // the dS buffer and, with two stages, the other K/V stage are free again.
+        fence_after();
+        if (tid == 0 && NST == 2 && j + 1 < nkv) {
+            const int sn = st ^ 1;
+            mbar_expect_tx(smem_u32(&bar_kv[sn]), 2 * L::TILE);
+            load_tile_tma<DK>(sK0 + sn * L::TILE, &map_k, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_kv[sn]));
+            load_tile_tma<DK>(sV0 + sn * L::TILE, &map_v, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_kv[sn]));
+        }
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            float pv[32], dsv[32];
+            softmax_grad_chunk(t_s, t_dp, ch, kv0, qi, p.S, p.causal != 0, row_ok, p.scale, p.scale_log2, lse2, delta, pv, dsv);
+            store_chunk_bf16(pDS, tid, ch, dsv);
+        }
+        fence_async_smem();
+        fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            fence_after();
+            const uint32_t sK = sK0 + st * L::TILE;
+#pragma unroll
+            for (int k = 0; k < AT_BN / 16; ++k)
+                mma_bf16(t_dq, desc_kmajor(sDS, k), desc_mnmajor(sK, k), idesc_q, (j > 0 || k > 0) ? 1u : 0u);
+            commit(smem_u32(bar_d));
+        }
+    }
+    if (ok) ok = mbar_wait(smem_u32(bar_d), (nkv - 1) & 1, abort_flag, &g_attn_tc_status);
+    if (ok) {
+        fence_after();
+        bf16* dst = p.dq + (seq0 + qi) * p.lddq + h * DK;
+#pragma unroll 1
+        for (int ch = 0; ch < DK / 32; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(t_dq + lane_off + ch * 32, r);
+            tmem_wait_ld();
+            if (row_ok) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4 w;
+                    w.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+                    w.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+                    w.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+                    w.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+                    *reinterpret_cast<uint4*>(dst + ch * 32 + g * 8) = w;
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+template <int DK>
+struct DkvSmem {
+    static constexpr int TILE = (DK / 64) * (int)CHUNK_BYTES;
+    static constexpr int NST = DK == 64 ? 2 : 1;  // Q/dO stages
+    static constexpr int OFF_K = 0;
+    static constexpr int OFF_V = TILE;
+    static constexpr int OFF_Q = 2 * TILE;               // NST stages
+    static constexpr int OFF_DO = 2 * TILE + NST * TILE;  // NST stages
+    static constexpr int OFF_P = 2 * TILE + 2 * NST * TILE;
+    static constexpr int OFF_DS = OFF_P + 2 * (int)CHUNK_BYTES;
+    static constexpr int OFF_BAR = OFF_DS + 2 * (int)CHUNK_BYTES;
+    static constexpr int BYTES = OFF_BAR + 128 + 1024;
+};
+
+template <int DK>
+__global__ void __launch_bounds__(128, 1)
+attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                       const BwdParams p) {
+    using L = DkvSmem<DK>;
+    constexpr int NST = L::NST;
+    constexpr uint32_t TMEM_COLS = 512;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+    uint64_t* bar_kv = bars;
+    uint64_t* bar_q = bars + 1;  // [2]
+    uint64_t* bar_s = bars + 3;
+    uint64_t* bar_d = bars + 4;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int kt = blockIdx.x;
+    const int hk = blockIdx.y, b = blockIdx.z;
+    const int group = p.Hq / p.Hkv;
+    const int64_t seq0 = static_cast<int64_t>(b) * p.S;
+    const int64_t k0 = static_cast<int64_t>(kt) * AT_BN;
+    const int nq_all = static_cast<int>((p.S + AT_BM - 1) / AT_BM);
+    const int i_begin = p.causal ? kt : 0;
+    const int per_head = nq_all - i_begin;
+    const int nit = per_head * group;
+
+    if (tid == 0) {
+        mbar_init(smem_u32(bar_kv), 1);
+        mbar_init(smem_u32(&bar_q[0]), 1);
+        mbar_init(smem_u32(&bar_q[1]), 1);
+        mbar_init(smem_u32(bar_s), 1);
+        mbar_init(smem_u32(bar_d), 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t t_s = tmem + lane_off, t_dp = tmem + 128 + lane_off;
+    const uint32_t t_dv = tmem + 256, t_dk = tmem + 256 + DK;
+    const uint32_t sK = smem_u32(smem + L::OFF_K), sV = smem_u32(smem + L::OFF_V);
+    const uint32_t sQ0 = smem_u32(smem + L::OFF_Q), sDO0 = smem_u32(smem + L::OFF_DO);
+    const uint32_t sP = smem_u32(smem + L::OFF_P), sDS = smem_u32(smem + L::OFF_DS);
+    uint8_t* pP = smem + L::OFF_P;
+    uint8_t* pDS = smem + L::OFF_DS;
+
+    if (tid == 0) {
+        mbar_expect_tx(smem_u32(bar_kv), 2 * L::TILE);
+        load_tile_tma<DK>(sK, &map_k, hk * DK, seq0 + k0, smem_u32(bar_kv));
+        load_tile_tma<DK>(sV, &map_v, hk * DK, seq0 + k0, smem_u32(bar_kv));
+        if (nit > 0) {
+            mbar_expect_tx(smem_u32(&bar_q[0]), 2 * L::TILE);
+            load_tile_tma<DK>(sQ0, &map_q, (hk * group) * DK, seq0 + static_cast<int64_t>(i_begin) * AT_BM, smem_u32(&bar_q[0]));
+            load_tile_tma<DK>(sDO0, &map_do, (hk * group) * DK, seq0 + static_cast<int64_t>(i_begin) * AT_BM, smem_u32(&bar_q[0]));
+        }
+    }
+    const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
+    const uint32_t idesc_g = idesc_bf16(DK, 1, 1);
+    bool ok = true;
+
+    for (int it = 0; it < nit && ok; ++it) {
+        const int g = it / per_head, i = i_begin + it % per_head;
+        const int h = hk * group + g;
+        const int st = NST == 2 ? (it & 1) : 0;
+        const uint32_t q_phase = NST == 2 ? ((it >> 1) & 1) : (it & 1);
+        const int64_t q0 = static_cast<int64_t>(i) * AT_BM;
+        const int64_t qi = q0 + tid;
+        const bool row_ok = qi < p.S;
+        if (tid == 0) {
+            if (NST == 1 && it > 0) {  // single Q/dO stage: wait for dV/dK of the previous iteration
+                ok = mbar_wait(smem_u32(bar_d), (it - 1) & 1, abort_flag, &g_attn_tc_status);
+                if (ok) {
+                    mbar_expect_tx(smem_u32(&bar_q[0]), 2 * L::TILE);
+                    load_tile_tma<DK>(sQ0, &map_q, h * DK, seq0 + q0, smem_u32(&bar_q[0]));
+                    load_tile_tma<DK>(sDO0, &map_do, h * DK, seq0 + q0, smem_u32(&bar_q[0]));
+                }
+            }
+            if (ok && it == 0) ok = mbar_wait(smem_u32(bar_kv), 0, abort_flag, &g_attn_tc_status);
+            if (ok) ok = mbar_wait(smem_u32(&bar_q[st]), q_phase, abort_flag, &g_attn_tc_status);
+            if (ok) {
+                fence_after();
+                const uint32_t sQ = sQ0 + st * L::TILE, sDO = sDO0 + st * L::TILE;
+#pragma unroll
+                for (int k = 0; k < DK / 16; ++k)
+                    mma_bf16(tmem, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < DK / 16; ++k)
+                    mma_bf16(tmem + 128, desc_kmajor(sDO, k), desc_kmajor(sV, k), idesc_s, k > 0 ? 1u : 0u);
+                commit(smem_u32(bar_s));
+            }
+        }
+        const float lse2 = row_ok ? p.lse[(seq0 + qi) * p.Hq + h] * LOG2E : 0.0f;
+        const float delta = row_ok ? p.delta[(seq0 + qi) * p.Hq + h] : 0.0f;
+        if (!mbar_wait(smem_u32(bar_s), it & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        // S of this iteration complete => dV/dK of the previous one (issued earlier) complete:
+        // P, dS and the other Q/dO stage may be overwritten.
+        fence_after();
+        if (tid == 0 && NST == 2 && it + 1 < nit) {
+            const int itn = it + 1, sn = st ^ 1;
+            const int hn = hk * group + itn / per_head, in_ = i_begin + itn % per_head;
+            mbar_expect_tx(smem_u32(&bar_q[sn]), 2 * L::TILE);
+            load_tile_tma<DK>(sQ0 + sn * L::TILE, &map_q, hn * DK, seq0 + static_cast<int64_t>(in_) * AT_BM, smem_u32(&bar_q[sn]));
+            load_tile_tma<DK>(sDO0 + sn * L::TILE, &map_do, hn * DK, seq0 + static_cast<int64_t>(in_) * AT_BM, smem_u32(&bar_q[sn]));
+        }
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+            float pv[32], dsv[32];
+            softmax_grad_chunk(t_s, t_dp, ch, k0, qi, p.S, p.causal != 0, row_ok, p.scale, p.scale_log2, lse2, delta, pv, dsv);
+            store_chunk_bf16(pP, tid, ch, pv);
+            store_chunk_bf16(pDS, tid, ch, dsv);
+        }
+        fence_async_smem();
+        fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            fence_after();
+            const uint32_t sQ = sQ0 + st * L::TILE, sDO = sDO0 + st * L::TILE;
+#pragma unroll
+            for (int k = 0; k < AT_BM / 16; ++k)   // dV += P^T dO   (contraction over the 128 queries)
+                mma_bf16(t_dv, desc_mnmajor(sP, k), desc_mnmajor(sDO, k), idesc_g, (it > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int k = 0; k < AT_BM / 16; ++k)   // dK += dS^T Q
+                mma_bf16(t_dk, desc_mnmajor(sDS, k), desc_mnmajor(sQ, k), idesc_g, (it > 0 || k > 0) ? 1u : 0u);
+            commit(smem_u32(bar_d));
+        }
+    }
+    if (ok && nit > 0) ok = mbar_wait(smem_u32(bar_d), (nit - 1) & 1, abort_flag, &g_attn_tc_status);
+    if (ok) {
+        fence_after();
+        const int64_t kj = k0 + tid;  // this thread's key row
+        const bool key_ok = kj < p.S;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+            bf16* dst = (which == 0 ? p.dv + (seq0 + kj) * p.lddv : p.dk + (seq0 + kj) * p.lddk) + hk * DK;
+            const uint32_t t_src = (which == 0 ? t_dv : t_dk) + lane_off;
+#pragma unroll 1
+            for (int ch = 0; ch < DK / 32; ++ch) {
+                uint32_t r[32];
+                if (nit > 0) {
+                    tmem_ld32(t_src + ch * 32, r);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) r[e] = 0u;
+                }
+                if (key_ok) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+                        w.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+                        w.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+                        w.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+                        *reinterpret_cast<uint4*>(dst + ch * 32 + g * 8) = w;
+                    }
+                }
+            }
+        }
+    }
+    fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after();
+        tmem_dealloc(tmem, TMEM_COLS);
+    }
+}
+
+template <int DK>
+static int launch_bwd(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                      const CUtensorMap& mdo, const BwdParams& p, int64_t B) {
+    auto kq = attn_bwd_dq_tc_kernel<DK>;
+    auto kkv = attn_bwd_dkv_tc_kernel<DK>;
+    static bool attr = false;
+    if (!attr) {
+        PK_CHECK_CUDA(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<DK>::BYTES));
+        PK_CHECK_CUDA(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<DK>::BYTES));
+        attr = true;
+    }
+    const unsigned tiles = static_cast<unsigned>((p.S + AT_BM - 1) / AT_BM);
+    dim3 gq(tiles, p.Hq, static_cast<unsigned>(B));
+    kq<<<gq, 128, DqSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
+    PK_LAUNCH_CHECK();
+    dim3 gkv(tiles, p.Hkv, static_cast<unsigned>(B));
+    kkv<<<gkv, 128, DkvSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+int attn_tc_bwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                const float* lse, const float* delta, const void* dout, int64_t lddo, void* dq, int64_t lddq,
+                void* dk_, int64_t lddk, void* dv, int64_t lddv, int64_t B, int64_t S, int Hq, int Hkv, int dk,
+                float scale, int causal) {
+    CUtensorMap mq, mk, mv, mdo;
+    const int64_t R = B * S;
+    int rc = make_tensor_map(&mq, q, static_cast<int64_t>(Hq) * dk, R, ldq, 64, AT_BM);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mk, k, static_cast<int64_t>(Hkv) * dk, R, ldk, 64, AT_BN);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mv, v, static_cast<int64_t>(Hkv) * dk, R, ldv, 64, AT_BN);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mdo, dout, static_cast<int64_t>(Hq) * dk, R, lddo, 64, AT_BM);
+    if (rc != PK_OK) return rc;
+    BwdParams p;
+    p.dq = static_cast<bf16*>(dq);
+    p.lddq = lddq;
+    p.dk = static_cast<bf16*>(dk_);
+    p.lddk = lddk;
+    p.dv = static_cast<bf16*>(dv);
+    p.lddv = lddv;
+    p.lse = lse;
+    p.delta = delta;
+    p.S = S;
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.scale = scale;
+    p.scale_log2 = scale * LOG2E;
+    p.causal = causal;
+    return dk == 64 ? launch_bwd<64>(st, mq, mk, mv, mdo, p, B) : launch_bwd<128>(st, mq, mk, mv, mdo, p, B);
+}
+
 // ---- entry points used by the dispatcher in pk_attn_simt.cu ------------------------------
 int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                       int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S) {

@@ -362,6 +362,16 @@ def test_attention(pk, dtype, cfg):
     pkt.check(pk.pk_attn_bwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
                              Hq * dk, ptr(lse), ptr(do), Hq * dk, ptr(dq), Hq * dk, ptr(dkk), Hkv * dk, ptr(dv),
                              Hkv * dk, ptr(sc), B, S, Hq, Hkv, dk, scale, int(causal)))
+    if dtype == torch.bfloat16 and dk in (64, 128):
+        assert pk.pk_attn_last_path() == 1, "tensor-core attention backward was not selected"
+        st = ctypes.c_int(0)
+        pkt.check(pk.pk_attn_tc_status(ctypes.byref(st), 1))
+        assert st.value == 0, "tensor-core attention backward reported a wait that gave up"
+        dq2, dk2, dv2 = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        pkt.check(pk.pk_attn_bwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
+                                 Hq * dk, ptr(lse), ptr(do), Hq * dk, ptr(dq2), Hq * dk, ptr(dk2), Hkv * dk, ptr(dv2),
+                                 Hkv * dk, ptr(sc), B, S, Hq, Hkv, dk, scale, int(causal)))
+        assert torch.equal(dq, dq2) and torch.equal(dkk, dk2) and torch.equal(dv, dv2), "backward not reproducible"
     gtol = 1e-4 if dtype == torch.float32 else 6e-2
     close(dq, qf.grad, gtol)
     close(dkk, kf.grad, gtol)
