@@ -275,25 +275,17 @@ def main():
             self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
 
     def make_step(m):
-        buckets = [torch.as_tensor(_Buf(p, n), device="cuda") for (p, n) in m.buckets()] if world > 1 else []
-        pending = []
-        n_blocks = len(buckets) - 1
-
-        def hook(k):  # block (n_blocks-1-k) finished its backward: start its all-reduce
-            i = n_blocks - 1 - k
-            if 0 <= i < n_blocks:
-                pending.append(dist.all_reduce(buckets[i], op=dist.ReduceOp.SUM, async_op=True))
-
+        reducer = None
         if world > 1:
-            mt.set_segment_hook(hook)
+            from paperkiln_b200.dp import BucketAllReducer
+            # block i's gradients are one contiguous fp32 range of the flat gradient buffer
+            reducer = BucketAllReducer([torch.as_tensor(_Buf(p, n), device="cuda") for (p, n) in m.buckets()])
+            mt.set_segment_hook(reducer.on_segment)  # fires as each block's backward is enqueued
 
         def step(i):
             loss = m.step_ptr(host_ids[i].data_ptr(), host_tg[i].data_ptr(), n_local, S, loss_scale=1.0 / world)
-            if world > 1:
-                pending.append(dist.all_reduce(buckets[-1], op=dist.ReduceOp.SUM, async_op=True))
-                for h in pending:
-                    h.wait()
-                pending.clear()
+            if reducer is not None:
+                reducer.finish()  # remaining buckets, then wait for all of them
             m.optimizer_step()
             return loss
         return step

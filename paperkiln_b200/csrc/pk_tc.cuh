@@ -9,7 +9,7 @@
 namespace pk {
 namespace tc {
 
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // a wait that lasts 2 s is abandoned
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // ~2 s of SM clock: a longer wait is abandoned
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -42,12 +42,14 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
 // Bounded wait: false when abandoned (time limit reached here or elsewhere in the CTA).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
     if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try(bar, parity)) return true;
         if ((it & 255u) == 0u) {
-            if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            // once any CTA of any launch has given up, the others drain instead of each
+            // waiting out its own limit
+            if (*abort_flag || *reinterpret_cast<volatile int*>(status) != 0) return false;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
                 atomicOr(status, PK_ERR_TIMEOUT);
                 return false;
