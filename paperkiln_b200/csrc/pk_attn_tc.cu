@@ -2,16 +2,26 @@
 // memory), head_dim 64 or 128, causal or full, grouped-query head mapping, B stacked
 // sequences. The score matrix lives only in tensor memory and registers.
 //
-// Forward, one CTA of 128 threads per (128-query tile, head, sequence); thread t owns query
-// row t (= tensor-memory lane t). Per 128-key tile:
-//     S = Q K^T                tcgen05.mma, operands TMA-loaded into swizzled smem
-//     p = exp2(S*c - m)        each thread reads its row of S from tensor memory (two sweeps:
-//                              max, then exponentials), writes P as bf16 into smem in the
-//                              operand layout of the next MMA
-//     O_tile = P V             tcgen05.mma (V read as an MN-major operand, no transpose)
-//     o = o*corr + O_tile      running output kept in registers, rescaled per tile
-// Two CTAs fit one SM (shared memory, tensor-memory columns), so one CTA's softmax overlaps
-// the other's MMAs. Every mbarrier wait is bounded (status word, no trap).
+// All three kernels use CTAs of 256 threads working on a 128-row tile: warps w and w+4
+// share tensor-memory lane quadrant w (rows 32w..32w+31) and split the COLUMNS of every
+// tile between them, so thread (row r, half hf) owns row r of the tile and 64 of its 128
+// score columns / half of its head_dim output columns. Thread 0 additionally issues the
+// TMA loads and the MMAs.
+//
+// Forward, per (128-query tile, head, sequence), per 128-key tile:
+//     S = Q K^T                tcgen05.mma, operands TMA-loaded into 128B-swizzled smem
+//     p = exp2(S*c - m)        one sweep over the thread's 64 columns held in registers; the
+//                              row maximum is combined with the partner thread through smem
+//     O_tile = P V             P written as a bf16 operand tile; V read MN-major (no transpose)
+//     o = o*corr + O_tile      running output in registers, rescaled per tile
+// Backward, two kernels, no atomics (every gradient element has one owner, fixed order):
+//     dQ kernel     per query tile, loops over key tiles: S = Q K^T, dP = dO V^T in tensor
+//                   memory; dS = P (dP - delta) scale -> bf16 smem; dQ += dS K (K MN-major)
+//     dK/dV kernel  per key tile, loops over the query heads of the group and their query
+//                   tiles; dV += P^T dO and dK += dS^T Q take P / dS as MN-major A operands
+//                   (the transpose is a descriptor bit) and dO / Q as MN-major B operands
+//     P is recomputed from the saved log-sum-exp: p = exp2(s*c - lse*log2 e).
+// Every mbarrier wait is bounded (status word, no trap).
 //
 // Semantics: ops::fused_attention of the reference (src/ops.cpp:863-934) applied per head.
 #include "pk_tc.cuh"
@@ -62,8 +72,9 @@ int make_tensor_map(CUtensorMap* map, const void* base, int64_t inner, int64_t o
 
 using namespace tc;
 
-constexpr int AT_BM = 128;  // queries per CTA
-constexpr int AT_BN = 128;  // keys per tile
+constexpr int AT_BM = 128;       // rows of the owning tile (queries, or keys in the dK/dV kernel)
+constexpr int AT_BN = 128;       // rows of the streamed tile
+constexpr int AT_THREADS_TC = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -71,12 +82,46 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
+// Barrier among the 64 threads (warps w and w+4) that share a lane quadrant.
+__device__ __forceinline__ void pair_sync(int quad) {
+    asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
+}
+template <int DK>
+__device__ __forceinline__ void load_tile_tma(uint32_t dst, const CUtensorMap* map, int col0, int64_t row, uint32_t bar) {
+#pragma unroll
+    for (int c = 0; c < DK / 64; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, col0 + c * 64, static_cast<int32_t>(row), bar);
+}
+// Writes 32 values as bf16 into 4 consecutive 16-byte units (unit0 .. unit0+3) of a row.
+__device__ __forceinline__ void store32_bf16(uint8_t* chunk, int row, int unit0, const float (&v)[32]) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint4 w;
+        w.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
+        w.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
+        w.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
+        w.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
+        st_swizzled(chunk, row, unit0 + g, w);
+    }
+}
+// 32 fp32 accumulator values of tensor memory -> bf16 -> global (64 contiguous bytes).
+__device__ __forceinline__ void store32_global(bf16* dst, const uint32_t (&r)[32], float mul) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint4 w;
+        w.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * mul, __uint_as_float(r[g * 8 + 1]) * mul);
+        w.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * mul, __uint_as_float(r[g * 8 + 3]) * mul);
+        w.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * mul, __uint_as_float(r[g * 8 + 5]) * mul);
+        w.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * mul, __uint_as_float(r[g * 8 + 7]) * mul);
+        *reinterpret_cast<uint4*>(dst + g * 8) = w;
+    }
+}
 
+// ================================================================================ forward
 struct FwdParams {
     bf16* out;
     int64_t ldo;
     float* lse;
-    int64_t S;
+    int S;
     int Hq, Hkv;
     float scale_log2;  // scale * log2(e)
     int causal;
@@ -84,23 +129,24 @@ struct FwdParams {
 
 template <int DK>
 struct FwdSmem {
-    static constexpr int NCH = DK / 64;                       // 64-wide chunks per Q/K/V tile
-    static constexpr int TILE = NCH * (int)CHUNK_BYTES;       // bytes of one Q/K/V tile
+    static constexpr int NCH = DK / 64;
+    static constexpr int TILE = NCH * (int)CHUNK_BYTES;
     static constexpr int OFF_Q = 0;
-    static constexpr int OFF_K = TILE;                        // 2 stages
-    static constexpr int OFF_V = 3 * TILE;                    // 1 stage
-    static constexpr int OFF_P = 4 * TILE;                    // 2 chunks (128 keys)
-    static constexpr int OFF_BAR = 4 * TILE + 2 * (int)CHUNK_BYTES;
-    static constexpr int BYTES = OFF_BAR + 128 + 1024;        // + alignment slack
+    static constexpr int OFF_K = TILE;        // 2 stages
+    static constexpr int OFF_V = 3 * TILE;    // 1 stage
+    static constexpr int OFF_P = 4 * TILE;    // 2 chunks (128 keys)
+    static constexpr int OFF_X = 4 * TILE + 2 * (int)CHUNK_BYTES;  // row max / row sum exchange: 2 x 128 floats
+    static constexpr int OFF_BAR = OFF_X + 1024;
+    static constexpr int BYTES = OFF_BAR + 128 + 1024;
 };
 
 template <int DK>
-__global__ void __launch_bounds__(128, DK == 64 ? 2 : 1)
+__global__ void __launch_bounds__(AT_THREADS_TC, DK == 64 ? 2 : 1)
 attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const FwdParams p) {
     using L = FwdSmem<DK>;
-    constexpr int NCH = L::NCH;
     constexpr uint32_t TMEM_COLS = 256;
+    constexpr int OH = DK / 2;  // output columns per thread
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
@@ -111,15 +157,18 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint64_t* bar_o = bars + 5;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(smem + L::OFF_X);  // [2][128]
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, hf = warp >> 2;
+    const int row = quad * 32 + lane;
     const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long tiles first
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (p.Hq / p.Hkv);
     const int64_t seq0 = static_cast<int64_t>(b) * p.S;
-    const int64_t q0 = static_cast<int64_t>(qt) * AT_BM;
-    const int64_t qi = q0 + tid;
-    int nkv = static_cast<int>((p.S + AT_BN - 1) / AT_BN);
+    const int q0 = qt * AT_BM;
+    const int qi = q0 + row;
+    int nkv = (p.S + AT_BN - 1) / AT_BN;
     if (p.causal && qt + 1 < nkv) nkv = qt + 1;
 
     if (tid == 0) {
@@ -137,41 +186,35 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_s = tmem;          // S: 128 columns
-    const uint32_t t_o = tmem + 128;    // O_tile: DK columns
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem + lane_off + hf * 64;        // this thread's 64 score columns
+    const uint32_t t_o = tmem + 128 + lane_off + hf * OH;  // this thread's output columns
     const uint32_t sQ = smem_u32(smem + L::OFF_Q), sK0 = smem_u32(smem + L::OFF_K), sV = smem_u32(smem + L::OFF_V);
     const uint32_t sP = smem_u32(smem + L::OFF_P);
-    uint8_t* pP = smem + L::OFF_P;
+    uint8_t* pP = smem + L::OFF_P + hf * CHUNK_BYTES;  // 64 keys = one chunk per half
 
     if (tid == 0) {
         mbar_expect_tx(smem_u32(bar_q), L::TILE);
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-            tma_load_2d(sQ + c * CHUNK_BYTES, &map_q, h * DK + c * 64, static_cast<int32_t>(seq0 + q0), smem_u32(bar_q));
+        load_tile_tma<DK>(sQ, &map_q, h * DK, seq0 + q0, smem_u32(bar_q));
         mbar_expect_tx(smem_u32(&bar_k[0]), L::TILE);
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-            tma_load_2d(sK0 + c * CHUNK_BYTES, &map_k, hk * DK + c * 64, static_cast<int32_t>(seq0), smem_u32(&bar_k[0]));
+        load_tile_tma<DK>(sK0, &map_k, hk * DK, seq0, smem_u32(&bar_k[0]));
     }
     const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
     const uint32_t idesc_o = idesc_bf16(DK, 0, 1);
 
-    float o[DK];
+    float o[OH];
 #pragma unroll
-    for (int i = 0; i < DK; ++i) o[i] = 0.0f;
-    float m = -INFINITY, l = 0.0f;
+    for (int i = 0; i < OH; ++i) o[i] = 0.0f;
+    float m = -INFINITY, l = 0.0f;  // l: partial row sum over this thread's columns
     bool ok = true;
 
     for (int j = 0; j < nkv && ok; ++j) {
         const int st = j & 1;
-        const int64_t kv0 = static_cast<int64_t>(j) * AT_BN;
+        const int kv0 = j * AT_BN;
         if (tid == 0) {
             // V_j: the single V buffer is free, P.V of the previous tile was waited for below
             mbar_expect_tx(smem_u32(bar_v), L::TILE);
-#pragma unroll
-            for (int c = 0; c < NCH; ++c)
-                tma_load_2d(sV + c * CHUNK_BYTES, &map_v, hk * DK + c * 64, static_cast<int32_t>(seq0 + kv0), smem_u32(bar_v));
+            load_tile_tma<DK>(sV, &map_v, hk * DK, seq0 + kv0, smem_u32(bar_v));
             if (j == 0) ok = mbar_wait(smem_u32(bar_q), 0, abort_flag, &g_attn_tc_status);
             if (ok) ok = mbar_wait(smem_u32(&bar_k[st]), (j >> 1) & 1, abort_flag, &g_attn_tc_status);
             if (ok) {
@@ -179,90 +222,78 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint32_t sK = sK0 + st * L::TILE;
 #pragma unroll
                 for (int k = 0; k < DK / 16; ++k)
-                    mma_bf16(t_s, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
+                    mma_bf16(tmem, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
                 commit(smem_u32(bar_s));
                 if (j + 1 < nkv) {  // prefetch K_{j+1}; its buffer was last read by S of tile j-1
-                    const uint32_t sKn = sK0 + (st ^ 1) * L::TILE;
                     mbar_expect_tx(smem_u32(&bar_k[st ^ 1]), L::TILE);
-#pragma unroll
-                    for (int c = 0; c < NCH; ++c)
-                        tma_load_2d(sKn + c * CHUNK_BYTES, &map_k, hk * DK + c * 64,
-                                    static_cast<int32_t>(seq0 + kv0 + AT_BN), smem_u32(&bar_k[st ^ 1]));
+                    load_tile_tma<DK>(sK0 + (st ^ 1) * L::TILE, &map_k, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_k[st ^ 1]));
                 }
             }
         }
-        if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) ok = false;
         fence_after();
+        uint32_t r0[32], r1[32];
+        tmem_ld32(t_s, r0);
+        tmem_ld32(t_s + 32, r1);
+        tmem_wait_ld();
         const bool need_mask = (p.causal && kv0 + AT_BN - 1 > q0) || (kv0 + AT_BN > p.S);
-        // ---- sweep 1: row maximum of the raw scores
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(t_s + lane_off + ch * 32, r);
-            tmem_wait_ld();
+        if (need_mask) {
+            const int key0 = kv0 + hf * 64;
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-                float s = __uint_as_float(r[e]);
-                if (need_mask) {
-                    const int64_t key = kv0 + ch * 32 + e;
-                    if (key >= p.S || (p.causal && key > qi)) s = -INFINITY;
-                }
-                mx = fmaxf(mx, s);
+                if (key0 + e >= p.S || (p.causal && key0 + e > qi)) r0[e] = 0xff800000u;            // -inf
+                if (key0 + 32 + e >= p.S || (p.causal && key0 + 32 + e > qi)) r1[e] = 0xff800000u;
             }
         }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
+        xch[hf * 128 + row] = mx;
+        pair_sync(quad);
+        mx = fmaxf(mx, xch[(hf ^ 1) * 128 + row]);
         const float m_new = fmaxf(m, mx * p.scale_log2);
         const float corr = m == -INFINITY ? 0.0f : exp2f(m - m_new);
-        l *= corr;
-        // ---- sweep 2: exponentials, row sum, P -> smem (bf16, operand layout)
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(t_s + lane_off + ch * 32, r);
-            tmem_wait_ld();
-            float pv[32];
+        // m_new is finite for every tile a row takes part in (its diagonal key is visible)
+        float sum = 0.0f;
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                float s = __uint_as_float(r[e]);
-                bool vis = true;
-                if (need_mask) {
-                    const int64_t key = kv0 + ch * 32 + e;
-                    vis = key < p.S && (!p.causal || key <= qi);
-                }
-                const float pe = vis ? exp2f(s * p.scale_log2 - m_new) : 0.0f;
-                pv[e] = pe;
-                l += pe;
-            }
+        for (int g = 0; g < 8; ++g) {  // 8 keys -> one 16-byte unit of the P operand tile
+            float pe[8];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int unit = ch * 4 + g;  // 16 units of 8 keys
-                uint4 v;
-                v.x = pack_bf16(pv[g * 8 + 0], pv[g * 8 + 1]);
-                v.y = pack_bf16(pv[g * 8 + 2], pv[g * 8 + 3]);
-                v.z = pack_bf16(pv[g * 8 + 4], pv[g * 8 + 5]);
-                v.w = pack_bf16(pv[g * 8 + 6], pv[g * 8 + 7]);
-                st_swizzled(pP + (unit >> 3) * CHUNK_BYTES, tid, unit & 7, v);
+            for (int e = 0; e < 8; ++e) {
+                const uint32_t raw = g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e];
+                pe[e] = exp2f(__uint_as_float(raw) * p.scale_log2 - m_new);
+                sum += pe[e];
             }
+            uint4 w;
+            w.x = pack_bf16(pe[0], pe[1]);
+            w.y = pack_bf16(pe[2], pe[3]);
+            w.z = pack_bf16(pe[4], pe[5]);
+            w.w = pack_bf16(pe[6], pe[7]);
+            st_swizzled(pP, row, g, w);
         }
+        l = l * corr + sum;
         fence_async_smem();
         fence_before();
-        __syncthreads();
+        if (__syncthreads_or(!ok)) {  // CTA-uniform exit as soon as any thread's wait gave up
+            ok = false;
+            break;
+        }
         if (tid == 0) {
             ok = mbar_wait(smem_u32(bar_v), j & 1, abort_flag, &g_attn_tc_status);
             if (ok) {
                 fence_after();
 #pragma unroll
                 for (int k = 0; k < AT_BN / 16; ++k)
-                    mma_bf16(t_o, desc_kmajor(sP, k), desc_mnmajor(sV, k), idesc_o, k > 0 ? 1u : 0u);
+                    mma_bf16(tmem + 128, desc_kmajor(sP, k), desc_mnmajor(sV, k), idesc_o, k > 0 ? 1u : 0u);
                 commit(smem_u32(bar_o));
             }
         }
-        if (!mbar_wait(smem_u32(bar_o), j & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(bar_o), j & 1, abort_flag, &g_attn_tc_status)) ok = false;
         fence_after();
 #pragma unroll
-        for (int ch = 0; ch < DK / 32; ++ch) {
+        for (int ch = 0; ch < OH / 32; ++ch) {
             uint32_t r[32];
-            tmem_ld32(t_o + lane_off + ch * 32, r);
+            tmem_ld32(t_o + ch * 32, r);
             tmem_wait_ld();
 #pragma unroll
             for (int e = 0; e < 32; ++e) o[ch * 32 + e] = o[ch * 32 + e] * corr + __uint_as_float(r[e]);
@@ -270,11 +301,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         m = m_new;
     }
 
+    // total row sum = the two halves' partial sums
+    __syncthreads();
+    xch[hf * 128 + row] = l;
+    pair_sync(quad);
+    l += xch[(hf ^ 1) * 128 + row];
     if (ok && qi < p.S) {
         const float inv = 1.0f / l;
-        bf16* dst = p.out + (seq0 + qi) * p.ldo + h * DK;
+        bf16* dst = p.out + (seq0 + qi) * p.ldo + h * DK + hf * OH;
 #pragma unroll
-        for (int g = 0; g < DK / 8; ++g) {
+        for (int g = 0; g < OH / 8; ++g) {
             uint4 v;
             v.x = pack_bf16(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
             v.y = pack_bf16(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
@@ -282,7 +318,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             v.w = pack_bf16(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
             *reinterpret_cast<uint4*>(dst + g * 8) = v;
         }
-        p.lse[(seq0 + qi) * p.Hq + h] = (m + log2f(l)) * LN2;
+        if (hf == 0) p.lse[(seq0 + qi) * p.Hq + h] = (m + log2f(l)) * LN2;
     }
     fence_before();
     __syncthreads();
@@ -303,21 +339,12 @@ static int launch_fwd(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap&
         attr = true;
     }
     dim3 grid(static_cast<unsigned>((p.S + AT_BM - 1) / AT_BM), p.Hq, static_cast<unsigned>(B));
-    kern<<<grid, 128, L::BYTES, st>>>(mq, mk, mv, p);
+    kern<<<grid, AT_THREADS_TC, L::BYTES, st>>>(mq, mk, mv, p);
     PK_LAUNCH_CHECK();
     return PK_OK;
 }
 
 // ================================================================================ backward
-// Two kernels, no atomics: gradients are owned by one CTA each and summed in a fixed order.
-//   dQ kernel     one CTA per (128-query tile, head, sequence), loops over key tiles:
-//                 S = Q K^T, dP = dO V^T (tensor memory); dS = P (dP - delta) scale as bf16
-//                 in smem; dQ += dS K with K read as an MN-major operand
-//   dK/dV kernel  one CTA per (128-key tile, kv head, sequence), loops over the query heads
-//                 of the group and their query tiles: S and dP as above, P and dS written as
-//                 bf16 [query, key]; dV += P^T dO and dK += dS^T Q take P / dS as MN-major A
-//                 operands (the transpose is a descriptor bit), dO / Q as MN-major B operands
-// P is recomputed from the saved log-sum-exp: p = exp2(s*c - lse*log2 e).
 struct BwdParams {
     bf16* dq;
     int64_t lddq;
@@ -327,45 +354,27 @@ struct BwdParams {
     int64_t lddv;
     const float* lse;
     const float* delta;
-    int64_t S;
+    int S;
     int Hq, Hkv;
     float scale, scale_log2;
     int causal;
 };
 
-template <int DK>
-__device__ __forceinline__ void load_tile_tma(uint32_t dst, const CUtensorMap* map, int col0, int64_t row, uint32_t bar) {
-#pragma unroll
-    for (int c = 0; c < DK / 64; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, col0 + c * 64, static_cast<int32_t>(row), bar);
-}
-
-// Reads one 32-column chunk of S and dP for this thread's query row and produces p and ds.
-__device__ __forceinline__ void softmax_grad_chunk(uint32_t t_s, uint32_t t_dp, int ch, int64_t key0, int64_t qi, int64_t S,
-                                                   bool causal, bool row_ok, float scale, float scale_log2, float lse2,
-                                                   float delta, float (&pv)[32], float (&dsv)[32]) {
+// p and ds for 32 columns starting at tensor-memory column `col` of this thread's row.
+__device__ __forceinline__ void softmax_grad32(uint32_t t_s, uint32_t t_dp, int key0, int qi, int S, bool causal,
+                                               bool row_ok, bool need_mask, float scale, float scale_log2, float lse2,
+                                               float delta, float (&pv)[32], float (&dsv)[32]) {
     uint32_t rs[32], rd[32];
-    tmem_ld32(t_s + ch * 32, rs);
-    tmem_ld32(t_dp + ch * 32, rd);
+    tmem_ld32(t_s, rs);
+    tmem_ld32(t_dp, rd);
     tmem_wait_ld();
 #pragma unroll
     for (int e = 0; e < 32; ++e) {
-        const int64_t key = key0 + ch * 32 + e;
-        const bool vis = row_ok && key < S && (!causal || key <= qi);
+        bool vis = row_ok;
+        if (need_mask) vis = vis && key0 + e < S && (!causal || key0 + e <= qi);
         const float pe = vis ? exp2f(__uint_as_float(rs[e]) * scale_log2 - lse2) : 0.0f;
         pv[e] = pe;
         dsv[e] = pe * (__uint_as_float(rd[e]) - delta) * scale;
-    }
-}
-__device__ __forceinline__ void store_chunk_bf16(uint8_t* tile, int row, int ch, const float (&v)[32]) {
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-        const int unit = ch * 4 + g;
-        uint4 w;
-        w.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
-        w.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
-        w.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
-        w.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
-        st_swizzled(tile + (unit >> 3) * CHUNK_BYTES, row, unit & 7, w);
     }
 }
 
@@ -375,21 +384,22 @@ struct DqSmem {
     static constexpr int NST = DK == 64 ? 2 : 1;  // K/V stages
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_DO = TILE;
-    static constexpr int OFF_K = 2 * TILE;               // NST stages
-    static constexpr int OFF_V = 2 * TILE + NST * TILE;  // NST stages
+    static constexpr int OFF_K = 2 * TILE;
+    static constexpr int OFF_V = 2 * TILE + NST * TILE;
     static constexpr int OFF_DS = 2 * TILE + 2 * NST * TILE;
     static constexpr int OFF_BAR = OFF_DS + 2 * (int)CHUNK_BYTES;
     static constexpr int BYTES = OFF_BAR + 128 + 1024;
 };
 
 template <int DK>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(AT_THREADS_TC, 1)
 attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                       const BwdParams p) {
     using L = DqSmem<DK>;
     constexpr int NST = L::NST;
     constexpr uint32_t TMEM_COLS = 512;
+    constexpr int OH = DK / 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
@@ -400,15 +410,17 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, hf = warp >> 2;
+    const int row = quad * 32 + lane;
     const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
     const int h = blockIdx.y, b = blockIdx.z;
     const int hk = h / (p.Hq / p.Hkv);
     const int64_t seq0 = static_cast<int64_t>(b) * p.S;
-    const int64_t q0 = static_cast<int64_t>(qt) * AT_BM;
-    const int64_t qi = q0 + tid;
+    const int q0 = qt * AT_BM;
+    const int qi = q0 + row;
     const bool row_ok = qi < p.S;
-    int nkv = static_cast<int>((p.S + AT_BN - 1) / AT_BN);
+    int nkv = (p.S + AT_BN - 1) / AT_BN;
     if (p.causal && qt + 1 < nkv) nkv = qt + 1;
 
     if (tid == 0) {
@@ -425,11 +437,12 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     __syncthreads();
     fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t t_s = tmem + lane_off, t_dp = tmem + 128 + lane_off, t_dq = tmem + 256;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem + lane_off + hf * 64, t_dp = tmem + 128 + lane_off + hf * 64;
+    const uint32_t t_dq = tmem + 256;
     const uint32_t sQ = smem_u32(smem + L::OFF_Q), sDO = smem_u32(smem + L::OFF_DO);
     const uint32_t sK0 = smem_u32(smem + L::OFF_K), sV0 = smem_u32(smem + L::OFF_V), sDS = smem_u32(smem + L::OFF_DS);
-    uint8_t* pDS = smem + L::OFF_DS;
+    uint8_t* pDS = smem + L::OFF_DS + hf * CHUNK_BYTES;
 
     if (tid == 0) {
         mbar_expect_tx(smem_u32(bar_q), 2 * L::TILE);
@@ -448,7 +461,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     for (int j = 0; j < nkv && ok; ++j) {
         const int st = NST == 2 ? (j & 1) : 0;
         const uint32_t kv_phase = NST == 2 ? ((j >> 1) & 1) : (j & 1);
-        const int64_t kv0 = static_cast<int64_t>(j) * AT_BN;
+        const int kv0 = j * AT_BN;
         if (tid == 0) {
             if (NST == 1 && j > 0) {  // the single K/V stage is free once dQ of tile j-1 is done
                 ok = mbar_wait(smem_u32(bar_d), (j - 1) & 1, abort_flag, &g_attn_tc_status);
@@ -472,7 +485,7 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 commit(smem_u32(bar_s));
             }
         }
-        if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) ok = false;
         // S_j complete implies dQ of tile j-1 (issued earlier on the same pipe) is complete:
         // the dS buffer and, with two stages, the other K/V stage are free again.
         fence_after();
@@ -482,15 +495,20 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             load_tile_tma<DK>(sK0 + sn * L::TILE, &map_k, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_kv[sn]));
             load_tile_tma<DK>(sV0 + sn * L::TILE, &map_v, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_kv[sn]));
         }
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        const bool need_mask = (p.causal && kv0 + AT_BN - 1 > q0) || (kv0 + AT_BN > p.S);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
             float pv[32], dsv[32];
-            softmax_grad_chunk(t_s, t_dp, ch, kv0, qi, p.S, p.causal != 0, row_ok, p.scale, p.scale_log2, lse2, delta, pv, dsv);
-            store_chunk_bf16(pDS, tid, ch, dsv);
+            softmax_grad32(t_s + c * 32, t_dp + c * 32, kv0 + hf * 64 + c * 32, qi, p.S, p.causal != 0, row_ok, need_mask,
+                           p.scale, p.scale_log2, lse2, delta, pv, dsv);
+            store32_bf16(pDS, row, c * 4, dsv);
         }
         fence_async_smem();
         fence_before();
-        __syncthreads();
+        if (__syncthreads_or(!ok)) {  // CTA-uniform exit as soon as any thread's wait gave up
+            ok = false;
+            break;
+        }
         if (tid == 0) {
             fence_after();
             const uint32_t sK = sK0 + st * L::TILE;
@@ -503,23 +521,13 @@ attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (ok) ok = mbar_wait(smem_u32(bar_d), (nkv - 1) & 1, abort_flag, &g_attn_tc_status);
     if (ok) {
         fence_after();
-        bf16* dst = p.dq + (seq0 + qi) * p.lddq + h * DK;
-#pragma unroll 1
-        for (int ch = 0; ch < DK / 32; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(t_dq + lane_off + ch * 32, r);
-            tmem_wait_ld();
-            if (row_ok) {
+        bf16* dst = p.dq + (seq0 + qi) * p.lddq + h * DK + hf * OH;
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4 w;
-                    w.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-                    w.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-                    w.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-                    w.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-                    *reinterpret_cast<uint4*>(dst + ch * 32 + g * 8) = w;
-                }
-            }
+        for (int ch = 0; ch < OH / 32; ++ch) {
+            uint32_t r[32];
+            tmem_ld32(t_dq + lane_off + hf * OH + ch * 32, r);
+            tmem_wait_ld();
+            if (row_ok) store32_global(dst + ch * 32, r, 1.0f);
         }
     }
     fence_before();
@@ -536,8 +544,8 @@ struct DkvSmem {
     static constexpr int NST = DK == 64 ? 2 : 1;  // Q/dO stages
     static constexpr int OFF_K = 0;
     static constexpr int OFF_V = TILE;
-    static constexpr int OFF_Q = 2 * TILE;               // NST stages
-    static constexpr int OFF_DO = 2 * TILE + NST * TILE;  // NST stages
+    static constexpr int OFF_Q = 2 * TILE;
+    static constexpr int OFF_DO = 2 * TILE + NST * TILE;
     static constexpr int OFF_P = 2 * TILE + 2 * NST * TILE;
     static constexpr int OFF_DS = OFF_P + 2 * (int)CHUNK_BYTES;
     static constexpr int OFF_BAR = OFF_DS + 2 * (int)CHUNK_BYTES;
@@ -545,13 +553,14 @@ struct DkvSmem {
 };
 
 template <int DK>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(AT_THREADS_TC, 1)
 attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
                        const BwdParams p) {
     using L = DkvSmem<DK>;
     constexpr int NST = L::NST;
     constexpr uint32_t TMEM_COLS = 512;
+    constexpr int OH = DK / 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
@@ -562,13 +571,15 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int quad = warp & 3, hf = warp >> 2;
+    const int row = quad * 32 + lane;
     const int kt = blockIdx.x;
     const int hk = blockIdx.y, b = blockIdx.z;
     const int group = p.Hq / p.Hkv;
     const int64_t seq0 = static_cast<int64_t>(b) * p.S;
-    const int64_t k0 = static_cast<int64_t>(kt) * AT_BN;
-    const int nq_all = static_cast<int>((p.S + AT_BM - 1) / AT_BM);
+    const int k0 = kt * AT_BN;
+    const int nq_all = (p.S + AT_BM - 1) / AT_BM;
     const int i_begin = p.causal ? kt : 0;
     const int per_head = nq_all - i_begin;
     const int nit = per_head * group;
@@ -587,14 +598,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t t_s = tmem + lane_off, t_dp = tmem + 128 + lane_off;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem + lane_off + hf * 64, t_dp = tmem + 128 + lane_off + hf * 64;
     const uint32_t t_dv = tmem + 256, t_dk = tmem + 256 + DK;
     const uint32_t sK = smem_u32(smem + L::OFF_K), sV = smem_u32(smem + L::OFF_V);
     const uint32_t sQ0 = smem_u32(smem + L::OFF_Q), sDO0 = smem_u32(smem + L::OFF_DO);
     const uint32_t sP = smem_u32(smem + L::OFF_P), sDS = smem_u32(smem + L::OFF_DS);
-    uint8_t* pP = smem + L::OFF_P;
-    uint8_t* pDS = smem + L::OFF_DS;
+    uint8_t* pP = smem + L::OFF_P + hf * CHUNK_BYTES;
+    uint8_t* pDS = smem + L::OFF_DS + hf * CHUNK_BYTES;
 
     if (tid == 0) {
         mbar_expect_tx(smem_u32(bar_kv), 2 * L::TILE);
@@ -602,8 +613,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         load_tile_tma<DK>(sV, &map_v, hk * DK, seq0 + k0, smem_u32(bar_kv));
         if (nit > 0) {
             mbar_expect_tx(smem_u32(&bar_q[0]), 2 * L::TILE);
-            load_tile_tma<DK>(sQ0, &map_q, (hk * group) * DK, seq0 + static_cast<int64_t>(i_begin) * AT_BM, smem_u32(&bar_q[0]));
-            load_tile_tma<DK>(sDO0, &map_do, (hk * group) * DK, seq0 + static_cast<int64_t>(i_begin) * AT_BM, smem_u32(&bar_q[0]));
+            load_tile_tma<DK>(sQ0, &map_q, (hk * group) * DK, seq0 + i_begin * AT_BM, smem_u32(&bar_q[0]));
+            load_tile_tma<DK>(sDO0, &map_do, (hk * group) * DK, seq0 + i_begin * AT_BM, smem_u32(&bar_q[0]));
         }
     }
     const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
@@ -615,8 +626,8 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int h = hk * group + g;
         const int st = NST == 2 ? (it & 1) : 0;
         const uint32_t q_phase = NST == 2 ? ((it >> 1) & 1) : (it & 1);
-        const int64_t q0 = static_cast<int64_t>(i) * AT_BM;
-        const int64_t qi = q0 + tid;
+        const int q0 = i * AT_BM;
+        const int qi = q0 + row;
         const bool row_ok = qi < p.S;
         if (tid == 0) {
             if (NST == 1 && it > 0) {  // single Q/dO stage: wait for dV/dK of the previous iteration
@@ -643,7 +654,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         const float lse2 = row_ok ? p.lse[(seq0 + qi) * p.Hq + h] * LOG2E : 0.0f;
         const float delta = row_ok ? p.delta[(seq0 + qi) * p.Hq + h] : 0.0f;
-        if (!mbar_wait(smem_u32(bar_s), it & 1, abort_flag, &g_attn_tc_status)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(bar_s), it & 1, abort_flag, &g_attn_tc_status)) ok = false;
         // S of this iteration complete => dV/dK of the previous one (issued earlier) complete:
         // P, dS and the other Q/dO stage may be overwritten.
         fence_after();
@@ -651,19 +662,24 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const int itn = it + 1, sn = st ^ 1;
             const int hn = hk * group + itn / per_head, in_ = i_begin + itn % per_head;
             mbar_expect_tx(smem_u32(&bar_q[sn]), 2 * L::TILE);
-            load_tile_tma<DK>(sQ0 + sn * L::TILE, &map_q, hn * DK, seq0 + static_cast<int64_t>(in_) * AT_BM, smem_u32(&bar_q[sn]));
-            load_tile_tma<DK>(sDO0 + sn * L::TILE, &map_do, hn * DK, seq0 + static_cast<int64_t>(in_) * AT_BM, smem_u32(&bar_q[sn]));
+            load_tile_tma<DK>(sQ0 + sn * L::TILE, &map_q, hn * DK, seq0 + in_ * AT_BM, smem_u32(&bar_q[sn]));
+            load_tile_tma<DK>(sDO0 + sn * L::TILE, &map_do, hn * DK, seq0 + in_ * AT_BM, smem_u32(&bar_q[sn]));
         }
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        const bool need_mask = (p.causal && k0 + AT_BN - 1 > q0) || (k0 + AT_BN > p.S) || (q0 + AT_BM > p.S);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
             float pv[32], dsv[32];
-            softmax_grad_chunk(t_s, t_dp, ch, k0, qi, p.S, p.causal != 0, row_ok, p.scale, p.scale_log2, lse2, delta, pv, dsv);
-            store_chunk_bf16(pP, tid, ch, pv);
-            store_chunk_bf16(pDS, tid, ch, dsv);
+            softmax_grad32(t_s + c * 32, t_dp + c * 32, k0 + hf * 64 + c * 32, qi, p.S, p.causal != 0, row_ok, need_mask,
+                           p.scale, p.scale_log2, lse2, delta, pv, dsv);
+            store32_bf16(pP, row, c * 4, pv);
+            store32_bf16(pDS, row, c * 4, dsv);
         }
         fence_async_smem();
         fence_before();
-        __syncthreads();
+        if (__syncthreads_or(!ok)) {  // CTA-uniform exit as soon as any thread's wait gave up
+            ok = false;
+            break;
+        }
         if (tid == 0) {
             fence_after();
             const uint32_t sQ = sQ0 + st * L::TILE, sDO = sDO0 + st * L::TILE;
@@ -679,14 +695,14 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok && nit > 0) ok = mbar_wait(smem_u32(bar_d), (nit - 1) & 1, abort_flag, &g_attn_tc_status);
     if (ok) {
         fence_after();
-        const int64_t kj = k0 + tid;  // this thread's key row
+        const int kj = k0 + row;  // this thread's key row
         const bool key_ok = kj < p.S;
-#pragma unroll 1
+#pragma unroll
         for (int which = 0; which < 2; ++which) {
-            bf16* dst = (which == 0 ? p.dv + (seq0 + kj) * p.lddv : p.dk + (seq0 + kj) * p.lddk) + hk * DK;
-            const uint32_t t_src = (which == 0 ? t_dv : t_dk) + lane_off;
-#pragma unroll 1
-            for (int ch = 0; ch < DK / 32; ++ch) {
+            bf16* dst = (which == 0 ? p.dv + (seq0 + kj) * p.lddv : p.dk + (seq0 + kj) * p.lddk) + hk * DK + hf * OH;
+            const uint32_t t_src = (which == 0 ? t_dv : t_dk) + lane_off + hf * OH;
+#pragma unroll
+            for (int ch = 0; ch < OH / 32; ++ch) {
                 uint32_t r[32];
                 if (nit > 0) {
                     tmem_ld32(t_src + ch * 32, r);
@@ -695,17 +711,7 @@ attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
                     for (int e = 0; e < 32; ++e) r[e] = 0u;
                 }
-                if (key_ok) {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-                        w.y = pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-                        w.z = pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-                        w.w = pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-                        *reinterpret_cast<uint4*>(dst + ch * 32 + g * 8) = w;
-                    }
-                }
+                if (key_ok) store32_global(dst + ch * 32, r, 1.0f);
             }
         }
     }
@@ -730,12 +736,45 @@ static int launch_bwd(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap&
     }
     const unsigned tiles = static_cast<unsigned>((p.S + AT_BM - 1) / AT_BM);
     dim3 gq(tiles, p.Hq, static_cast<unsigned>(B));
-    kq<<<gq, 128, DqSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
+    kq<<<gq, AT_THREADS_TC, DqSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
     PK_LAUNCH_CHECK();
     dim3 gkv(tiles, p.Hkv, static_cast<unsigned>(B));
-    kkv<<<gkv, 128, DkvSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
+    kkv<<<gkv, AT_THREADS_TC, DkvSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
     PK_LAUNCH_CHECK();
     return PK_OK;
+}
+
+// ---- entry points used by the dispatcher in pk_attn_simt.cu ------------------------------
+int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
+                      int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S) {
+    if (dtype != PK_BF16 || (dk != 64 && dk != 128)) return 0;
+    if (ldq % 8 || ldk % 8 || ldv % 8 || ldo % 8) return 0;
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return 0;
+    if (B * S >= (int64_t(1) << 31) || S >= (int64_t(1) << 30)) return 0;
+    return 1;
+}
+
+int attn_tc_fwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
+                int causal) {
+    CUtensorMap mq, mk, mv;
+    const int64_t R = B * S;
+    int rc = make_tensor_map(&mq, q, static_cast<int64_t>(Hq) * dk, R, ldq, 64, AT_BM);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mk, k, static_cast<int64_t>(Hkv) * dk, R, ldk, 64, AT_BN);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mv, v, static_cast<int64_t>(Hkv) * dk, R, ldv, 64, AT_BN);
+    if (rc != PK_OK) return rc;
+    FwdParams p;
+    p.out = static_cast<bf16*>(out);
+    p.ldo = ldo;
+    p.lse = lse;
+    p.S = static_cast<int>(S);
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.scale_log2 = scale * LOG2E;
+    p.causal = causal;
+    return dk == 64 ? launch_fwd<64>(st, mq, mk, mv, p, B) : launch_fwd<128>(st, mq, mk, mv, p, B);
 }
 
 int attn_tc_bwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
@@ -761,46 +800,13 @@ int attn_tc_bwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int6
     p.lddv = lddv;
     p.lse = lse;
     p.delta = delta;
-    p.S = S;
+    p.S = static_cast<int>(S);
     p.Hq = Hq;
     p.Hkv = Hkv;
     p.scale = scale;
     p.scale_log2 = scale * LOG2E;
     p.causal = causal;
     return dk == 64 ? launch_bwd<64>(st, mq, mk, mv, mdo, p, B) : launch_bwd<128>(st, mq, mk, mv, mdo, p, B);
-}
-
-// ---- entry points used by the dispatcher in pk_attn_simt.cu ------------------------------
-int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
-                      int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S) {
-    if (dtype != PK_BF16 || (dk != 64 && dk != 128)) return 0;
-    if (ldq % 8 || ldk % 8 || ldv % 8 || ldo % 8) return 0;
-    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out)) return 0;
-    if (B * S >= (int64_t(1) << 31)) return 0;
-    return 1;
-}
-
-int attn_tc_fwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
-                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
-                int causal) {
-    CUtensorMap mq, mk, mv;
-    const int64_t R = B * S;
-    int rc = make_tensor_map(&mq, q, static_cast<int64_t>(Hq) * dk, R, ldq, 64, AT_BM);
-    if (rc != PK_OK) return rc;
-    rc = make_tensor_map(&mk, k, static_cast<int64_t>(Hkv) * dk, R, ldk, 64, AT_BN);
-    if (rc != PK_OK) return rc;
-    rc = make_tensor_map(&mv, v, static_cast<int64_t>(Hkv) * dk, R, ldv, 64, AT_BN);
-    if (rc != PK_OK) return rc;
-    FwdParams p;
-    p.out = static_cast<bf16*>(out);
-    p.ldo = ldo;
-    p.lse = lse;
-    p.S = S;
-    p.Hq = Hq;
-    p.Hkv = Hkv;
-    p.scale_log2 = scale * LOG2E;
-    p.causal = causal;
-    return dk == 64 ? launch_fwd<64>(st, mq, mk, mv, p, B) : launch_fwd<128>(st, mq, mk, mv, p, B);
 }
 
 }  // namespace pk
