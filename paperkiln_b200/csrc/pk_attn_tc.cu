@@ -31,6 +31,7 @@
 namespace pk {
 
 __device__ int g_attn_tc_status = 0;
+int attn_bwd_tc_status(int* status_h, int clear);  // pk_attn_bwd_tc.cu
 
 namespace tc {
 
@@ -344,406 +345,6 @@ static int launch_fwd(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap&
     return PK_OK;
 }
 
-// ================================================================================ backward
-struct BwdParams {
-    bf16* dq;
-    int64_t lddq;
-    bf16* dk;
-    int64_t lddk;
-    bf16* dv;
-    int64_t lddv;
-    const float* lse;
-    const float* delta;
-    int S;
-    int Hq, Hkv;
-    float scale, scale_log2;
-    int causal;
-};
-
-// p and ds for 32 columns starting at tensor-memory column `col` of this thread's row.
-__device__ __forceinline__ void softmax_grad32(uint32_t t_s, uint32_t t_dp, int key0, int qi, int S, bool causal,
-                                               bool row_ok, bool need_mask, float scale, float scale_log2, float lse2,
-                                               float delta, float (&pv)[32], float (&dsv)[32]) {
-    uint32_t rs[32], rd[32];
-    tmem_ld32(t_s, rs);
-    tmem_ld32(t_dp, rd);
-    tmem_wait_ld();
-#pragma unroll
-    for (int e = 0; e < 32; ++e) {
-        bool vis = row_ok;
-        if (need_mask) vis = vis && key0 + e < S && (!causal || key0 + e <= qi);
-        const float pe = vis ? exp2f(__uint_as_float(rs[e]) * scale_log2 - lse2) : 0.0f;
-        pv[e] = pe;
-        dsv[e] = pe * (__uint_as_float(rd[e]) - delta) * scale;
-    }
-}
-
-template <int DK>
-struct DqSmem {
-    static constexpr int TILE = (DK / 64) * (int)CHUNK_BYTES;
-    static constexpr int NST = DK == 64 ? 2 : 1;  // K/V stages
-    static constexpr int OFF_Q = 0;
-    static constexpr int OFF_DO = TILE;
-    static constexpr int OFF_K = 2 * TILE;
-    static constexpr int OFF_V = 2 * TILE + NST * TILE;
-    static constexpr int OFF_DS = 2 * TILE + 2 * NST * TILE;
-    static constexpr int OFF_BAR = OFF_DS + 2 * (int)CHUNK_BYTES;
-    static constexpr int BYTES = OFF_BAR + 128 + 1024;
-};
-
-template <int DK>
-__global__ void __launch_bounds__(AT_THREADS_TC, 1)
-attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                      const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                      const BwdParams p) {
-    using L = DqSmem<DK>;
-    constexpr int NST = L::NST;
-    constexpr uint32_t TMEM_COLS = 512;
-    constexpr int OH = DK / 2;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-    uint64_t* bar_q = bars;
-    uint64_t* bar_kv = bars + 1;  // [2]
-    uint64_t* bar_s = bars + 3;
-    uint64_t* bar_d = bars + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quad = warp & 3, hf = warp >> 2;
-    const int row = quad * 32 + lane;
-    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);
-    const int h = blockIdx.y, b = blockIdx.z;
-    const int hk = h / (p.Hq / p.Hkv);
-    const int64_t seq0 = static_cast<int64_t>(b) * p.S;
-    const int q0 = qt * AT_BM;
-    const int qi = q0 + row;
-    const bool row_ok = qi < p.S;
-    int nkv = (p.S + AT_BN - 1) / AT_BN;
-    if (p.causal && qt + 1 < nkv) nkv = qt + 1;
-
-    if (tid == 0) {
-        mbar_init(smem_u32(bar_q), 1);
-        mbar_init(smem_u32(&bar_kv[0]), 1);
-        mbar_init(smem_u32(&bar_kv[1]), 1);
-        mbar_init(smem_u32(bar_s), 1);
-        mbar_init(smem_u32(bar_d), 1);
-        *abort_flag = 0;
-        mbar_fence_init();
-    }
-    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    fence_before();
-    __syncthreads();
-    fence_after();
-    const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t t_s = tmem + lane_off + hf * 64, t_dp = tmem + 128 + lane_off + hf * 64;
-    const uint32_t t_dq = tmem + 256;
-    const uint32_t sQ = smem_u32(smem + L::OFF_Q), sDO = smem_u32(smem + L::OFF_DO);
-    const uint32_t sK0 = smem_u32(smem + L::OFF_K), sV0 = smem_u32(smem + L::OFF_V), sDS = smem_u32(smem + L::OFF_DS);
-    uint8_t* pDS = smem + L::OFF_DS + hf * CHUNK_BYTES;
-
-    if (tid == 0) {
-        mbar_expect_tx(smem_u32(bar_q), 2 * L::TILE);
-        load_tile_tma<DK>(sQ, &map_q, h * DK, seq0 + q0, smem_u32(bar_q));
-        load_tile_tma<DK>(sDO, &map_do, h * DK, seq0 + q0, smem_u32(bar_q));
-        mbar_expect_tx(smem_u32(&bar_kv[0]), 2 * L::TILE);
-        load_tile_tma<DK>(sK0, &map_k, hk * DK, seq0, smem_u32(&bar_kv[0]));
-        load_tile_tma<DK>(sV0, &map_v, hk * DK, seq0, smem_u32(&bar_kv[0]));
-    }
-    const float lse2 = row_ok ? p.lse[(seq0 + qi) * p.Hq + h] * LOG2E : 0.0f;
-    const float delta = row_ok ? p.delta[(seq0 + qi) * p.Hq + h] : 0.0f;
-    const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
-    const uint32_t idesc_q = idesc_bf16(DK, 0, 1);
-    bool ok = true;
-
-    for (int j = 0; j < nkv && ok; ++j) {
-        const int st = NST == 2 ? (j & 1) : 0;
-        const uint32_t kv_phase = NST == 2 ? ((j >> 1) & 1) : (j & 1);
-        const int kv0 = j * AT_BN;
-        if (tid == 0) {
-            if (NST == 1 && j > 0) {  // the single K/V stage is free once dQ of tile j-1 is done
-                ok = mbar_wait(smem_u32(bar_d), (j - 1) & 1, abort_flag, &g_attn_tc_status);
-                if (ok) {
-                    mbar_expect_tx(smem_u32(&bar_kv[0]), 2 * L::TILE);
-                    load_tile_tma<DK>(sK0, &map_k, hk * DK, seq0 + kv0, smem_u32(&bar_kv[0]));
-                    load_tile_tma<DK>(sV0, &map_v, hk * DK, seq0 + kv0, smem_u32(&bar_kv[0]));
-                }
-            }
-            if (ok && j == 0) ok = mbar_wait(smem_u32(bar_q), 0, abort_flag, &g_attn_tc_status);
-            if (ok) ok = mbar_wait(smem_u32(&bar_kv[st]), kv_phase, abort_flag, &g_attn_tc_status);
-            if (ok) {
-                fence_after();
-                const uint32_t sK = sK0 + st * L::TILE, sV = sV0 + st * L::TILE;
-#pragma unroll
-                for (int k = 0; k < DK / 16; ++k)
-                    mma_bf16(tmem, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < DK / 16; ++k)
-                    mma_bf16(tmem + 128, desc_kmajor(sDO, k), desc_kmajor(sV, k), idesc_s, k > 0 ? 1u : 0u);
-                commit(smem_u32(bar_s));
-            }
-        }
-        if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) ok = false;
-        // S_j complete implies dQ of tile j-1 (issued earlier on the same pipe) is complete:
-        // the dS buffer and, with two stages, the other K/V stage are free again.
-        fence_after();
-        if (tid == 0 && NST == 2 && j + 1 < nkv) {
-            const int sn = st ^ 1;
-            mbar_expect_tx(smem_u32(&bar_kv[sn]), 2 * L::TILE);
-            load_tile_tma<DK>(sK0 + sn * L::TILE, &map_k, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_kv[sn]));
-            load_tile_tma<DK>(sV0 + sn * L::TILE, &map_v, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_kv[sn]));
-        }
-        const bool need_mask = (p.causal && kv0 + AT_BN - 1 > q0) || (kv0 + AT_BN > p.S);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            float pv[32], dsv[32];
-            softmax_grad32(t_s + c * 32, t_dp + c * 32, kv0 + hf * 64 + c * 32, qi, p.S, p.causal != 0, row_ok, need_mask,
-                           p.scale, p.scale_log2, lse2, delta, pv, dsv);
-            store32_bf16(pDS, row, c * 4, dsv);
-        }
-        fence_async_smem();
-        fence_before();
-        if (__syncthreads_or(!ok)) {  // CTA-uniform exit as soon as any thread's wait gave up
-            ok = false;
-            break;
-        }
-        if (tid == 0) {
-            fence_after();
-            const uint32_t sK = sK0 + st * L::TILE;
-#pragma unroll
-            for (int k = 0; k < AT_BN / 16; ++k)
-                mma_bf16(t_dq, desc_kmajor(sDS, k), desc_mnmajor(sK, k), idesc_q, (j > 0 || k > 0) ? 1u : 0u);
-            commit(smem_u32(bar_d));
-        }
-    }
-    if (ok) ok = mbar_wait(smem_u32(bar_d), (nkv - 1) & 1, abort_flag, &g_attn_tc_status);
-    if (ok) {
-        fence_after();
-        bf16* dst = p.dq + (seq0 + qi) * p.lddq + h * DK + hf * OH;
-#pragma unroll
-        for (int ch = 0; ch < OH / 32; ++ch) {
-            uint32_t r[32];
-            tmem_ld32(t_dq + lane_off + hf * OH + ch * 32, r);
-            tmem_wait_ld();
-            if (row_ok) store32_global(dst + ch * 32, r, 1.0f);
-        }
-    }
-    fence_before();
-    __syncthreads();
-    if (warp == 0) {
-        fence_after();
-        tmem_dealloc(tmem, TMEM_COLS);
-    }
-}
-
-template <int DK>
-struct DkvSmem {
-    static constexpr int TILE = (DK / 64) * (int)CHUNK_BYTES;
-    static constexpr int NST = DK == 64 ? 2 : 1;  // Q/dO stages
-    static constexpr int OFF_K = 0;
-    static constexpr int OFF_V = TILE;
-    static constexpr int OFF_Q = 2 * TILE;
-    static constexpr int OFF_DO = 2 * TILE + NST * TILE;
-    static constexpr int OFF_P = 2 * TILE + 2 * NST * TILE;
-    static constexpr int OFF_DS = OFF_P + 2 * (int)CHUNK_BYTES;
-    static constexpr int OFF_BAR = OFF_DS + 2 * (int)CHUNK_BYTES;
-    static constexpr int BYTES = OFF_BAR + 128 + 1024;
-};
-
-template <int DK>
-__global__ void __launch_bounds__(AT_THREADS_TC, 1)
-attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                       const BwdParams p) {
-    using L = DkvSmem<DK>;
-    constexpr int NST = L::NST;
-    constexpr uint32_t TMEM_COLS = 512;
-    constexpr int OH = DK / 2;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
-    uint64_t* bar_kv = bars;
-    uint64_t* bar_q = bars + 1;  // [2]
-    uint64_t* bar_s = bars + 3;
-    uint64_t* bar_d = bars + 4;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 5);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int quad = warp & 3, hf = warp >> 2;
-    const int row = quad * 32 + lane;
-    const int kt = blockIdx.x;
-    const int hk = blockIdx.y, b = blockIdx.z;
-    const int group = p.Hq / p.Hkv;
-    const int64_t seq0 = static_cast<int64_t>(b) * p.S;
-    const int k0 = kt * AT_BN;
-    const int nq_all = (p.S + AT_BM - 1) / AT_BM;
-    const int i_begin = p.causal ? kt : 0;
-    const int per_head = nq_all - i_begin;
-    const int nit = per_head * group;
-
-    if (tid == 0) {
-        mbar_init(smem_u32(bar_kv), 1);
-        mbar_init(smem_u32(&bar_q[0]), 1);
-        mbar_init(smem_u32(&bar_q[1]), 1);
-        mbar_init(smem_u32(bar_s), 1);
-        mbar_init(smem_u32(bar_d), 1);
-        *abort_flag = 0;
-        mbar_fence_init();
-    }
-    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    fence_before();
-    __syncthreads();
-    fence_after();
-    const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t t_s = tmem + lane_off + hf * 64, t_dp = tmem + 128 + lane_off + hf * 64;
-    const uint32_t t_dv = tmem + 256, t_dk = tmem + 256 + DK;
-    const uint32_t sK = smem_u32(smem + L::OFF_K), sV = smem_u32(smem + L::OFF_V);
-    const uint32_t sQ0 = smem_u32(smem + L::OFF_Q), sDO0 = smem_u32(smem + L::OFF_DO);
-    const uint32_t sP = smem_u32(smem + L::OFF_P), sDS = smem_u32(smem + L::OFF_DS);
-    uint8_t* pP = smem + L::OFF_P + hf * CHUNK_BYTES;
-    uint8_t* pDS = smem + L::OFF_DS + hf * CHUNK_BYTES;
-
-    if (tid == 0) {
-        mbar_expect_tx(smem_u32(bar_kv), 2 * L::TILE);
-        load_tile_tma<DK>(sK, &map_k, hk * DK, seq0 + k0, smem_u32(bar_kv));
-        load_tile_tma<DK>(sV, &map_v, hk * DK, seq0 + k0, smem_u32(bar_kv));
-        if (nit > 0) {
-            mbar_expect_tx(smem_u32(&bar_q[0]), 2 * L::TILE);
-            load_tile_tma<DK>(sQ0, &map_q, (hk * group) * DK, seq0 + i_begin * AT_BM, smem_u32(&bar_q[0]));
-            load_tile_tma<DK>(sDO0, &map_do, (hk * group) * DK, seq0 + i_begin * AT_BM, smem_u32(&bar_q[0]));
-        }
-    }
-    const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
-    const uint32_t idesc_g = idesc_bf16(DK, 1, 1);
-    bool ok = true;
-
-    for (int it = 0; it < nit && ok; ++it) {
-        const int g = it / per_head, i = i_begin + it % per_head;
-        const int h = hk * group + g;
-        const int st = NST == 2 ? (it & 1) : 0;
-        const uint32_t q_phase = NST == 2 ? ((it >> 1) & 1) : (it & 1);
-        const int q0 = i * AT_BM;
-        const int qi = q0 + row;
-        const bool row_ok = qi < p.S;
-        if (tid == 0) {
-            if (NST == 1 && it > 0) {  // single Q/dO stage: wait for dV/dK of the previous iteration
-                ok = mbar_wait(smem_u32(bar_d), (it - 1) & 1, abort_flag, &g_attn_tc_status);
-                if (ok) {
-                    mbar_expect_tx(smem_u32(&bar_q[0]), 2 * L::TILE);
-                    load_tile_tma<DK>(sQ0, &map_q, h * DK, seq0 + q0, smem_u32(&bar_q[0]));
-                    load_tile_tma<DK>(sDO0, &map_do, h * DK, seq0 + q0, smem_u32(&bar_q[0]));
-                }
-            }
-            if (ok && it == 0) ok = mbar_wait(smem_u32(bar_kv), 0, abort_flag, &g_attn_tc_status);
-            if (ok) ok = mbar_wait(smem_u32(&bar_q[st]), q_phase, abort_flag, &g_attn_tc_status);
-            if (ok) {
-                fence_after();
-                const uint32_t sQ = sQ0 + st * L::TILE, sDO = sDO0 + st * L::TILE;
-#pragma unroll
-                for (int k = 0; k < DK / 16; ++k)
-                    mma_bf16(tmem, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < DK / 16; ++k)
-                    mma_bf16(tmem + 128, desc_kmajor(sDO, k), desc_kmajor(sV, k), idesc_s, k > 0 ? 1u : 0u);
-                commit(smem_u32(bar_s));
-            }
-        }
-        const float lse2 = row_ok ? p.lse[(seq0 + qi) * p.Hq + h] * LOG2E : 0.0f;
-        const float delta = row_ok ? p.delta[(seq0 + qi) * p.Hq + h] : 0.0f;
-        if (!mbar_wait(smem_u32(bar_s), it & 1, abort_flag, &g_attn_tc_status)) ok = false;
-        // S of this iteration complete => dV/dK of the previous one (issued earlier) complete:
-        // P, dS and the other Q/dO stage may be overwritten.
-        fence_after();
-        if (tid == 0 && NST == 2 && it + 1 < nit) {
-            const int itn = it + 1, sn = st ^ 1;
-            const int hn = hk * group + itn / per_head, in_ = i_begin + itn % per_head;
-            mbar_expect_tx(smem_u32(&bar_q[sn]), 2 * L::TILE);
-            load_tile_tma<DK>(sQ0 + sn * L::TILE, &map_q, hn * DK, seq0 + in_ * AT_BM, smem_u32(&bar_q[sn]));
-            load_tile_tma<DK>(sDO0 + sn * L::TILE, &map_do, hn * DK, seq0 + in_ * AT_BM, smem_u32(&bar_q[sn]));
-        }
-        const bool need_mask = (p.causal && k0 + AT_BN - 1 > q0) || (k0 + AT_BN > p.S) || (q0 + AT_BM > p.S);
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-            float pv[32], dsv[32];
-            softmax_grad32(t_s + c * 32, t_dp + c * 32, k0 + hf * 64 + c * 32, qi, p.S, p.causal != 0, row_ok, need_mask,
-                           p.scale, p.scale_log2, lse2, delta, pv, dsv);
-            store32_bf16(pP, row, c * 4, pv);
-            store32_bf16(pDS, row, c * 4, dsv);
-        }
-        fence_async_smem();
-        fence_before();
-        if (__syncthreads_or(!ok)) {  // CTA-uniform exit as soon as any thread's wait gave up
-            ok = false;
-            break;
-        }
-        if (tid == 0) {
-            fence_after();
-            const uint32_t sQ = sQ0 + st * L::TILE, sDO = sDO0 + st * L::TILE;
-#pragma unroll
-            for (int k = 0; k < AT_BM / 16; ++k)   // dV += P^T dO   (contraction over the 128 queries)
-                mma_bf16(t_dv, desc_mnmajor(sP, k), desc_mnmajor(sDO, k), idesc_g, (it > 0 || k > 0) ? 1u : 0u);
-#pragma unroll
-            for (int k = 0; k < AT_BM / 16; ++k)   // dK += dS^T Q
-                mma_bf16(t_dk, desc_mnmajor(sDS, k), desc_mnmajor(sQ, k), idesc_g, (it > 0 || k > 0) ? 1u : 0u);
-            commit(smem_u32(bar_d));
-        }
-    }
-    if (ok && nit > 0) ok = mbar_wait(smem_u32(bar_d), (nit - 1) & 1, abort_flag, &g_attn_tc_status);
-    if (ok) {
-        fence_after();
-        const int kj = k0 + row;  // this thread's key row
-        const bool key_ok = kj < p.S;
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-            bf16* dst = (which == 0 ? p.dv + (seq0 + kj) * p.lddv : p.dk + (seq0 + kj) * p.lddk) + hk * DK + hf * OH;
-            const uint32_t t_src = (which == 0 ? t_dv : t_dk) + lane_off + hf * OH;
-#pragma unroll
-            for (int ch = 0; ch < OH / 32; ++ch) {
-                uint32_t r[32];
-                if (nit > 0) {
-                    tmem_ld32(t_src + ch * 32, r);
-                    tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) r[e] = 0u;
-                }
-                if (key_ok) store32_global(dst + ch * 32, r, 1.0f);
-            }
-        }
-    }
-    fence_before();
-    __syncthreads();
-    if (warp == 0) {
-        fence_after();
-        tmem_dealloc(tmem, TMEM_COLS);
-    }
-}
-
-template <int DK>
-static int launch_bwd(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                      const CUtensorMap& mdo, const BwdParams& p, int64_t B) {
-    auto kq = attn_bwd_dq_tc_kernel<DK>;
-    auto kkv = attn_bwd_dkv_tc_kernel<DK>;
-    static bool attr = false;
-    if (!attr) {
-        PK_CHECK_CUDA(cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, DqSmem<DK>::BYTES));
-        PK_CHECK_CUDA(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, DkvSmem<DK>::BYTES));
-        attr = true;
-    }
-    const unsigned tiles = static_cast<unsigned>((p.S + AT_BM - 1) / AT_BM);
-    dim3 gq(tiles, p.Hq, static_cast<unsigned>(B));
-    kq<<<gq, AT_THREADS_TC, DqSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
-    PK_LAUNCH_CHECK();
-    dim3 gkv(tiles, p.Hkv, static_cast<unsigned>(B));
-    kkv<<<gkv, AT_THREADS_TC, DkvSmem<DK>::BYTES, st>>>(mq, mk, mv, mdo, p);
-    PK_LAUNCH_CHECK();
-    return PK_OK;
-}
-
 // ---- entry points used by the dispatcher in pk_attn_simt.cu ------------------------------
 int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
                       int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S) {
@@ -777,38 +378,6 @@ int attn_tc_fwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int6
     return dk == 64 ? launch_fwd<64>(st, mq, mk, mv, p, B) : launch_fwd<128>(st, mq, mk, mv, p, B);
 }
 
-int attn_tc_bwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
-                const float* lse, const float* delta, const void* dout, int64_t lddo, void* dq, int64_t lddq,
-                void* dk_, int64_t lddk, void* dv, int64_t lddv, int64_t B, int64_t S, int Hq, int Hkv, int dk,
-                float scale, int causal) {
-    CUtensorMap mq, mk, mv, mdo;
-    const int64_t R = B * S;
-    int rc = make_tensor_map(&mq, q, static_cast<int64_t>(Hq) * dk, R, ldq, 64, AT_BM);
-    if (rc != PK_OK) return rc;
-    rc = make_tensor_map(&mk, k, static_cast<int64_t>(Hkv) * dk, R, ldk, 64, AT_BN);
-    if (rc != PK_OK) return rc;
-    rc = make_tensor_map(&mv, v, static_cast<int64_t>(Hkv) * dk, R, ldv, 64, AT_BN);
-    if (rc != PK_OK) return rc;
-    rc = make_tensor_map(&mdo, dout, static_cast<int64_t>(Hq) * dk, R, lddo, 64, AT_BM);
-    if (rc != PK_OK) return rc;
-    BwdParams p;
-    p.dq = static_cast<bf16*>(dq);
-    p.lddq = lddq;
-    p.dk = static_cast<bf16*>(dk_);
-    p.lddk = lddk;
-    p.dv = static_cast<bf16*>(dv);
-    p.lddv = lddv;
-    p.lse = lse;
-    p.delta = delta;
-    p.S = static_cast<int>(S);
-    p.Hq = Hq;
-    p.Hkv = Hkv;
-    p.scale = scale;
-    p.scale_log2 = scale * LOG2E;
-    p.causal = causal;
-    return dk == 64 ? launch_bwd<64>(st, mq, mk, mv, mdo, p, B) : launch_bwd<128>(st, mq, mk, mv, mdo, p, B);
-}
-
 }  // namespace pk
 
 extern "C" {
@@ -821,6 +390,10 @@ int pk_attn_tc_status(int* status_h, int clear) {
         const int zero = 0;
         PK_CHECK_CUDA(cudaMemcpyToSymbol(pk::g_attn_tc_status, &zero, sizeof(int)));
     }
+    int bwd = 0;  // the backward kernels (pk_attn_bwd_tc.cu) keep their own word
+    const int rc = pk::attn_bwd_tc_status(&bwd, clear);
+    if (rc != PK_OK) return rc;
+    *status_h |= bwd;
     return PK_OK;
 }
 
