@@ -74,7 +74,7 @@ def build_libpk(verbose: bool = False, force: bool = False, ptxas_info: bool = F
     for src in sorted(CSRC.glob("*.cu")):
         obj = OBJ / (src.stem + ".o")
         if force or not _newer(obj, [src, *headers]):
-            cmd = [nvcc, "-ccbin", cxx, *NVCC_FLAGS, "-c", src, "-o", obj]
+            cmd = [nvcc, "-ccbin", cxx, *NVCC_FLAGS, *os.environ.get("PK_NVCC_EXTRA", "").split(), "-c", src, "-o", obj]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)

@@ -27,6 +27,13 @@ namespace pk {
 
 __device__ int g_attn_bwd_tc_status = 0;
 
+#ifdef PK_ATTN_TIMING
+__device__ long long g_attn_dbg[64];
+#define PK_T(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 5 && (tid == 0 || tid == 200)) g_attn_dbg[(tid != 0) * 16 + (i)] = clock64(); } while (0)
+#else
+#define PK_T(i) do { } while (0)
+#endif
+
 using namespace tc;
 
 namespace {
@@ -171,8 +178,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_tile<DK>(sK0, &map_k, hk * DK, seq0, smem_u32(&bar_kv[0]), CH64);
         tma_tile<DK>(sV0, &map_v, hk * DK, seq0, smem_u32(&bar_kv[0]), CH64);
     }
-    const float lse2 = row_ok ? p.lse[(seq0 + qi) * p.Hq + h] * LOG2E_ : 0.0f;
-    const float delta = row_ok ? p.delta[(seq0 + qi) * p.Hq + h] : 0.0f;
+    // rows past the end of the sequence get lse = +inf, i.e. p = 0 everywhere
+    const float neg_lse2 = row_ok ? -p.lse[(seq0 + qi) * p.Hq + h] * LOG2E_ : -INFINITY;
+    const float neg_delta_s = row_ok ? -p.delta[(seq0 + qi) * p.Hq + h] * p.scale : 0.0f;
     const uint32_t idesc_s = idesc_bf16(BW_COLS, 0, 0);
     const uint32_t idesc_q = idesc_bf16(DK, 0, 1);
     bool ok = true;
@@ -181,6 +189,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int st = NST == 2 ? (j & 1) : 0;
         const uint32_t kv_phase = NST == 2 ? ((j >> 1) & 1) : (j & 1);
         const int kv0 = j * BW_COLS;
+        PK_T(0);
         if (tid == 0) {
             if (NST == 1 && j > 0) {  // the single K/V stage is free once dQ of tile j-1 is done
                 ok = ok && mbar_wait(smem_u32(bar_d), (j - 1) & 1, abort_flag, &g_attn_bwd_tc_status);
@@ -193,6 +202,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (ok && j == 0) ok = mbar_wait(smem_u32(bar_q), 0, abort_flag, &g_attn_bwd_tc_status);
             if (ok) ok = mbar_wait(smem_u32(&bar_kv[st]), kv_phase, abort_flag, &g_attn_bwd_tc_status);
             if (ok) {
+                PK_T(1);
                 fence_after();
                 const uint32_t sK = sK0 + st * L::TILEK, sV = sV0 + st * L::TILEK;
 #pragma unroll
@@ -202,9 +212,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int k = 0; k < DK / 16; ++k)
                     mma_bf16(tmem + 64, dk_major(sDO, k, CH128), dk_major(sV, k, CH64), idesc_s, k > 0 ? 1u : 0u);
                 commit(smem_u32(bar_s));
+                PK_T(2);
             }
         }
         if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_bwd_tc_status)) ok = false;
+        PK_T(3);
         // S_j complete implies dQ of tile j-1 (issued earlier on the same pipe) is complete:
         // the dS buffer and, with two stages, the other K/V stage are free again.
         fence_after();
@@ -221,22 +233,28 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tmem_ld32(t_s, rs);
             tmem_ld32(t_dp, rd);
             tmem_wait_ld();
+            PK_T(4);
+            // per element: p = 2^(s*c - lse2) (FFMA + MUFU), ds = p * (dp*scale - delta*scale) (FFMA + FMUL)
             float dsv[32];
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-                bool vis = row_ok;
-                if (need_mask) vis = vis && key0 + e < p.S && (!p.causal || key0 + e <= qi);
-                const float pe = vis ? exp2f(__uint_as_float(rs[e]) * p.scale_log2 - lse2) : 0.0f;
-                dsv[e] = pe * (__uint_as_float(rd[e]) - delta) * p.scale;
+                float pe = ex2_approx(fmaf(__uint_as_float(rs[e]), p.scale_log2, neg_lse2));
+                if (need_mask) {
+                    const bool vis = key0 + e < p.S && (!p.causal || key0 + e <= qi);
+                    pe = vis ? pe : 0.0f;
+                }
+                dsv[e] = pe * fmaf(__uint_as_float(rd[e]), p.scale, neg_delta_s);
             }
             st32_bf16(pDS, row, hf * 4, dsv);
         }
+        PK_T(5);
         fence_async_smem();
         fence_before();
         if (__syncthreads_or(!ok)) {  // CTA-uniform exit as soon as any thread's wait gave up
             ok = false;
             break;
         }
+        PK_T(6);
         if (tid == 0) {
             fence_after();
             const uint32_t sK = sK0 + st * L::TILEK;
@@ -244,6 +262,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int k = 0; k < BW_COLS / 16; ++k)
                 mma_bf16(t_dq, dk_major(sDS, k, CH128), dmn_major(sK, k, CH64), idesc_q, (j > 0 || k > 0) ? 1u : 0u);
             commit(smem_u32(bar_d));
+            PK_T(7);
         }
     }
     if (ok) ok = mbar_wait(smem_u32(bar_d), (nkv - 1) & 1, abort_flag, &g_attn_bwd_tc_status);
@@ -323,8 +342,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (tid < 128) {
             const int c = tid & 63;
             const int q = q0 + c;
-            float v = 0.0f;
-            if (q < p.S) v = tid < 64 ? p.lse[(seq0 + q) * p.Hq + h] * LOG2E_ : p.delta[(seq0 + q) * p.Hq + h];
+            // -lse*log2(e) (queries past the end: -inf, so that p = 0) and -delta*scale
+            float v = tid < 64 ? -INFINITY : 0.0f;
+            if (q < p.S)
+                v = tid < 64 ? -p.lse[(seq0 + q) * p.Hq + h] * LOG2E_ : -p.delta[(seq0 + q) * p.Hq + h] * p.scale;
             xb[buf * 128 + (tid < 64 ? 0 : 64) + c] = v;
         }
     };
@@ -425,10 +446,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                 for (int e8 = 0; e8 < 8; ++e8) {
                     const int e = g * 8 + e8;
-                    bool vis = true;
-                    if (need_mask) vis = key_ok && qc0 + e < p.S && (!p.causal || kj <= qc0 + e);
-                    pe[e8] = vis ? exp2f(__uint_as_float(rs[e]) * p.scale_log2 - xs[e]) : 0.0f;
-                    de[e8] = pe[e8] * (__uint_as_float(rd[e]) - xs[64 + e]) * p.scale;
+                    float pq = ex2_approx(fmaf(__uint_as_float(rs[e]), p.scale_log2, xs[e]));
+                    if (need_mask) {
+                        const bool vis = key_ok && (!p.causal || kj <= qc0 + e);
+                        pq = vis ? pq : 0.0f;
+                    }
+                    pe[e8] = pq;
+                    de[e8] = pq * fmaf(__uint_as_float(rd[e]), p.scale, xs[64 + e]);
                 }
                 uint4 wp, wd;
                 wp.x = pack2(pe[0], pe[1]); wp.y = pack2(pe[2], pe[3]); wp.z = pack2(pe[4], pe[5]); wp.w = pack2(pe[6], pe[7]);
@@ -552,5 +576,12 @@ int attn_bwd_tc_status(int* status_h, int clear) {
     }
     return PK_OK;
 }
+
+#ifdef PK_ATTN_TIMING
+extern "C" int pk_debug_read(long long* out_h) {
+    cudaDeviceSynchronize();
+    return cudaMemcpyFromSymbol(out_h, g_attn_dbg, sizeof(long long) * 64) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 }  // namespace pk

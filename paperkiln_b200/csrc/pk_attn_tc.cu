@@ -256,13 +256,14 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float corr = m == -INFINITY ? 0.0f : exp2f(m - m_new);
         // m_new is finite for every tile a row takes part in (its diagonal key is visible)
         float sum = 0.0f;
+        const float neg_m = -m_new;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {  // 8 keys -> one 16-byte unit of the P operand tile
             float pe[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const uint32_t raw = g < 4 ? r0[g * 8 + e] : r1[(g - 4) * 8 + e];
-                pe[e] = exp2f(__uint_as_float(raw) * p.scale_log2 - m_new);
+                pe[e] = ex2_approx(fmaf(__uint_as_float(raw), p.scale_log2, neg_m));  // FFMA + MUFU
                 sum += pe[e];
             }
             uint4 w;
