@@ -12,7 +12,7 @@ namespace pk {
 
 int gemm_tc_supported(int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A,
                       int64_t lda, const void* B, int64_t ldb, const void* C, int64_t ldc,
-                      const void* residual, int64_t ldr);
+                      const void* residual, int64_t ldr, const float* bias);
 int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K,
                    const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
                    int accumulate, const float* bias, const void* residual, int64_t ldr);
@@ -150,7 +150,7 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
     PK_REQUIRE(!(ab_dtype == PK_F32 && c_dtype == PK_BF16), "fp32 operands with bf16 output are not provided");
     cudaStream_t st = as_stream(stream);
     if (ab_dtype == PK_BF16 && !g_force_simt &&
-        gemm_tc_supported(c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, residual, ldr)) {
+        gemm_tc_supported(c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, residual, ldr, bias)) {
         g_last_path = 2;
         ProfScope prof(PROF_GEMM_TC, 2.0 * M * N * K, st);
         return gemm_tc_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate,

@@ -323,7 +323,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const int64_t c = c0 + g * 8;
-                        if (c < p.N) {
+                        if (c < p.N && c + 8 > p.N) {
+                            // ragged last group (N not a multiple of 8): element by element
+                            for (int e = 0; e < 8 && c + e < p.N; ++e) {
+                                float x = __uint_as_float(r[g * 8 + e]);
+                                if (p.bias) x += p.bias[c + e];
+                                if (Rsd) x += to_f32(Rsd[m * p.ldr + c + e]);
+                                if (p.accumulate) x += to_f32(C[m * p.ldc + c + e]);
+                                C[m * p.ldc + c + e] = from_f32<TC>(x);
+                            }
+                        } else if (c < p.N) {
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]);
@@ -409,13 +418,16 @@ static int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t o
 
 int gemm_tc_supported(int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A,
                       int64_t lda, const void* B, int64_t ldb, const void* C, int64_t ldc,
-                      const void* residual, int64_t ldr) {
+                      const void* residual, int64_t ldr, const float* bias) {
     (void)c_dtype; (void)ta; (void)tb;
+    const bool bias_unaligned = bias != nullptr && !aligned16(bias);
+    // TMA needs 16-byte aligned bases and row strides; the extents themselves may be ragged
+    // (out-of-range parts of a box are filled with zeros, the epilogue guards rows/columns).
     if (M < 1 || N < 1 || K < 1) return 0;
-    if (M % 8 || N % 8 || K % 8) return 0;
     if (lda % 8 || ldb % 8 || ldc % 8) return 0;
     if (!aligned16(A) || !aligned16(B) || !aligned16(C)) return 0;
     if (residual && (!aligned16(residual) || ldr % 8)) return 0;
+    if (bias_unaligned) return 0;
     if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) return 0;
     return 1;
 }

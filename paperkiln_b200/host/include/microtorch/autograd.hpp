@@ -108,8 +108,11 @@ public:
     // Gradient buffer to accumulate into in place (allocated and zeroed on first use).
     Tensor& grad_for_accumulate();
 
-    // Tensor of `data` in the compute dtype (cached cast for fp32 leaves in bf16 mode).
+    // Tensor of `data` in the compute dtype (cached cast for fp32 leaves in bf16 mode),
+    // with packed rows.
     const Tensor& compute() const;
+    // Same, but a padded row stride is kept (for consumers that take a leading dimension).
+    const Tensor& compute_strided() const;
     // bf16 shadow slot that the optimizer refreshes in the same pass as the fp32 master.
     Tensor shadow;
     uint64_t shadow_version = ~uint64_t(0);

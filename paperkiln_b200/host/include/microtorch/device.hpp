@@ -92,6 +92,11 @@ class Tensor {
 public:
     Tensor() = default;
     static Tensor empty(size_t rows, size_t cols, DType dt, device::Pool pool = device::Pool::Activation);
+    // Rows `ld` elements apart (ld >= cols). Only GEMM outputs use a padded row stride (a
+    // row stride that is a multiple of 16 bytes lets the tensor-core kernel write shapes
+    // such as a 50257-wide vocabulary); every other consumer sees dense().
+    static Tensor empty_strided(size_t rows, size_t cols, size_t ld, DType dt,
+                                device::Pool pool = device::Pool::Activation);
     static Tensor zeros(size_t rows, size_t cols, DType dt, device::Pool pool = device::Pool::Activation);
     static Tensor from_host(const Matrix& m, DType dt = DType::F32, device::Pool pool = device::Pool::Activation);
     // Raw byte buffer (scratch, index arrays): rows = 1, cols = bytes, dtype tag F32 unused.
@@ -101,7 +106,11 @@ public:
     size_t rows() const { return rows_; }
     size_t cols() const { return cols_; }
     size_t numel() const { return rows_ * cols_; }
-    size_t nbytes() const { return numel() * dtype_bytes(dt_); }
+    size_t ld() const { return ld_ ? ld_ : cols_; }
+    bool is_dense() const { return ld() == cols_; }
+    // bytes spanned in memory (rows * ld)
+    size_t nbytes() const { return rows_ * ld() * dtype_bytes(dt_); }
+    Tensor dense() const;  // *this when dense, else a packed copy
     DType dtype() const { return dt_; }
     int dt() const { return static_cast<int>(dt_); }
     void* ptr() const { return st_ ? static_cast<char*>(st_->ptr) + off_ : nullptr; }
@@ -120,7 +129,7 @@ public:
 private:
     std::shared_ptr<Storage> st_;
     size_t off_ = 0;  // bytes
-    size_t rows_ = 0, cols_ = 0;
+    size_t rows_ = 0, cols_ = 0, ld_ = 0;  // ld_ == 0: dense
     DType dt_ = DType::F32;
 };
 

@@ -98,6 +98,11 @@ DType Variable::grad_dtype() const { return is_param ? DType::F32 : device::comp
 
 const Tensor& Variable::compute() const {
     const DType want = device::compute_dtype();
+    if (!data.device().is_dense()) {
+        // a GEMM output with a padded row stride meets a consumer that wants packed rows
+        Variable* self = const_cast<Variable*>(this);
+        self->data.set_device(data.device().dense());
+    }
     const Tensor& d = data.device();
     if (d.dtype() == want) return d;
     Variable* self = const_cast<Variable*>(this);
@@ -112,6 +117,12 @@ const Tensor& Variable::compute() const {
         self->shadow_version = data.version();
     }
     return shadow;
+}
+
+const Tensor& Variable::compute_strided() const {
+    const Tensor& d = data.device();
+    if (d.dtype() == device::compute_dtype()) return d;
+    return compute();
 }
 
 Tensor& Variable::grad_for_accumulate() {
@@ -134,6 +145,13 @@ void Variable::accumulate(const Tensor& g) {
     void* s = device::stream();
     if (grad.empty() && !grad_home.defined() && g.dtype() == want) {
         grad.set_device(g);  // adopt: no copy, no add
+        return;
+    }
+    if (!g.is_dense() || (!grad.empty() && !grad.device().is_dense())) {
+        // element-wise sums need packed rows on both sides
+        const Tensor gd = g.dense();
+        if (!grad.empty() && !grad.device().is_dense()) grad.set_device(grad.device().dense());
+        accumulate(gd);
         return;
     }
     if (grad.empty()) {

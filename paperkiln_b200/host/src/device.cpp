@@ -195,6 +195,23 @@ Tensor Tensor::empty(size_t rows, size_t cols, DType dt, device::Pool pool) {
     return t;
 }
 
+Tensor Tensor::empty_strided(size_t rows, size_t cols, size_t ld, DType dt, device::Pool pool) {
+    if (ld < cols) throw std::runtime_error("Tensor::empty_strided: ld < cols");
+    Tensor t = empty(rows, ld, dt, pool);
+    t.cols_ = cols;
+    t.ld_ = ld == cols ? 0 : ld;
+    return t;
+}
+
+Tensor Tensor::dense() const {
+    if (is_dense()) return *this;
+    Tensor t = empty(rows_, cols_, dt_);
+    device::check(pk_copy_cols(device::stream(), dt(), ptr(), static_cast<int64_t>(ld()), 0, t.ptr(),
+                               static_cast<int64_t>(cols_), 0, static_cast<int64_t>(rows_),
+                               static_cast<int64_t>(cols_), 0), "pk_copy_cols");
+    return t;
+}
+
 Tensor Tensor::zeros(size_t rows, size_t cols, DType dt, device::Pool pool) {
     Tensor t = empty(rows, cols, dt, pool);
     t.zero_();
@@ -211,6 +228,7 @@ Tensor Tensor::from_host(const Matrix& m, DType dt, device::Pool pool) {
 
 Tensor Tensor::view(size_t elem_offset, size_t rows, size_t cols) const {
     if (!st_) throw std::runtime_error("Tensor::view on an undefined tensor");
+    if (!is_dense()) throw std::runtime_error("Tensor::view on a strided tensor");
     const size_t end = off_ + (elem_offset + rows * cols) * dtype_bytes(dt_);
     if (end > st_->bytes) throw std::runtime_error("Tensor::view exceeds the storage");
     Tensor t = *this;
@@ -221,6 +239,7 @@ Tensor Tensor::view(size_t elem_offset, size_t rows, size_t cols) const {
 }
 
 Tensor Tensor::reshape(size_t rows, size_t cols) const {
+    if (!is_dense()) throw std::runtime_error("Tensor::reshape on a strided tensor");
     if (rows * cols != numel()) throw std::runtime_error("Tensor::reshape changes the element count");
     Tensor t = *this;
     t.rows_ = rows;
@@ -228,14 +247,15 @@ Tensor Tensor::reshape(size_t rows, size_t cols) const {
     return t;
 }
 
-Tensor Tensor::clone() const {
-    Tensor t = empty(rows_, cols_, dt_);
+Tensor Tensor::clone() const {  // keeps the row stride
+    Tensor t = empty_strided(rows_, cols_, ld(), dt_);
     device::check(pk_memcpy_d2d(t.ptr(), ptr(), nbytes(), device::stream()), "pk_memcpy_d2d");
     return t;
 }
 
 Tensor Tensor::cast(DType dt) const {
     if (dt == dt_) return *this;
+    if (!is_dense()) return dense().cast(dt);
     Tensor t = empty(rows_, cols_, dt);
     device::check(pk_cast(device::stream(), this->dt(), ptr(), t.dt(), t.ptr(), static_cast<int64_t>(numel())), "pk_cast");
     return t;
@@ -247,6 +267,7 @@ void Tensor::zero_() {
 
 void Tensor::copy_from_host(const Matrix& m) {
     if (m.rows() != rows_ || m.cols() != cols_) throw std::runtime_error("Tensor::copy_from_host: shape mismatch");
+    if (!is_dense()) throw std::runtime_error("Tensor::copy_from_host on a strided tensor");
     if (numel() == 0) return;
     void* s = device::stream();
     if (dt_ == DType::F32) {
@@ -261,6 +282,7 @@ void Tensor::copy_from_host(const Matrix& m) {
 }
 
 Matrix Tensor::to_host() const {
+    if (!is_dense()) return dense().to_host();
     Matrix m(rows_, cols_);
     if (numel() == 0) return m;
     void* s = device::stream();

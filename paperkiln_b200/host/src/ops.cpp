@@ -64,9 +64,9 @@ void gemm(const Tensor& A, bool ta, const Tensor& B, bool tb, Tensor& C, bool ac
           const float* bias = nullptr, const Tensor* residual = nullptr) {
     const int64_t M = i64(ta ? A.cols() : A.rows()), K = i64(ta ? A.rows() : A.cols());
     const int64_t N = i64(tb ? B.rows() : B.cols());
-    check(pk_gemm(S(), A.dt(), C.dt(), ta, tb, M, N, K, A.ptr(), i64(A.cols()), B.ptr(), i64(B.cols()), C.ptr(),
-                  i64(C.cols()), accumulate ? 1 : 0, bias, residual ? residual->ptr() : nullptr,
-                  residual ? i64(residual->cols()) : 0),
+    check(pk_gemm(S(), A.dt(), C.dt(), ta, tb, M, N, K, A.ptr(), i64(A.ld()), B.ptr(), i64(B.ld()), C.ptr(),
+                  i64(C.ld()), accumulate ? 1 : 0, bias, residual ? residual->ptr() : nullptr,
+                  residual ? i64(residual->ld()) : 0),
           "pk_gemm");
 }
 
@@ -348,7 +348,10 @@ Var linear(const Var& x, const Var& W, const Var& bias, const Var& residual, boo
         throw std::runtime_error("linear: residual shape mismatch");
     const Tensor& xt = x->compute();
     const Tensor& wt = W->compute();
-    Tensor y = new_act(xt.rows(), out);
+    // A row stride that is a multiple of 16 bytes keeps ragged widths (a 50257-wide
+    // vocabulary) on the tensor-core kernel.
+    Tensor y = (cdt() == DType::BF16 && out % 8 != 0) ? Tensor::empty_strided(xt.rows(), out, (out + 7) / 8 * 8, cdt())
+                                                      : new_act(xt.rows(), out);
     Tensor bt;
     if (bias) bt = f32_of(bias);
     Tensor rt;
@@ -368,15 +371,16 @@ Var linear(const Var& x, const Var& W, const Var& bias, const Var& residual, boo
         if (has_bias) {
             const Var& b = self->parents[idx++];
             if (b->requires_grad) {
-                Tensor scratch = Tensor::bytes(pk_colsum_scratch_bytes(i64(g.rows()), i64(g.cols())));
+                const Tensor gd = g.dense();
+                Tensor scratch = Tensor::bytes(pk_colsum_scratch_bytes(i64(gd.rows()), i64(gd.cols())));
                 into_f32_grad(b, [&](float* dst) {
-                    check(pk_colsum(S(), g.dt(), g.ptr(), dst, scratch.ptr(), i64(g.rows()), i64(g.cols())), "pk_colsum");
+                    check(pk_colsum(S(), gd.dt(), gd.ptr(), dst, scratch.ptr(), i64(gd.rows()), i64(gd.cols())), "pk_colsum");
                 });
             }
         }
         if (has_res) {
             const Var& r = self->parents[idx++];
-            if (r->requires_grad) r->accumulate(g);
+            if (r->requires_grad) r->accumulate(g.dense());
         }
     });
 }
@@ -644,13 +648,13 @@ Var cross_entropy(const Var& logits, const std::vector<int>& targets) {
     if (targets.size() != R) throw std::runtime_error("cross_entropy: one target per row");
     for (int t : targets)
         if (t < 0 || static_cast<size_t>(t) >= C) throw std::runtime_error("cross_entropy: target out of range");
-    const Tensor& lt = logits->compute();
+    const Tensor& lt = logits->compute_strided();
     Tensor dt = device_ints(targets);
     const bool want = grad_enabled() && logits->requires_grad;
     // The kernel writes (softmax - onehot)/R over its input, so a training step works on a copy.
     Tensor work = want ? lt.clone() : lt;
     Tensor rows = Tensor::empty(1, R, DType::F32);
-    check(pk_cross_entropy(S(), work.dt(), work.ptr(), i64(C), static_cast<const int32_t*>(dt.ptr()), rows.f32(), i64(R),
+    check(pk_cross_entropy(S(), work.dt(), work.ptr(), i64(work.ld()), static_cast<const int32_t*>(dt.ptr()), rows.f32(), i64(R),
                            i64(C), 1.0f / static_cast<float>(R), want ? 1 : 0, nullptr),
           "pk_cross_entropy");
     Tensor sum = Tensor::bytes(8), scratch = Tensor::bytes(pk_reduce_scratch_bytes());
@@ -662,7 +666,8 @@ Var cross_entropy(const Var& logits, const std::vector<int>& targets) {
         if (!l->requires_grad) return;
         const float g = self->grad(0, 0);  // the seed is host-known: no readback in the common case
         Tensor dl = work;
-        if (g != 1.0f) check(pk_scale(S(), dl.dt(), dl.ptr(), g, dl.ptr(), i64(dl.numel())), "pk_scale");
+        if (g != 1.0f)  // padding columns of a strided buffer hold zeros and stay zero
+            check(pk_scale(S(), dl.dt(), dl.ptr(), g, dl.ptr(), i64(dl.rows() * dl.ld())), "pk_scale");
         l->accumulate(dl);
     });
 }

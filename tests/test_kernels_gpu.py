@@ -308,6 +308,36 @@ def test_gemm_bf16_tensor_core(pk, ta, tb, mnk):
     assert torch.equal(C, C3)
 
 
+@pytest.mark.parametrize("ta,tb", [(False, True), (False, False), (True, False)])
+@pytest.mark.parametrize("mnk", [(130, 97, 70), (257, 50257 // 64, 100), (64, 1003, 48)])
+def test_gemm_bf16_tensor_core_ragged(pk, ta, tb, mnk):
+    """Extents that are not multiples of 8 (a 50257-wide vocabulary) stay on the tensor-core
+    kernel as long as the row strides are multiples of 16 bytes."""
+    M, N, K = mnk
+    bf = torch.bfloat16
+
+    def padded(rows, cols, seed, dtype=bf):
+        ld = (cols + 7) // 8 * 8
+        buf = torch.full((rows, ld), float("nan"), dtype=dtype, device="cuda")
+        buf[:, :cols] = rnd(rows, cols, seed=seed, lo=-1, hi=1, dtype=dtype)
+        return buf[:, :cols]
+
+    A = padded(K, M, 1) if ta else padded(M, K, 1)
+    B = padded(N, K, 2) if tb else padded(K, N, 2)
+    ref = (A.t() if ta else A).float() @ (B.t() if tb else B).float()
+    C = padded(M, N, 3, dtype=torch.float32)
+    C0 = C.clone()
+    pkt.gemm(A, B, ta=ta, tb=tb, C=C, accumulate=True)
+    assert pk.pk_gemm_last_path() == 2, "tensor-core kernel was not selected"
+    close(C, ref + C0, 2e-3 * math.sqrt(max(K, 64) / 64), 1e-3)
+    Cb = padded(M, N, 4)
+    pkt.gemm(A, B, ta=ta, tb=tb, C=Cb)
+    close(Cb, ref, 3e-2, 2 ** -7)
+    st = ctypes.c_int(0)
+    pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
+    assert st.value == 0
+
+
 def attn_ref(q, k, v, B, S, Hq, Hkv, dk, scale, causal):
     """fp32 restatement of ops::fused_attention per head (src/ops.cpp:863-934)."""
     q = q.float().view(B, S, Hq, dk).transpose(1, 2)
