@@ -31,6 +31,16 @@
 namespace pk {
 
 __device__ int g_attn_tc_status = 0;
+#ifdef PK_ATTN_TIMING
+__device__ long long g_attn_fwd_dbg[64];
+#define PK_TF(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 5 && (tid == 0 || tid == 200)) g_attn_fwd_dbg[(tid != 0) * 16 + (i)] = clock64(); } while (0)
+extern "C" int pk_debug_read_fwd(long long* out_h) {
+    cudaDeviceSynchronize();
+    return cudaMemcpyFromSymbol(out_h, g_attn_fwd_dbg, sizeof(long long) * 64) == cudaSuccess ? 0 : 2;
+}
+#else
+#define PK_TF(i) do { } while (0)
+#endif
 int attn_bwd_tc_status(int* status_h, int clear);  // pk_attn_bwd_tc.cu
 
 namespace tc {
@@ -194,12 +204,6 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t sP = smem_u32(smem + L::OFF_P);
     uint8_t* pP = smem + L::OFF_P + hf * CHUNK_BYTES;  // 64 keys = one chunk per half
 
-    if (tid == 0) {
-        mbar_expect_tx(smem_u32(bar_q), L::TILE);
-        load_tile_tma<DK>(sQ, &map_q, h * DK, seq0 + q0, smem_u32(bar_q));
-        mbar_expect_tx(smem_u32(&bar_k[0]), L::TILE);
-        load_tile_tma<DK>(sK0, &map_k, hk * DK, seq0, smem_u32(&bar_k[0]));
-    }
     const uint32_t idesc_s = idesc_bf16(AT_BN, 0, 0);
     const uint32_t idesc_o = idesc_bf16(DK, 0, 1);
 
@@ -209,34 +213,49 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     float m = -INFINITY, l = 0.0f;  // l: partial row sum over this thread's columns
     bool ok = true;
 
-    for (int j = 0; j < nkv && ok; ++j) {
-        const int st = j & 1;
+    // S of tile t: issued one tile ahead of its softmax, so that it runs on the tensor pipe
+    // while the CTA is still busy with tile t-1 (only thread 0 calls this).
+    auto issue_s = [&](int t) {
+        const int st = t & 1;
+        if (ok) ok = mbar_wait(smem_u32(&bar_k[st]), (t >> 1) & 1, abort_flag, &g_attn_tc_status);
+        if (!ok) return;
+        fence_after();
+        const uint32_t sK = sK0 + st * L::TILE;
+#pragma unroll
+        for (int k = 0; k < DK / 16; ++k)
+            mma_bf16(tmem, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
+        commit(smem_u32(bar_s));
+    };
+    auto load_k = [&](int t) {  // K of tile t into buffer t & 1
+        mbar_expect_tx(smem_u32(&bar_k[t & 1]), L::TILE);
+        load_tile_tma<DK>(sK0 + (t & 1) * L::TILE, &map_k, hk * DK, seq0 + static_cast<int64_t>(t) * AT_BN, smem_u32(&bar_k[t & 1]));
+    };
+    if (tid == 0) {
+        mbar_expect_tx(smem_u32(bar_q), L::TILE);
+        load_tile_tma<DK>(sQ, &map_q, h * DK, seq0 + q0, smem_u32(bar_q));
+        load_k(0);
+        if (nkv > 1) load_k(1);
+        ok = mbar_wait(smem_u32(bar_q), 0, abort_flag, &g_attn_tc_status);
+        issue_s(0);
+    }
+
+    for (int j = 0; j < nkv; ++j) {
         const int kv0 = j * AT_BN;
+        PK_TF(0);
         if (tid == 0) {
             // V_j: the single V buffer is free, P.V of the previous tile was waited for below
             mbar_expect_tx(smem_u32(bar_v), L::TILE);
             load_tile_tma<DK>(sV, &map_v, hk * DK, seq0 + kv0, smem_u32(bar_v));
-            if (j == 0) ok = mbar_wait(smem_u32(bar_q), 0, abort_flag, &g_attn_tc_status);
-            if (ok) ok = mbar_wait(smem_u32(&bar_k[st]), (j >> 1) & 1, abort_flag, &g_attn_tc_status);
-            if (ok) {
-                fence_after();
-                const uint32_t sK = sK0 + st * L::TILE;
-#pragma unroll
-                for (int k = 0; k < DK / 16; ++k)
-                    mma_bf16(tmem, desc_kmajor(sQ, k), desc_kmajor(sK, k), idesc_s, k > 0 ? 1u : 0u);
-                commit(smem_u32(bar_s));
-                if (j + 1 < nkv) {  // prefetch K_{j+1}; its buffer was last read by S of tile j-1
-                    mbar_expect_tx(smem_u32(&bar_k[st ^ 1]), L::TILE);
-                    load_tile_tma<DK>(sK0 + (st ^ 1) * L::TILE, &map_k, hk * DK, seq0 + kv0 + AT_BN, smem_u32(&bar_k[st ^ 1]));
-                }
-            }
+            PK_TF(1);
         }
         if (!mbar_wait(smem_u32(bar_s), j & 1, abort_flag, &g_attn_tc_status)) ok = false;
+        PK_TF(2);
         fence_after();
         uint32_t r0[32], r1[32];
         tmem_ld32(t_s, r0);
         tmem_ld32(t_s + 32, r1);
         tmem_wait_ld();
+        PK_TF(3);
         const bool need_mask = (p.causal && kv0 + AT_BN - 1 > q0) || (kv0 + AT_BN > p.S);
         if (need_mask) {
             const int key0 = kv0 + hf * 64;
@@ -251,6 +270,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
         xch[hf * 128 + row] = mx;
         pair_sync(quad);
+        PK_TF(4);
         mx = fmaxf(mx, xch[(hf ^ 1) * 128 + row]);
         const float m_new = fmaxf(m, mx * p.scale_log2);
         const float corr = m == -INFINITY ? 0.0f : exp2f(m - m_new);
@@ -274,6 +294,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             st_swizzled(pP, row, g, w);
         }
         l = l * corr + sum;
+        PK_TF(5);
         fence_async_smem();
         fence_before();
         if (__syncthreads_or(!ok)) {  // CTA-uniform exit as soon as any thread's wait gave up
@@ -288,9 +309,15 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int k = 0; k < AT_BN / 16; ++k)
                     mma_bf16(tmem + 128, desc_kmajor(sP, k), desc_mnmajor(sV, k), idesc_o, k > 0 ? 1u : 0u);
                 commit(smem_u32(bar_o));
+                if (j + 1 < nkv) {
+                    issue_s(j + 1);                   // S of tile j was consumed before the barrier above
+                    if (ok && j + 2 < nkv) load_k(j + 2);  // its buffer held K_j, read by S_j (complete)
+                }
+                PK_TF(6);
             }
         }
         if (!mbar_wait(smem_u32(bar_o), j & 1, abort_flag, &g_attn_tc_status)) ok = false;
+        PK_TF(7);
         fence_after();
 #pragma unroll
         for (int ch = 0; ch < OH / 32; ++ch) {
@@ -301,6 +328,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int e = 0; e < 32; ++e) o[ch * 32 + e] = o[ch * 32 + e] * corr + __uint_as_float(r[e]);
         }
         m = m_new;
+        PK_TF(8);
     }
 
     // total row sum = the two halves' partial sums
