@@ -40,6 +40,10 @@ int mt_sync(void);
 int mt_model_create(const char* spec, void** model_h);
 int mt_model_destroy(void* model);
 int mt_model_set_checkpoint(void* model, int on);
+/* rows > 0: the vocabulary projection and the cross entropy run fused over chunks of that many
+ * rows, so the [tokens, vocab] logits never exist as a whole (default 8192). rows = 0: the two
+ * separate ops of the reference (src/llama.cpp:85-88 then src/ops.cpp:350-376). */
+int mt_model_set_loss_chunk(void* model, int64_t rows);
 
 int mt_model_num_params(void* model, int64_t* n_h);
 int mt_model_param_info(void* model, int64_t index, char* name_h, size_t cap, int64_t* rows_h, int64_t* cols_h);

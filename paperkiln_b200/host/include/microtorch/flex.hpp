@@ -37,6 +37,10 @@ class FlexLM : public nn::Module {
 public:
     FlexLM(const FlexConfig& c, unsigned seed);
     Var forward(const std::vector<int>& ids, size_t seq_len = 0) const;
+    Var hidden(const std::vector<int>& ids, size_t seq_len = 0) const;  // final-norm output
+    // cross_entropy(forward(ids), targets) with the head and the loss fused over row chunks.
+    Var loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len = 0,
+             size_t chunk_rows = 8192) const;
 
     FlexConfig cfg;
     bool checkpoint_blocks = false;

@@ -30,11 +30,18 @@ struct Model {
     std::unique_ptr<nn::AdamW> opt;
     float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, wd = 0.01f;
     int64_t live_after_fwd = 0;
+    size_t loss_chunk = 8192;
 
     Var forward(const std::vector<int>& ids, size_t seq_len) const {
         if (llama) return llama->forward(ids, seq_len);
         if (gpt2) return gpt2->forward(ids, seq_len);
         return flex->forward(ids, seq_len);
+    }
+    Var loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len) const {
+        if (loss_chunk == 0) return ops::cross_entropy(forward(ids, seq_len), targets);
+        if (llama) return llama->loss(ids, targets, seq_len, loss_chunk);
+        if (gpt2) return gpt2->loss(ids, targets, seq_len, loss_chunk);
+        return flex->loss(ids, targets, seq_len, loss_chunk);
     }
     void set_ckpt(bool on) {
         if (llama) llama->checkpoint_blocks = on;
@@ -217,6 +224,12 @@ int mt_model_destroy(void* h) {
 int mt_model_set_checkpoint(void* h, int on) {
     return guard([&] { M(h)->set_ckpt(on != 0); });
 }
+int mt_model_set_loss_chunk(void* h, int64_t rows) {
+    return guard([&] {
+        if (rows < 0) throw std::runtime_error("negative chunk size");
+        M(h)->loss_chunk = static_cast<size_t>(rows);
+    });
+}
 int mt_model_num_params(void* h, int64_t* n) {
     return guard([&] { *n = static_cast<int64_t>(M(h)->named.size()); });
 }
@@ -273,17 +286,14 @@ int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64
         if (do_backward) {
             zero_grad(m->params);
             const size_t live0 = live_variables();
-            Var logits = m->forward(ids, static_cast<size_t>(seq_len));
-            Var loss = ops::cross_entropy(logits, targets);
-            logits.reset();
+            Var loss = m->loss(ids, targets, static_cast<size_t>(seq_len));
             m->live_after_fwd = static_cast<int64_t>(live_variables() - live0);
             Var root = loss_scale == 1.0f ? loss : ops::scale(loss, loss_scale);
             backward(root);
             loss_value = loss->data(0, 0);
         } else {
             NoGrad ng;
-            Var logits = m->forward(ids, static_cast<size_t>(seq_len));
-            Var loss = ops::cross_entropy(logits, targets);
+            Var loss = m->loss(ids, targets, static_cast<size_t>(seq_len));
             loss_value = loss->data(0, 0);
         }
         device::step_end();

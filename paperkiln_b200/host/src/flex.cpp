@@ -62,7 +62,7 @@ FlexLM::FlexLM(const FlexConfig& c, unsigned seed) : cfg(c) {
     head = mod<nn::Linear>("head", c.d, c.vocab, false, seed + 99);
 }
 
-Var FlexLM::forward(const std::vector<int>& ids, size_t seq_len) const {
+Var FlexLM::hidden(const std::vector<int>& ids, size_t seq_len) const {
     const size_t sl = seq_len == 0 ? ids.size() : seq_len;
     if (sl == 0 || ids.size() % sl != 0) throw std::runtime_error("ids not a multiple of seq_len");
     if (sl > cfg.n_ctx) throw std::runtime_error("sequence too long");
@@ -81,8 +81,14 @@ Var FlexLM::forward(const std::vector<int>& ids, size_t seq_len) const {
                 ? checkpoint([b, seq_len](const Var& in) { return b->forward(in, seq_len); }, h)
                 : b->forward(h, seq_len);
     }
-    Var n = ln_f_ln ? ln_f_ln->forward(h) : ops::rmsnorm(h, ln_f_w);
-    return head->forward(n);
+    return ln_f_ln ? ln_f_ln->forward(h) : ops::rmsnorm(h, ln_f_w);
+}
+
+Var FlexLM::forward(const std::vector<int>& ids, size_t seq_len) const { return head->forward(hidden(ids, seq_len)); }
+
+Var FlexLM::loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len, size_t chunk_rows) const {
+    if (head->b) return ops::cross_entropy(forward(ids, seq_len), targets);
+    return ops::linear_cross_entropy(hidden(ids, seq_len), head->W, false, targets, chunk_rows);
 }
 
 }  // namespace parity

@@ -86,7 +86,7 @@ Llama::Llama(const LlamaConfig& cfg_, unsigned seed) : cfg(cfg_) {
     if (!cfg.tie_embeddings && !cfg.qlora) lm_head = mod<Linear>("lm_head", cfg.d, cfg.vocab, false, seed + 12);
 }
 
-Var Llama::forward(const std::vector<int>& ids, size_t seq_len) const {
+Var Llama::hidden(const std::vector<int>& ids, size_t seq_len) const {
     const size_t sl = seq_len == 0 ? ids.size() : seq_len;
     if (sl == 0 || ids.size() % sl != 0) throw std::runtime_error("ids not a multiple of seq_len");
     std::vector<int> pos(ids.size());
@@ -98,11 +98,24 @@ Var Llama::forward(const std::vector<int>& ids, size_t seq_len) const {
                 ? checkpoint([b, pos, seq_len](const Var& in) { return b->forward(in, pos, seq_len); }, h)
                 : b->forward(h, pos, seq_len);
     }
-    h = ops::rmsnorm(h, norm_w);
+    return ops::rmsnorm(h, norm_w);
+}
+
+Var Llama::forward(const std::vector<int>& ids, size_t seq_len) const {
+    Var h = hidden(ids, seq_len);
     if (lm_head) return lm_head->forward(h);
     // Tied head: logits = h E^T; the embedding receives gradient from the gather and
     // from this GEMM (src/llama.cpp:85-88). No transposed copy of E is made.
+    const Var& table = cfg.qlora ? embed_frozen : embed_tokens->weight;
     return ops::linear(h, table, nullptr, nullptr, /*transposed_w=*/true);
+}
+
+Var Llama::loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len, size_t chunk_rows) const {
+    if (lm_head && lm_head->b) return ops::cross_entropy(forward(ids, seq_len), targets);
+    Var h = hidden(ids, seq_len);
+    if (lm_head) return ops::linear_cross_entropy(h, lm_head->W, false, targets, chunk_rows);
+    const Var& table = cfg.qlora ? embed_frozen : embed_tokens->weight;
+    return ops::linear_cross_entropy(h, table, true, targets, chunk_rows);
 }
 
 }  // namespace nn

@@ -188,7 +188,7 @@ GPT2::GPT2(const GPT2Config& c, unsigned seed) : cfg(c) {
     ln_f = mod<LayerNorm>("ln_f", cfg.d);
 }
 
-Var GPT2::forward(const std::vector<int>& ids, size_t seq_len) const {
+Var GPT2::hidden(const std::vector<int>& ids, size_t seq_len) const {
     const size_t sl = seq_len == 0 ? ids.size() : seq_len;
     if (sl > cfg.n_ctx) throw std::runtime_error("sequence too long");
     if (sl == 0 || ids.size() % sl != 0) throw std::runtime_error("ids not a multiple of seq_len");
@@ -200,8 +200,15 @@ Var GPT2::forward(const std::vector<int>& ids, size_t seq_len) const {
                 ? checkpoint([blk, seq_len](const Var& in) { return blk->forward(in, seq_len); }, x)
                 : blk->forward(x, seq_len);
     }
-    x = ln_f->forward(x);
-    return ops::linear(x, wte->weight, nullptr, nullptr, /*transposed_w=*/true);  // tied head: x wte^T
+    return ln_f->forward(x);
+}
+
+Var GPT2::forward(const std::vector<int>& ids, size_t seq_len) const {
+    return ops::linear(hidden(ids, seq_len), wte->weight, nullptr, nullptr, /*transposed_w=*/true);  // tied head: x wte^T
+}
+
+Var GPT2::loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len, size_t chunk_rows) const {
+    return ops::linear_cross_entropy(hidden(ids, seq_len), wte->weight, true, targets, chunk_rows);
 }
 
 // ---------------------------------------------------------------- optimizers

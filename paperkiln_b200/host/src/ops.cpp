@@ -672,6 +672,74 @@ Var cross_entropy(const Var& logits, const std::vector<int>& targets) {
     });
 }
 
+// cross_entropy(linear(h, W), targets) without ever holding the [rows, vocab] logits: the rows
+// are processed in chunks; each chunk's logits are produced, turned into (softmax - onehot)/R
+// in place, and immediately contracted into dh and dW. Same arithmetic per row as the two
+// separate ops (reference: src/ops.cpp:33-58 and 350-376); only the order in which rows are
+// visited differs, and dW sums chunk contributions in ascending chunk order.
+Var linear_cross_entropy(const Var& h, const Var& W, bool transposed_w, const std::vector<int>& targets,
+                         size_t chunk_rows) {
+    const size_t R = h->data.rows(), d = h->data.cols();
+    const size_t in = transposed_w ? W->data.cols() : W->data.rows();
+    const size_t V = transposed_w ? W->data.rows() : W->data.cols();
+    if (d != in) throw std::runtime_error("matmul: inner dimensions disagree");
+    if (targets.size() != R) throw std::runtime_error("cross_entropy: one target per row");
+    for (int t : targets)
+        if (t < 0 || static_cast<size_t>(t) >= V) throw std::runtime_error("cross_entropy: target out of range");
+    if (chunk_rows == 0) chunk_rows = 8192;
+    const Tensor& ht = h->compute();
+    const Tensor& wt = W->compute();
+    Tensor dtg = device_ints(targets);
+    const bool want_h = grad_enabled() && h->requires_grad, want_w = grad_enabled() && W->requires_grad;
+    const bool want = want_h || want_w;
+    Tensor rows = Tensor::empty(1, R, DType::F32);
+    Tensor dh, dw;
+    if (want_h) dh = new_act(R, d);
+    if (want_w) dw = Tensor::zeros(W->data.rows(), W->data.cols(), DType::F32);
+    const size_t ldl = cdt() == DType::BF16 ? (V + 7) / 8 * 8 : V;
+    for (size_t r0 = 0; r0 < R; r0 += chunk_rows) {
+        const size_t rc = std::min(chunk_rows, R - r0);
+        Tensor hc = ht.view(r0 * d, rc, d);
+        Tensor logits = Tensor::empty_strided(rc, V, ldl, cdt());
+        gemm(hc, false, wt, transposed_w, logits, false);
+        check(pk_cross_entropy(S(), logits.dt(), logits.ptr(), i64(ldl), static_cast<const int32_t*>(dtg.ptr()) + r0,
+                               rows.f32() + r0, i64(rc), i64(V), 1.0f / static_cast<float>(R), want ? 1 : 0, nullptr),
+              "pk_cross_entropy");
+        if (want_h) {  // dh = dlogits W^T   ([in,out] storage)  or  dlogits W   ([out,in] storage)
+            Tensor dhc = dh.view(r0 * d, rc, d);
+            gemm(logits, false, wt, !transposed_w, dhc, false);
+        }
+        if (want_w) {
+            if (!transposed_w) gemm(hc, true, logits, false, dw, true);   // [in,out] += h^T dlogits
+            else gemm(logits, true, hc, false, dw, true);                  // [out,in] += dlogits^T h
+        }
+    }
+    Tensor sum = Tensor::bytes(8), scratch = Tensor::bytes(pk_reduce_scratch_bytes());
+    check(pk_reduce_sum_f64(S(), rows.f32(), i64(R), 0, 0, static_cast<double*>(sum.ptr()), scratch.ptr()), "pk_reduce_sum_f64");
+    Tensor out = Tensor::empty(1, 1, DType::F32);
+    check(pk_sum_to_mean(S(), static_cast<const double*>(sum.ptr()), static_cast<double>(R), out.f32()), "pk_sum_to_mean");
+    return record(std::move(out), {h, W}, [dh, dw](Variable* self) {
+        const Var& h = self->parents[0];
+        const Var& W = self->parents[1];
+        const float g = self->grad(0, 0);
+        if (h->requires_grad && dh.defined()) {
+            Tensor t = dh;
+            if (g != 1.0f) check(pk_scale(S(), t.dt(), t.ptr(), g, t.ptr(), i64(t.numel())), "pk_scale");
+            h->accumulate(t);
+        }
+        if (W->requires_grad && dw.defined()) {
+            if (W->grad_dtype() == DType::F32) {
+                Tensor& gw = W->grad_for_accumulate();
+                check(pk_axpy(S(), gw.dt(), gw.ptr(), dw.dt(), dw.ptr(), g, i64(dw.numel())), "pk_axpy");
+            } else {
+                Tensor t = dw;
+                if (g != 1.0f) check(pk_scale(S(), t.dt(), t.ptr(), g, t.ptr(), i64(t.numel())), "pk_scale");
+                W->accumulate(t);
+            }
+        }
+    });
+}
+
 // reference: src/ops.cpp:481-537 (first head of q and of k only)
 Var apply_rope(const Var& qk, const std::vector<int>& pos, float theta_base, size_t head_dim) {
     const size_t T = qk->data.rows(), d3 = qk->data.cols();

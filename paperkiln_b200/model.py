@@ -144,6 +144,10 @@ class Model:
     def set_checkpoint(self, on: bool):
         _check(libmt().mt_model_set_checkpoint(self._h, int(on)), "mt_model_set_checkpoint")
 
+    def set_loss_chunk(self, rows: int):
+        """rows > 0: fused head + cross entropy over row chunks (default 8192); 0: separate ops."""
+        _check(libmt().mt_model_set_loss_chunk(self._h, int(rows)), "mt_model_set_loss_chunk")
+
     def step(self, ids, targets, seq_len: int = 0, loss_scale: float = 1.0, backward: bool = True) -> float:
         """zero_grad + forward + cross entropy (+ backward). ids/targets: int32 arrays (host)."""
         ids = np.ascontiguousarray(ids, dtype=np.int32)
