@@ -119,6 +119,26 @@ size_t pk_rmsnorm_bwd_scratch_bytes(int64_t R, int64_t C);
 int pk_rmsnorm_bwd(void* stream, int dtype, const void* dy, const void* x, const float* w,
                    const float* rinv, void* dx, float* dw, void* scratch,
                    int64_t R, int64_t C);
+/* pk_rmsnorm_bwd for hosts that cannot allocate device memory. (No counterpart in the
+ * reference: this entry exists only in this library.)
+ * Who needs it: a host that gave the whole GPU to its own memory pool before this library was
+ * loaded has no memory left to allocate the dw scratch from, and a latency-critical loop
+ * cannot afford cudaMalloc, which synchronises the device. This variant takes no scratch
+ * argument and calls no allocator (CUDA's or anyone else's): the per-block partial sums of dw
+ * go to a fixed buffer inside the library image (~9.3 MiB of device memory held by every GPU
+ * that loads libpk, until the process exits).
+ * Limits and rules:
+ *   - C is limited by that buffer: pk_rmsnorm_bwd_scratch_bytes(R, C) must not exceed
+ *     592*4096*4 bytes (C <= 4096 on a 148-SM GPU); larger C returns PK_ERR_UNSUPPORTED with
+ *     a message, and pk_rmsnorm_bwd with caller scratch remains available.
+ *   - The first call on a device resolves the buffer's device address (a CUDA runtime query,
+ *     made with that device current): make that first call before starting any stream capture.
+ *   - All calls share the one buffer and it keeps whatever the last call wrote. Nothing has
+ *     to be cleared between calls (each call overwrites what it reads), but two calls that
+ *     overlap on the GPU (different streams) race on it: serialise them.
+ * Results are identical to pk_rmsnorm_bwd, bit for bit. */
+int pk_rmsnorm_bwd_noalloc(void* stream, int dtype, const void* dy, const void* x, const float* w,
+                           const float* rinv, void* dx, float* dw, int64_t R, int64_t C);
 /* LayerNorm (biased variance). Saves mean[R] and rstd[R] instead of the
  * reference's xhat [R,C]. Replaces ops::layernorm (src/ops.cpp:248-327),
  * devops::layernorm_fwd/bwd and k_layernorm_* / k_colsum_dgb in

@@ -472,6 +472,62 @@ int pk_rmsnorm_bwd(void* stream, int dtype, const void* dy, const void* x, const
                                           static_cast<float*>(scratch), R, C);
 }
 
+// ---- RMSNorm backward for callers that cannot allocate -----------------------------------
+// pk_rmsnorm_bwd needs a scratch buffer for the per-block partial sums of dw, and expects the
+// caller to allocate it. Some hosts cannot: a runtime that claimed the whole GPU for its own
+// memory pool before loading this library has nothing left for cudaMalloc to hand out, and a
+// latency-critical loop must not call cudaMalloc at all because it synchronises the device.
+// For them the partial sums live in a fixed array that is part of the library image.
+//
+// The array below is device memory reserved by the module itself (~9.3 MiB on every GPU that
+// loads the library, until the process exits). Its name is only a host-side handle: the
+// device address is looked up once per device with cudaGetSymbolAddress and that pointer is
+// what the kernels receive.
+constexpr size_t PK_STATIC_SCRATCH_FLOATS = size_t(592) * 4096;  // 592 partial rows of up to 4096 columns
+static __device__ __align__(256) float g_rmsnorm_static_scratch[PK_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int PK_MAX_DEVICES = 64;
+float* g_static_scratch_ptr[PK_MAX_DEVICES] = {};  // device address per ordinal, resolved lazily
+}  // namespace
+
+int pk_rmsnorm_bwd_noalloc(void* stream, int dtype, const void* dy, const void* x, const float* w,
+                           const float* rinv, void* dx, float* dw, int64_t R, int64_t C) {
+    PK_REQUIRE(valid_dtype(dtype), "bad dtype");
+    PK_REQUIRE(R >= 0 && C > 0, "bad shape");
+    // the same partial-row count pk_rmsnorm_bwd_scratch_bytes() is based on
+    const size_t need = static_cast<size_t>(norm_partial_blocks()) * static_cast<size_t>(C);
+    if (need > PK_STATIC_SCRATCH_FLOATS) {
+        set_error("pk_rmsnorm_bwd_noalloc: %lld columns need %zu floats of scratch, the built-in buffer holds %zu "
+                  "(about %zu columns on this GPU); use pk_rmsnorm_bwd with caller-provided scratch",
+                  static_cast<long long>(C), need, PK_STATIC_SCRATCH_FLOATS,
+                  PK_STATIC_SCRATCH_FLOATS / static_cast<size_t>(norm_partial_blocks()));
+        return PK_ERR_UNSUPPORTED;
+    }
+    if (R == 0) return PK_OK;
+    PK_REQUIRE(dy && x && w && rinv, "null pointer");
+    int dev = 0;
+    PK_CHECK_CUDA(cudaGetDevice(&dev));
+    PK_REQUIRE(dev >= 0 && dev < PK_MAX_DEVICES, "device ordinal out of range");
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        // First call on this device (it is the current one): resolve the symbol. This is a
+        // runtime query, so make this first call outside any stream capture.
+        void* p = nullptr;
+        PK_CHECK_CUDA(cudaGetSymbolAddress(&p, g_rmsnorm_static_scratch));
+        g_static_scratch_ptr[dev] = static_cast<float*>(p);
+    }
+    float* scratch = g_static_scratch_ptr[dev];
+    // Nothing needs clearing: every partial row that the second stage reads is written in
+    // full by the first stage of the same call, whatever an earlier call left behind.
+    if (dtype == PK_F32)
+        return norm_bwd_dispatch<float, false>(as_stream(stream), static_cast<const float*>(dy),
+                                               static_cast<const float*>(x), w, rinv, nullptr,
+                                               static_cast<float*>(dx), dw, nullptr, scratch, R, C);
+    return norm_bwd_dispatch<bf16, false>(as_stream(stream), static_cast<const bf16*>(dy),
+                                          static_cast<const bf16*>(x), w, rinv, nullptr,
+                                          static_cast<bf16*>(dx), dw, nullptr, scratch, R, C);
+}
+
 int pk_layernorm_fwd(void* stream, int dtype, const void* x, const float* gamma, const float* beta,
                      void* y, float* mean, float* rstd, int64_t R, int64_t C, float eps) {
     PK_REQUIRE(valid_dtype(dtype), "bad dtype");
