@@ -36,6 +36,8 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+SAMPLE_LAYERS = 2  # depth of the CPU baseline sample (see run_reference)
+
 WORKLOADS = {
     "c1": dict(family="llama", dtype="fp32", vocab=4096, d=128, layers=4, heads=4, kv_heads=0, dff=512, nctx=256,
                theta=10000.0, rope_all=0, qlora=0, batch=8, seq=256,
@@ -151,12 +153,25 @@ def ref_harness_args(w, sample_tokens):
     return a
 
 
+def step_flops_per_token(w):
+    """Dense FLOPs one checkpointed training step executes per token (forward + recompute + backward)."""
+    f_blk, f_attn, f_head = flops_per_token(w)
+    return w["layers"] * 4 * (f_blk + f_attn) + 3 * f_head
+
+
 def run_reference(w, steps, warmup, sample_tokens):
-    """Times the unmodified reference's CPU path on a bounded sample of the workload."""
+    """Times the unmodified reference's CPU path on a bounded sample of the workload: one sequence of
+    `sample_tokens` tokens through the first SAMPLE_LAYERS blocks (+ embedding, final norm, head, AdamW)
+    of the same model. Its tokens/s is scaled to the full model by the ratio of dense FLOPs per token
+    (a full-depth step of even 16 tokens costs the reference minutes: its per-step weight transposes
+    and serial AdamW over 1.2 G parameters do not shrink with the token count)."""
     harness = ROOT / "oracle" / "_ref" / "ref_harness"
     if not harness.exists():
         return None, f"{harness} missing (built by `make -C oracle` from the reference's sources)"
-    args = ref_harness_args(w, sample_tokens)
+    sw = dict(w)
+    sw["layers"] = min(w["layers"], SAMPLE_LAYERS)
+    sw["seq"] = sample_tokens
+    args = ref_harness_args(sw, sample_tokens)
     argv = [str(harness), "bench"]
     for k, v in args.items():
         argv += [f"--{k}", str(v)]
@@ -168,8 +183,13 @@ def run_reference(w, steps, warmup, sample_tokens):
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     out = json.loads(line)
     out["wall_s_total"] = time.time() - t0
-    out["sample"] = (f"{steps} timed step(s) of {sample_tokens} tokens (1 sequence) of the same model, reference "
-                     f"CPU fp32 path with per-block checkpointing + AdamW")
+    ratio = step_flops_per_token(sw) / step_flops_per_token(w)
+    out["tokens_per_s_sample"] = out["tokens_per_s"]
+    out["tokens_per_s"] = out["tokens_per_s"] * ratio
+    out["sample"] = (f"{steps} timed step(s) of {sample_tokens} tokens (1 sequence) through {sw['layers']} of the "
+                     f"{w['layers']} blocks + embedding, head and AdamW of the same model on the reference's CPU fp32 "
+                     f"path with per-block checkpointing: {out['tokens_per_s_sample']:.3f} tokens/s measured, scaled by "
+                     f"{ratio:.4f} (dense FLOPs per token, sample model / full model at seq {w['seq']})")
     return out, None
 
 
@@ -181,6 +201,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("PK_BENCH_WORKLOAD", "c4"), choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the global batch (sequences)")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of blocks (small profiling cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=0)
     ap.add_argument("--skip-nockpt", action="store_true", help="do not measure the un-checkpointed step")
@@ -189,10 +210,13 @@ def main():
     w = dict(WORKLOADS[args.workload])
     if args.batch:
         w["batch"] = args.batch
+    if args.layers:
+        w["layers"] = args.layers
+        w["name"] += f" [reduced to {args.layers} block(s)]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    sample_tokens = args.cpu_sample_tokens or {"c1": 2048, "c2": 64, "c3": 64, "c4": 16}[args.workload]
+    sample_tokens = args.cpu_sample_tokens or {"c1": 2048, "c2": 64, "c3": 32, "c4": 32}[args.workload]
     if args.workload == "c1":
         sample_tokens = 256  # per sequence; the harness batches 8 of them below
 
@@ -206,11 +230,17 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
-        out, err = run_reference(w, args.steps, max(args.warmup, 0), sample_tokens)
+        if args.workload == "c1":
+            # bounded: at most 3 full-size steps (each ~20 s of CPU work)
+            out, err = run_reference_c1(w, min(args.steps, 3), min(max(args.warmup, 0), 1))
+        else:
+            out, err = run_reference(w, min(args.steps, 3), min(max(args.warmup, 0), 1), sample_tokens)
         if out is None:
             print(json.dumps({"impl": "reference", "unavailable": err}))
             return 0
         line = dict(base)
+        # the CPU arm is bounded: it never times more than 3 steps after at most 1 warm-up step
+        line.update({"steps": min(args.steps, 3), "warmup": min(max(args.warmup, 0), 1)})
         line.update({"impl": "reference", "value": out["tokens_per_s"], "ms_per_step": out["step_s"] * 1e3,
                      "dtype": "f32", "gpu_launches": 0,
                      "cpu_baseline": {"value": out["tokens_per_s"], "unit": "tokens/s", "cores": 1, "kind": "reference",
@@ -412,18 +442,19 @@ def main():
     return 0
 
 
-def run_reference_c1(w):
-    """Config 1 is the reference's own CPU-runnable case: one full-size step (8 x 256 tokens)."""
+def run_reference_c1(w, steps=1, warmup=0):
+    """Config 1 is the reference's own CPU-runnable case: full-size steps (8 x 256 tokens)."""
     harness = ROOT / "oracle" / "_ref" / "ref_harness"
     if not harness.exists():
-        return None, f"{harness} missing"
+        return None, f"{harness} missing (built by `make -C oracle` from the reference's sources)"
     argv = [str(harness), "bench", "--family", "llama", "--vocab", "4096", "--d", "128", "--layers", "4", "--heads", "4",
-            "--dff", "512", "--nctx", "256", "--batch", "8", "--seq", "256", "--ckpt", "1", "--steps", "1"]
+            "--dff", "512", "--nctx", "256", "--batch", "8", "--seq", "256", "--ckpt", "1",
+            "--steps", str(steps + warmup), "--warmup", str(warmup)]
     res = subprocess.run(argv, capture_output=True, text=True)
     if res.returncode != 0:
         return None, res.stderr[-300:]
     out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
-    out["sample"] = "1 full-size step (8 x 256 tokens), reference CPU fp32 path with checkpointing + AdamW"
+    out["sample"] = f"{steps} full-size step(s) (8 x 256 tokens), reference CPU fp32 path with checkpointing + AdamW"
     return out, None
 
 
