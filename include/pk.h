@@ -225,6 +225,10 @@ int pk_attn_last_path(void);
  * gave up). Synchronises the device; clear != 0 resets it. */
 int pk_attn_tc_status(int* status_h, int clear);
 int pk_attn_force_simt(int on);
+/* Which tensor-core forward kernel runs: 1 (default) = warp-specialised, two 128-query slots per
+ * CTA with P and O kept in tensor memory; 0 = one 128-query tile per CTA. Same results up to
+ * rounding; meant for tests and measurements. */
+int pk_attn_fwd_variant(int variant);
 
 /* ---- embedding / loss --------------------------------------------------------
  * Row gather out[i,:] = table[ids[i],:] (pure copy; table has the out dtype).

@@ -1,0 +1,507 @@
+// Flash attention forward, warp-specialised (bf16 operands, fp32 accumulation in tensor
+// memory), head_dim 64 or 128, causal or full, grouped-query head mapping, B stacked sequences.
+//
+// One CTA per SM works on 256 consecutive queries of one head as two 128-row slots that take
+// turns on the tensor pipe: while the softmax warps of slot 0 work on the scores of key tile j,
+// the MMA warp computes slot 1's scores / output update, and vice versa.
+//   warps 0-7    softmax of slot 0     warps w and w+4 share tensor-memory lane quadrant w & 3
+//   warps 8-15   softmax of slot 1     (rows 32(w&3) ..) and split every row's 128 score columns
+//   warp 16      issues every tcgen05.mma (one thread)
+//   warp 17      issues every TMA load (one thread); warps 18-19 idle. This warpgroup hands
+//                most of its registers to the softmax warps (setmaxnreg).
+// Per slot and 128-key tile:
+//   S = Q K^T            smem operands (128B swizzle), fp32 result in tensor memory
+//   p = exp2(S c - m)    in registers; P is written back to TENSOR MEMORY as packed bf16 and
+//                        is the A operand of the next MMA -- it never touches shared memory
+//   O += P V             V read MN-major (no transpose); O stays in tensor memory for the whole
+//                        key loop and is rescaled in place only when a row maximum grew by more
+//                        than 2^8 since the last rescale (p <= 256 is harmless in bf16 / fp32)
+// Everything a thread does depends only on the data, so results are reproducible bit for bit.
+// Every mbarrier wait is bounded (status word, no trap); pairs of threads that meet at a named
+// barrier agree on leaving the loop through shared memory, so none is left waiting.
+//
+// Semantics: ops::fused_attention of the reference (src/ops.cpp:863-934) applied per head.
+#include "pk_tc.cuh"
+
+namespace pk {
+
+__device__ int g_attn_fwd_ws_status = 0;
+
+using namespace tc;
+
+#ifdef PK_WS_TIMING
+// Development aid (not compiled into the library): clock64 stamps of one CTA's iteration 5.
+__device__ long long g_ws_dbg[64];
+#define WS_T(slot, i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 5) g_ws_dbg[(slot) * 16 + (i)] = clock64(); } while (0)
+extern "C" int pk_debug_read_ws(long long* out_h) {
+    cudaDeviceSynchronize();
+    return cudaMemcpyFromSymbol(out_h, g_ws_dbg, sizeof(long long) * 64) == cudaSuccess ? 0 : 2;
+}
+#else
+#define WS_T(slot, i) do { } while (0)
+#endif
+
+namespace {
+
+constexpr int WS_BM = 128;                   // rows per slot
+constexpr int WS_BN = 128;                   // keys per tile
+constexpr int WS_SOFT_WARPS = 16;
+constexpr int WS_THREADS = (WS_SOFT_WARPS + 4) * 32;   // + one control warpgroup: MMA warp, TMA warp, 2 idle
+constexpr float WS_LOG2E = 1.4426950408889634f;
+constexpr float WS_LN2 = 0.6931471805599453f;
+constexpr float WS_RESCALE_GAP = 8.0f;       // log2 units
+constexpr int WS_REGS_SOFT = 112;            // registers per softmax thread after setmaxnreg (literal in the asm below)
+constexpr int WS_REGS_CTRL = 32;             // registers per control thread
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void named_sync64(int id) { asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// The issuing thread keeps every operand descriptor as a constant high word and a low word
+// (start address and leading-dimension offset) to which a k-step adds a compile-time constant,
+// so that one MMA costs one or two integer instructions besides itself.
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, 128B swizzle
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t tile) { return ((tile & 0x3ffffu) >> 4) | ((16u >> 4) << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t tile) { return ((tile & 0x3ffffu) >> 4) | ((CHUNK_BYTES >> 4) << 16); }
+__host__ __device__ constexpr uint32_t kstep_kmajor(int k) { return static_cast<uint32_t>((k >> 2) * (CHUNK_BYTES >> 4) + (k & 3) * 2); }
+__host__ __device__ constexpr uint32_t kstep_mnmajor(int k) { return static_cast<uint32_t>(k * (2048 >> 4)); }
+__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem, 128 x 16 bf16 packed two per column] . B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+template <int DK>
+__device__ __forceinline__ void load_tile(uint32_t dst, const CUtensorMap* map, int col0, int64_t row, uint32_t bar) {
+#pragma unroll
+    for (int c = 0; c < DK / 64; ++c) tma_load_2d(dst + c * CHUNK_BYTES, map, col0 + c * 64, static_cast<int32_t>(row), bar);
+}
+
+struct WsParams {
+    bf16* out;
+    int64_t ldo;
+    float* lse;
+    int S;
+    int Hq, Hkv;
+    float scale_log2;  // scale * log2(e)
+    int causal;
+};
+
+template <int DK>
+struct WsLayout {
+    static constexpr int NCH = DK / 64;
+    static constexpr int TILE = NCH * (int)CHUNK_BYTES;   // 128 rows x DK bf16
+    static constexpr int NS = DK == 64 ? 3 : 2;           // K and V stages
+    static constexpr int OFF_Q = 0;                       // 2 slots
+    static constexpr int OFF_K = 2 * TILE;
+    static constexpr int OFF_V = OFF_K + NS * TILE;
+    static constexpr int OFF_X = OFF_V + NS * TILE;       // row max / row sum exchange: [2 slots][2 halves][128] floats
+    static constexpr int OFF_F = OFF_X + 2048;            // "still fine" flags, same shape, ints
+    static constexpr int OFF_BAR = OFF_F + 2048;
+    static constexpr int BYTES = OFF_BAR + 256 + 1024;
+    // tensor memory columns
+    static constexpr int T_S = 0;                          // + slot * 128
+    static constexpr int T_O = 256;                        // + slot * DK
+    static constexpr int T_P = DK == 64 ? 384 : 0;         // + slot * (DK == 64 ? 64 : 128); aliases S when DK = 128
+    static constexpr int P_PITCH = DK == 64 ? 64 : 128;
+};
+
+template <int DK>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const WsParams p) {
+    using L = WsLayout<DK>;
+    constexpr int NS = L::NS;
+    constexpr int OH = DK / 2;  // output columns per softmax thread
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+    uint64_t* q_full = bars;            // [2]
+    uint64_t* k_full = bars + 2;        // [NS]
+    uint64_t* k_empty = bars + 5;       // [NS]
+    uint64_t* v_full = bars + 8;        // [NS]
+    uint64_t* v_empty = bars + 11;      // [NS]
+    uint64_t* s_full = bars + 14;       // [2]
+    uint64_t* p_full = bars + 16;       // [2]
+    uint64_t* o_done = bars + 18;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(smem + L::OFF_X);
+    int* fine = reinterpret_cast<int*>(smem + L::OFF_F);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // long tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (p.Hq / p.Hkv);
+    const int64_t seq0 = static_cast<int64_t>(b) * p.S;
+    const int nkv_tot = (p.S + WS_BN - 1) / WS_BN;
+    int nkv[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) nkv[s] = p.causal ? min(2 * qt + s + 1, nkv_tot) : nkv_tot;
+    const int nkv_max = nkv[1];
+
+    if (tid == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&q_full[i]), 1);
+            mbar_init(smem_u32(&s_full[i]), 1);
+            mbar_init(smem_u32(&p_full[i]), WS_SOFT_WARPS / 2);
+            mbar_init(smem_u32(&o_done[i]), 1);
+        }
+        for (int i = 0; i < NS; ++i) {
+            mbar_init(smem_u32(&k_full[i]), 1);
+            mbar_init(smem_u32(&k_empty[i]), 1);
+            mbar_init(smem_u32(&v_full[i]), 1);
+            mbar_init(smem_u32(&v_empty[i]), 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) tmem_alloc(smem_u32(tmem_slot), 512);
+    fence_before();
+    __syncthreads();
+    fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t sQ = smem_u32(smem + L::OFF_Q), sK = smem_u32(smem + L::OFF_K), sV = smem_u32(smem + L::OFF_V);
+
+    // Register budget: setmaxnreg moves registers inside the pool the CTA was LAUNCHED with
+    // (threads x registers per thread of the compiled kernel), not the SM's whole file; an
+    // increase that the pool cannot cover would wait forever. The control warpgroup shrinks to
+    // WS_REGS_CTRL and the softmax warps grow to WS_REGS_SOFT; launch_ws() refuses to launch
+    // unless 512 * WS_REGS_SOFT + 128 * WS_REGS_CTRL fits the launch allocation.
+    // setmaxnreg is a warpgroup-wide aligned instruction: all four warps of the control
+    // warpgroup execute the one instance below before they part ways.
+    if (warp >= WS_SOFT_WARPS) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+      if (warp == WS_SOFT_WARPS + 1) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            for (int s = 0; s < 2; ++s) {
+                mbar_expect_tx(smem_u32(&q_full[s]), L::TILE);
+                load_tile<DK>(sQ + s * L::TILE, &map_q, h * DK, seq0 + (2 * qt + s) * WS_BM, smem_u32(&q_full[s]));
+            }
+            for (int j = 0; j < nkv_max && ok; ++j) {
+                const int st = j % NS, n = j / NS;
+                const int64_t row = seq0 + static_cast<int64_t>(j) * WS_BN;
+                if (n > 0) ok = mbar_wait(smem_u32(&k_empty[st]), (n - 1) & 1, abort_flag, &g_attn_fwd_ws_status);
+                if (!ok) break;
+                mbar_expect_tx(smem_u32(&k_full[st]), L::TILE);
+                load_tile<DK>(sK + st * L::TILE, &map_k, hk * DK, row, smem_u32(&k_full[st]));
+                if (n > 0) ok = mbar_wait(smem_u32(&v_empty[st]), (n - 1) & 1, abort_flag, &g_attn_fwd_ws_status);
+                if (!ok) break;
+                mbar_expect_tx(smem_u32(&v_full[st]), L::TILE);
+                load_tile<DK>(sV + st * L::TILE, &map_v, hk * DK, row, smem_u32(&v_full[st]));
+            }
+        }
+        __syncwarp();
+      } else if (warp == WS_SOFT_WARPS) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = idesc_bf16(WS_BN, 0, 0);
+            const uint32_t idesc_o = idesc_bf16(DK, 0, 1);
+            bool ok = true;
+            const uint32_t q_lo0 = desc_lo_kmajor(sQ), k_lo0 = desc_lo_kmajor(sK), v_lo0 = desc_lo_mnmajor(sV);
+            auto issue_s = [&](int s, int j) {  // S_s(j) = Q_s K_j^T
+                const uint32_t q_lo = q_lo0 + s * (L::TILE >> 4), k_lo = k_lo0 + (j % NS) * (L::TILE >> 4);
+                const uint32_t d = tmem + L::T_S + s * 128;
+#pragma unroll
+                for (int k = 0; k < DK / 16; ++k) mma_ss(d, q_lo + kstep_kmajor(k), k_lo + kstep_kmajor(k), idesc_s, k > 0 ? 1u : 0u);
+                commit(smem_u32(&s_full[s]));
+            };
+            ok = mbar_wait(smem_u32(&q_full[0]), 0, abort_flag, &g_attn_fwd_ws_status);
+            if (ok) ok = mbar_wait(smem_u32(&q_full[1]), 0, abort_flag, &g_attn_fwd_ws_status);
+            if (ok) ok = mbar_wait(smem_u32(&k_full[0]), 0, abort_flag, &g_attn_fwd_ws_status);
+            if (ok) {
+                fence_after();
+                issue_s(0, 0);
+                issue_s(1, 0);
+                commit(smem_u32(&k_empty[0]));
+            }
+            for (int j = 0; j < nkv_max && ok; ++j) {
+                const int st = j % NS;
+                bool v_ready = false, k_ready = false;
+#pragma unroll 1
+                for (int s = 0; s < 2; ++s) {
+                    if (j >= nkv[s] || !ok) continue;
+                    WS_T(2, s * 4 + 0);
+                    ok = mbar_wait(smem_u32(&p_full[s]), j & 1, abort_flag, &g_attn_fwd_ws_status);
+                    WS_T(2, s * 4 + 1);
+                    if (ok && !v_ready) {
+                        ok = mbar_wait(smem_u32(&v_full[st]), (j / NS) & 1, abort_flag, &g_attn_fwd_ws_status);
+                        v_ready = true;
+                    }
+                    if (!ok) break;
+                    fence_after();
+                    const uint32_t v_lo = v_lo0 + st * (L::TILE >> 4);
+                    const uint32_t d = tmem + L::T_O + s * DK, a = tmem + L::T_P + s * L::P_PITCH;
+#pragma unroll
+                    for (int k = 0; k < WS_BN / 16; ++k)
+                        mma_ts(d, a + k * 8, v_lo + kstep_mnmajor(k), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+                    WS_T(2, s * 4 + 2);
+                    if (j + 1 < nkv[s]) {
+                        if (!k_ready) {
+                            ok = mbar_wait(smem_u32(&k_full[(j + 1) % NS]), ((j + 1) / NS) & 1, abort_flag, &g_attn_fwd_ws_status);
+                            k_ready = true;
+                            if (!ok) break;
+                            fence_after();
+                        }
+                        issue_s(s, j + 1);
+                    } else {
+                        commit(smem_u32(&o_done[s]));
+                    }
+                    WS_T(2, s * 4 + 3);
+                }
+                if (!ok) break;
+                commit(smem_u32(&v_empty[st]));                              // V_j free once P.V of both slots is done
+                if (j + 1 < nkv_max) commit(smem_u32(&k_empty[(j + 1) % NS]));  // K_{j+1}: after its last S
+            }
+        }
+        __syncwarp();
+      }
+    } else {
+        // ------------------------------------------------------------------ softmax warps
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+        const int s = warp >> 3;              // slot
+        const int wl = warp & 7;
+        const int quad = wl & 3, hf = wl >> 2;
+        const int row = quad * 32 + lane;
+        const int q0 = (2 * qt + s) * WS_BM;
+        const int qi = q0 + row;
+        const int bar_id = 1 + s * 4 + quad;
+        const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+        const uint32_t t_s = tmem + lane_off + L::T_S + s * 128 + hf * 64;            // this thread's 64 score columns
+        const uint32_t t_p = tmem + lane_off + L::T_P + s * L::P_PITCH + hf * 32;     // its 64 keys as 32 packed columns
+        const uint32_t t_o = tmem + lane_off + L::T_O + s * DK + hf * OH;             // its output columns
+        float* my_x = xch + (s * 2 + hf) * 128 + row;
+        float* other_x = xch + (s * 2 + (hf ^ 1)) * 128 + row;
+        int* my_f = fine + (s * 2 + hf) * 128 + row;
+        int* other_f = fine + (s * 2 + (hf ^ 1)) * 128 + row;
+        const int my_nkv = nkv[s];
+
+        float m = -INFINITY, l = 0.0f;  // l: partial row sum over this thread's columns
+        bool ok = true;
+        for (int j = 0; j < my_nkv; ++j) {
+            const int kv0 = j * WS_BN;
+            if (wl == 0 && lane == 0) WS_T(s, 0);
+            ok = mbar_wait(smem_u32(&s_full[s]), j & 1, abort_flag, &g_attn_fwd_ws_status);
+            if (wl == 0 && lane == 0) WS_T(s, 1);
+            ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tensor-memory accesses below are warp-wide
+            fence_after();
+            uint32_t r0[32], r1[32];
+            if (ok) {
+                tmem_ld32(t_s, r0);
+                tmem_ld32(t_s + 32, r1);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) r0[e] = r1[e] = 0u;
+            }
+            if (wl == 0 && lane == 0) WS_T(s, 2);
+            const bool need_mask = (p.causal && kv0 + WS_BN - 1 > q0) || (kv0 + WS_BN > p.S);
+            if (need_mask) {
+                const int key0 = kv0 + hf * 64;
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    if (key0 + e >= p.S || (p.causal && key0 + e > qi)) r0[e] = 0xff800000u;            // -inf
+                    if (key0 + 32 + e >= p.S || (p.causal && key0 + 32 + e > qi)) r1[e] = 0xff800000u;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
+            *my_x = mx;
+            *my_f = ok ? 1 : 0;
+            named_sync64(bar_id);
+            mx = fmaxf(mx, *other_x);
+            ok = ok && (*other_f != 0);
+            named_sync64(bar_id);  // the exchange slots are rewritten next tile
+            if (wl == 0 && lane == 0) WS_T(s, 3);
+            if (!ok) break;        // both threads of the pair leave together
+            // Row maximum in log2 units. Every row sees at least one key in its first tile
+            // (key 0), so cand is finite from j = 0 on.
+            const float cand = fmaxf(m, mx * p.scale_log2);
+            if (j == 0) {
+                m = cand;
+            } else {
+                const bool grow = cand > m + WS_RESCALE_GAP;
+                if (__any_sync(0xffffffffu, grow)) {
+                    // s_full(j) also covers P.V of tile j-1 (issued before S(j)): O is quiescent
+                    const float f = grow ? ex2_approx(m - cand) : 1.0f;
+                    if (grow) m = cand;
+                    l *= f;
+#pragma unroll 1
+                    for (int ch = 0; ch < OH / 16; ++ch) {  // 16 columns at a time: the scores stay in registers
+                        uint32_t r[16];
+                        tmem_ld16(t_o + ch * 16, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * f);
+                        tmem_st16(t_o + ch * 16, r);
+                    }
+                }
+            }
+            if (wl == 0 && lane == 0) WS_T(s, 4);
+            const float neg_m = -m;
+            float sum = 0.0f;
+            uint32_t pk[32];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float a0 = ex2_approx(fmaf(__uint_as_float(r0[2 * e]), p.scale_log2, neg_m));
+                const float a1 = ex2_approx(fmaf(__uint_as_float(r0[2 * e + 1]), p.scale_log2, neg_m));
+                const float b0 = ex2_approx(fmaf(__uint_as_float(r1[2 * e]), p.scale_log2, neg_m));
+                const float b1 = ex2_approx(fmaf(__uint_as_float(r1[2 * e + 1]), p.scale_log2, neg_m));
+                sum += (a0 + a1) + (b0 + b1);
+                pk[e] = pack2(a0, a1);
+                pk[16 + e] = pack2(b0, b1);
+            }
+            l += sum;
+            if (wl == 0 && lane == 0) WS_T(s, 5);
+            tmem_st32(t_p, pk);
+            tmem_wait_st();
+            if (wl == 0 && lane == 0) WS_T(s, 6);
+            fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[s]));
+            if (wl == 0 && lane == 0) WS_T(s, 7);
+        }
+
+        // total row sum = the two halves' partial sums (both threads of a pair get here together)
+        *my_x = l;
+        named_sync64(bar_id);
+        l += *other_x;
+        if (ok) ok = mbar_wait(smem_u32(&o_done[s]), 0, abort_flag, &g_attn_fwd_ws_status);
+        ok = __all_sync(0xffffffffu, ok);
+        fence_after();
+        if (ok) {
+            const float inv = 1.0f / l;
+            bf16* dst = p.out + (seq0 + qi) * p.ldo + h * DK + hf * OH;
+#pragma unroll
+            for (int ch = 0; ch < OH / 32; ++ch) {
+                uint32_t r[32];
+                tmem_ld32(t_o + ch * 32, r);
+                tmem_wait_ld();
+                if (qi < p.S) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 v;
+                        v.x = pack2(__uint_as_float(r[g * 8 + 0]) * inv, __uint_as_float(r[g * 8 + 1]) * inv);
+                        v.y = pack2(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
+                        v.z = pack2(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
+                        v.w = pack2(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + ch * 32 + g * 8) = v;
+                    }
+                }
+            }
+            if (hf == 0 && qi < p.S) p.lse[(seq0 + qi) * p.Hq + h] = (m + log2f(l)) * WS_LN2;
+        }
+    }
+
+    fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+template <int DK>
+int launch_ws(cudaStream_t st, const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const WsParams& p,
+              int64_t B) {
+    using L = WsLayout<DK>;
+    auto kern = attn_fwd_ws_kernel<DK>;
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncAttributes fa;
+        PK_CHECK_CUDA(cudaFuncGetAttributes(&fa, kern));
+        PK_REQUIRE(fa.numRegs * WS_THREADS >= WS_SOFT_WARPS * 32 * WS_REGS_SOFT + 4 * 32 * WS_REGS_CTRL,
+                   "attention forward: the kernel's launch register allocation cannot cover its setmaxnreg plan");
+        PK_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
+        attr = true;
+    }
+    dim3 grid(static_cast<unsigned>((p.S + 2 * WS_BM - 1) / (2 * WS_BM)), p.Hq, static_cast<unsigned>(B));
+    kern<<<grid, WS_THREADS, L::BYTES, st>>>(mq, mk, mv, p);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+}  // namespace
+
+int attn_fwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
+                int causal) {
+    CUtensorMap mq, mk, mv;
+    const int64_t R = B * S;
+    int rc = make_tensor_map(&mq, q, static_cast<int64_t>(Hq) * dk, R, ldq, 64, WS_BM);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mk, k, static_cast<int64_t>(Hkv) * dk, R, ldk, 64, WS_BN);
+    if (rc != PK_OK) return rc;
+    rc = make_tensor_map(&mv, v, static_cast<int64_t>(Hkv) * dk, R, ldv, 64, WS_BN);
+    if (rc != PK_OK) return rc;
+    WsParams p;
+    p.out = static_cast<bf16*>(out);
+    p.ldo = ldo;
+    p.lse = lse;
+    p.S = static_cast<int>(S);
+    p.Hq = Hq;
+    p.Hkv = Hkv;
+    p.scale_log2 = scale * WS_LOG2E;
+    p.causal = causal;
+    return dk == 64 ? launch_ws<64>(st, mq, mk, mv, p, B) : launch_ws<128>(st, mq, mk, mv, p, B);
+}
+
+int attn_fwd_ws_status(int* status_h, int clear) {
+    PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, g_attn_fwd_ws_status, sizeof(int)));
+    if (clear) {
+        const int zero = 0;
+        PK_CHECK_CUDA(cudaMemcpyToSymbol(g_attn_fwd_ws_status, &zero, sizeof(int)));
+    }
+    return PK_OK;
+}
+
+}  // namespace pk

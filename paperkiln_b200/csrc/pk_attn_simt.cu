@@ -248,6 +248,11 @@ attn_bwd_dkv_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ 
 
 static thread_local int g_attn_last_path = -1;
 static int g_attn_force_simt = 0;
+static int g_attn_fwd_variant = 1;  // 1: warp-specialised forward (pk_attn_fwd_ws.cu), 0: single-tile forward (pk_attn_tc.cu)
+
+int attn_fwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
+                int causal);
 
 // tensor-core kernels (pk_attn_tc.cu)
 int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
@@ -352,6 +357,8 @@ int pk_attn_fwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     ProfScope prof(PROF_ATTN_FWD, (causal ? 2.0 : 4.0) * B * S * S * Hq * dk, as_stream(stream));
     if (!g_attn_force_simt && attn_tc_supported(dtype, dk, q, ldq, k, ldk, v, ldv, out, ldo, B, S)) {
         g_attn_last_path = 1;
+        if (g_attn_fwd_variant == 1)
+            return attn_fwd_ws(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
         return attn_tc_fwd(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
     }
     g_attn_last_path = 0;
@@ -398,6 +405,11 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
 int pk_attn_last_path(void) { return g_attn_last_path; }
 int pk_attn_force_simt(int on) {
     g_attn_force_simt = on ? 1 : 0;
+    return PK_OK;
+}
+int pk_attn_fwd_variant(int variant) {
+    PK_REQUIRE(variant == 0 || variant == 1, "unknown forward variant");
+    g_attn_fwd_variant = variant;
     return PK_OK;
 }
 

@@ -42,6 +42,7 @@ extern "C" int pk_debug_read_fwd(long long* out_h) {
 #define PK_TF(i) do { } while (0)
 #endif
 int attn_bwd_tc_status(int* status_h, int clear);  // pk_attn_bwd_tc.cu
+int attn_fwd_ws_status(int* status_h, int clear);  // pk_attn_fwd_ws.cu
 
 namespace tc {
 
@@ -423,6 +424,10 @@ int pk_attn_tc_status(int* status_h, int clear) {
     const int rc = pk::attn_bwd_tc_status(&bwd, clear);
     if (rc != PK_OK) return rc;
     *status_h |= bwd;
+    int ws = 0;
+    const int rc2 = pk::attn_fwd_ws_status(&ws, clear);
+    if (rc2 != PK_OK) return rc2;
+    *status_h |= ws;
     return PK_OK;
 }
 
