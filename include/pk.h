@@ -229,6 +229,10 @@ int pk_attn_force_simt(int on);
  * CTA with P and O kept in tensor memory; 0 = one 128-query tile per CTA. Same results up to
  * rounding; meant for tests and measurements. */
 int pk_attn_fwd_variant(int variant);
+/* The same for the tensor-core backward: 1 (default) = warp-specialised (scores of the next
+ * tiles computed while the current ones are processed, P / dS kept in tensor memory), 0 = one
+ * tile at a time per CTA. */
+int pk_attn_bwd_variant(int variant);
 
 /* ---- embedding / loss --------------------------------------------------------
  * Row gather out[i,:] = table[ids[i],:] (pure copy; table has the out dtype).

@@ -248,6 +248,12 @@ attn_bwd_dkv_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ 
 
 static thread_local int g_attn_last_path = -1;
 static int g_attn_force_simt = 0;
+static int g_attn_bwd_variant = 1;  // 1: warp-specialised backward (pk_attn_bwd_ws.cu), 0: pk_attn_bwd_tc.cu
+int attn_bwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                const void* out, int64_t ldo, const float* lse, const void* dout, int64_t lddo, void* dq, int64_t lddq,
+                void* dk_, int64_t lddk, void* dv, int64_t lddv, float* scratch, int64_t B, int64_t S, int Hq, int Hkv,
+                int dk, float scale, int causal);
+size_t attn_bwd_ws_scratch_bytes(int64_t B, int64_t S, int Hq);
 static int g_attn_fwd_variant = 1;  // 1: warp-specialised forward (pk_attn_fwd_ws.cu), 0: single-tile forward (pk_attn_tc.cu)
 
 int attn_fwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
@@ -367,7 +373,11 @@ int pk_attn_fwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
 }
 
 size_t pk_attn_bwd_scratch_bytes(int64_t B, int64_t S, int Hq) {
-    return static_cast<size_t>(B) * static_cast<size_t>(S) * static_cast<size_t>(Hq) * sizeof(float);
+    // delta [B*S, Hq] for the SIMT and single-tile kernels; two head-major padded arrays for the
+    // warp-specialised ones
+    const size_t plain = static_cast<size_t>(B) * static_cast<size_t>(S) * static_cast<size_t>(Hq) * sizeof(float);
+    const size_t ws = attn_bwd_ws_scratch_bytes(B, S, Hq);
+    return plain > ws ? plain : ws;
 }
 
 int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void* k, int64_t ldk,
@@ -390,6 +400,9 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     if (!g_attn_force_simt && attn_tc_supported(dtype, dk, q, ldq, k, ldk, v, ldv, out, ldo, B, S) &&
         attn_tc_supported(dtype, dk, dout, lddo, dk_, lddk, dv, lddv, dq, lddq, B, S)) {
         g_attn_last_path = 1;
+        if (g_attn_bwd_variant == 1)
+            return attn_bwd_ws(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, dout, lddo, dq, lddq, dk_, lddk,
+                               dv, lddv, a.delta, B, S, Hq, Hkv, dk, scale, causal);
         const int64_t R = B * S;
         attn_delta_kernel<bf16><<<static_cast<unsigned>((R * Hq + 7) / 8), 256, 0, as_stream(stream)>>>(
             static_cast<const bf16*>(out), ldo, static_cast<const bf16*>(dout), lddo, a.delta, R, Hq, dk);
@@ -405,6 +418,11 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
 int pk_attn_last_path(void) { return g_attn_last_path; }
 int pk_attn_force_simt(int on) {
     g_attn_force_simt = on ? 1 : 0;
+    return PK_OK;
+}
+int pk_attn_bwd_variant(int variant) {
+    PK_REQUIRE(variant == 0 || variant == 1, "unknown backward variant");
+    g_attn_bwd_variant = variant;
     return PK_OK;
 }
 int pk_attn_fwd_variant(int variant) {
