@@ -19,8 +19,12 @@
 //   warps 0-7    element-wise work on the even streamed tiles (tensor-memory buffer 0)
 //   warps 8-15   the same on the odd tiles (buffer 1); warps w and w+4 of a group share lane
 //                quadrant w & 3 and split the 64 columns
-//   warp 16      issues every tcgen05.mma: the scores of tile t+2 are computed while the other
-//                group is still working on tile t+1
+//   warps 16, 18, 19  issue the tcgen05.mma instructions, one kind each (gradient products /
+//                S / dP): the scores of tile t+2 are computed while the other group still
+//                works on tile t+1. An issuing thread cannot run ahead of the tensor pipe, so
+//                its barrier waits and address arithmetic would leave the pipe idle; with three
+//                issuers the gaps of one are filled by the others' MMAs. Every accumulator
+//                has one owner and a fixed order.
 //   warp 17      issues every TMA / bulk load
 // Nothing passes through shared memory on the way from the scores to the gradient MMAs.
 // Per-query statistics (-lse log2 e and -delta scale) are kept head-major and padded to a
@@ -163,7 +167,8 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     uint64_t* kv_empty = kv_full + NS;    // [NS]
     uint64_t* s_full = kv_empty + NS;     // [2]
     uint64_t* ds_full = s_full + 2;       // [2]
-    uint64_t* done = ds_full + 2;
+    uint64_t* dq_done = ds_full + 2;      // [2]  dQ of a buffer's tile complete: its dS may be overwritten
+    uint64_t* done = dq_done + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -183,8 +188,9 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(smem_u32(&kv_empty[i]), 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&s_full[i]), 1);
+            mbar_init(smem_u32(&s_full[i]), 2);   // S issuer + dP issuer
             mbar_init(smem_u32(&ds_full[i]), BW_SOFT_WARPS / 2);
+            mbar_init(smem_u32(&dq_done[i]), 1);
         }
         mbar_init(smem_u32(done), 1);
         *abort_flag = 0;
@@ -221,22 +227,47 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         __syncwarp();
       } else if (warp == BW_SOFT_WARPS) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ issuer X: dQ += dS K
         if (lane == 0) {
-            const uint32_t idesc_s = idesc_bf16(BW_COLS, 0, 0);
             const uint32_t idesc_q = idesc_bf16(DK, 0, 1);
-            const uint32_t q_lo = desc_lo_kmajor(sQ), do_lo = desc_lo_kmajor(sDO);
-            const uint32_t k_lo0 = desc_lo_kmajor(sK), v_lo0 = desc_lo_kmajor(sV), kmn_lo0 = desc_lo_mnmajor(sK, CH64);
+            const uint32_t kmn_lo0 = desc_lo_mnmajor(sK, CH64);
             bool ok = true;
-            auto issue_scores = [&](int j) {  // S(j), dP(j) into buffer j & 1
-                const uint32_t st_off = (j % NS) * (L::TILEK >> 4);
-                const uint32_t t = tmem + (j & 1) * 128;
+            for (int j = 0; j < nkv && ok; ++j) {
+                const int bsel = j & 1;
+                ok = mbar_wait(smem_u32(&ds_full[bsel]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                // K_j landed long ago (S(j) used it); this thread observes its barrier too before reading it
+                if (ok) ok = mbar_wait(smem_u32(&kv_full[j % NS]), (j / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (!ok) break;
+                fence_after();
+                const uint32_t kmn = kmn_lo0 + (j % NS) * (L::TILEK >> 4);
+                const uint32_t a = tmem + L::T_DS + bsel * 32;
+#pragma unroll
+                for (int k = 0; k < BW_COLS / 16; ++k)   // contraction over the 64 keys
+                    mma_ts(tmem + L::T_DQ, a + k * 8, kmn + kstep_mnmajor(k), idesc_q, (j > 0 || k > 0) ? 1u : 0u);
+                commit(smem_u32(&kv_empty[j % NS]));  // last use of K_j; V_j was last read by dP(j), complete long before
+                commit(smem_u32(&dq_done[bsel]));
+            }
+            if (ok) commit(smem_u32(done));
+        }
+        __syncwarp();
+      } else {
+        // ------------------------------------------------------------------ issuers Y: S = Q K^T (warp 18), Z: dP = dO V^T (warp 19)
+        // An issuing thread cannot run ahead of the tensor pipe: its barrier waits and address
+        // arithmetic would leave the pipe idle. With three issuers the gaps of one are filled by
+        // the MMAs of the others; every accumulator still has one owner and a fixed order.
+        if (lane == 0) {
+            const bool is_s = warp == BW_SOFT_WARPS + 2;
+            const uint32_t idesc_s = idesc_bf16(BW_COLS, 0, 0);
+            const uint32_t a_lo = desc_lo_kmajor(is_s ? sQ : sDO);
+            const uint32_t b_lo0 = desc_lo_kmajor(is_s ? sK : sV);
+            const uint32_t t_off = is_s ? 0u : 64u;
+            bool ok = true;
+            auto issue = [&](int j) {  // S(j) or dP(j) into buffer j & 1
+                const uint32_t b_lo = b_lo0 + (j % NS) * (L::TILEK >> 4);
+                const uint32_t t = tmem + (j & 1) * 128 + t_off;
 #pragma unroll
                 for (int k = 0; k < DK / 16; ++k)
-                    mma_ss(t, q_lo + kstep_kmajor(k, CH128), k_lo0 + st_off + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < DK / 16; ++k)
-                    mma_ss(t + 64, do_lo + kstep_kmajor(k, CH128), v_lo0 + st_off + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
+                    mma_ss(t, a_lo + kstep_kmajor(k, CH128), b_lo + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
                 commit(smem_u32(&s_full[j & 1]));
             };
             ok = mbar_wait(smem_u32(qdo_full), 0, abort_flag, &g_attn_bwd_ws_status);
@@ -244,32 +275,21 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 ok = mbar_wait(smem_u32(&kv_full[j % NS]), 0, abort_flag, &g_attn_bwd_ws_status);
                 if (ok) {
                     fence_after();
-                    issue_scores(j);
+                    issue(j);
                 }
             }
-            for (int j = 0; j < nkv && ok; ++j) {
-                const int bsel = j & 1;
-                BWS_T(0, 2, bsel * 4 + 0, j);
-                ok = mbar_wait(smem_u32(&ds_full[bsel]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
-                BWS_T(0, 2, bsel * 4 + 1, j);
+            for (int j = 0; j + 2 < nkv && ok; ++j) {
+                // buffer j & 1 is free once the element-wise group has read S(j) and dP(j)
+                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 0, j);
+                ok = mbar_wait(smem_u32(&ds_full[j & 1]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 1, j);
+                if (ok) ok = mbar_wait(smem_u32(&kv_full[(j + 2) % NS]), ((j + 2) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
+                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 2, j);
                 fence_after();
-                const uint32_t kmn = kmn_lo0 + (j % NS) * (L::TILEK >> 4);
-                const uint32_t a = tmem + L::T_DS + bsel * 32;
-#pragma unroll
-                for (int k = 0; k < BW_COLS / 16; ++k)   // dQ += dS K  (contraction over the 64 keys)
-                    mma_ts(tmem + L::T_DQ, a + k * 8, kmn + kstep_mnmajor(k), idesc_q, (j > 0 || k > 0) ? 1u : 0u);
-                commit(smem_u32(&kv_empty[j % NS]));
-                BWS_T(0, 2, bsel * 4 + 2, j);
-                if (j + 2 < nkv) {
-                    ok = mbar_wait(smem_u32(&kv_full[(j + 2) % NS]), ((j + 2) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
-                    if (!ok) break;
-                    fence_after();
-                    issue_scores(j + 2);
-                }
-                BWS_T(0, 2, bsel * 4 + 3, j);
+                issue(j + 2);
+                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 3, j);
             }
-            if (ok) commit(smem_u32(done));
         }
         __syncwarp();
       }
@@ -294,7 +314,10 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int j = grp; j < nkv; j += 2) {
             const int kv0 = j * BW_COLS;
             if (wl == 0 && lane == 0) BWS_T(0, grp, 0, j);
-            ok = mbar_wait(smem_u32(&s_full[grp]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+            // dS of this group's previous tile must have been consumed by its dQ MMAs (issued by
+            // another thread than the scores) before it is overwritten below
+            if (j >= 2) ok = mbar_wait(smem_u32(&dq_done[grp]), ((j - 2) >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+            if (ok) ok = mbar_wait(smem_u32(&s_full[grp]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
             ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tensor-memory accesses are warp-wide
             if (!ok) break;
             if (wl == 0 && lane == 0) BWS_T(0, grp, 1, j);
@@ -388,7 +411,8 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     uint64_t* q_empty = q_full + NS;      // [NS]
     uint64_t* s_full = q_empty + NS;      // [2]
     uint64_t* p_full = s_full + 2;        // [2]
-    uint64_t* done = p_full + 2;
+    uint64_t* g_done = p_full + 2;        // [2]  dV / dK of a buffer's tile issued and complete
+    uint64_t* done = g_done + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const float* xs_base = reinterpret_cast<const float*>(smem + L::OFF_X);
@@ -411,8 +435,9 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(smem_u32(&q_empty[i]), 1);
         }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&s_full[i]), 1);
+            mbar_init(smem_u32(&s_full[i]), 2);   // S^T issuer + dP^T issuer
             mbar_init(smem_u32(&p_full[i]), BW_SOFT_WARPS / 2);
+            mbar_init(smem_u32(&g_done[i]), 1);
         }
         mbar_init(smem_u32(done), 1);
         *abort_flag = 0;
@@ -453,23 +478,50 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         __syncwarp();
       } else if (warp == BW_SOFT_WARPS) {
-        // ------------------------------------------------------------------ MMA issuer
+        // ------------------------------------------------------------------ issuer X: dV += P^T dO, dK += dS^T Q
         if (lane == 0) {
-            const uint32_t idesc_s = idesc_bf16(BW_COLS, 0, 0);
             const uint32_t idesc_g = idesc_bf16(DK, 0, 1);
-            const uint32_t k_lo = desc_lo_kmajor(sK), v_lo = desc_lo_kmajor(sV);
-            const uint32_t q_lo0 = desc_lo_kmajor(sQ), do_lo0 = desc_lo_kmajor(sDO);
             const uint32_t qmn_lo0 = desc_lo_mnmajor(sQ, CH64), domn_lo0 = desc_lo_mnmajor(sDO, CH64);
             bool ok = true;
-            auto issue_scores = [&](int it) {  // S^T = K Q^T, dP^T = V dO^T into buffer it & 1
+            for (int it = 0; it < nit && ok; ++it) {
+                const int bsel = it & 1;
+                ok = mbar_wait(smem_u32(&p_full[bsel]), (it >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                // Q_i / dO_i landed long ago (the scores used them); observe their barrier too
+                if (ok) ok = mbar_wait(smem_u32(&q_full[it % NS]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (!ok) break;
+                fence_after();
                 const uint32_t st_off = (it % NS) * (L::TILEQ >> 4);
-                const uint32_t t = tmem + (it & 1) * 128;
+                const uint32_t a_p = tmem + bsel * 128, a_ds = a_p + 64;
+                const uint32_t acc = it > 0 ? 1u : 0u;
+#pragma unroll
+                for (int k = 0; k < BW_COLS / 16; ++k)   // contraction over the 64 queries
+                    mma_ts(tmem + L::T_DV, a_p + (k >> 1) * 32 + (k & 1) * 8, domn_lo0 + st_off + kstep_mnmajor(k), idesc_g,
+                           k > 0 ? 1u : acc);
+#pragma unroll
+                for (int k = 0; k < BW_COLS / 16; ++k)
+                    mma_ts(tmem + L::T_DK, a_ds + (k >> 1) * 32 + (k & 1) * 8, qmn_lo0 + st_off + kstep_mnmajor(k), idesc_g,
+                           k > 0 ? 1u : acc);
+                commit(smem_u32(&q_empty[it % NS]));
+                commit(smem_u32(&g_done[bsel]));   // P^T / dS^T of this buffer consumed: the score issuers may overwrite it
+            }
+            if (ok) commit(smem_u32(done));
+        }
+        __syncwarp();
+      } else {
+        // ------------------------------------------------------------------ issuers Y: S^T = K Q^T (warp 18), Z: dP^T = V dO^T (warp 19)
+        if (lane == 0) {
+            const bool is_s = warp == BW_SOFT_WARPS + 2;
+            const uint32_t idesc_s = idesc_bf16(BW_COLS, 0, 0);
+            const uint32_t a_lo = desc_lo_kmajor(is_s ? sK : sV);
+            const uint32_t b_lo0 = desc_lo_kmajor(is_s ? sQ : sDO);
+            const uint32_t t_off = is_s ? 0u : 64u;
+            bool ok = true;
+            auto issue = [&](int it) {  // S^T or dP^T of tile `it` into buffer it & 1
+                const uint32_t b_lo = b_lo0 + (it % NS) * (L::TILEQ >> 4);
+                const uint32_t t = tmem + (it & 1) * 128 + t_off;
 #pragma unroll
                 for (int k = 0; k < DK / 16; ++k)
-                    mma_ss(t, k_lo + kstep_kmajor(k, CH128), q_lo0 + st_off + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < DK / 16; ++k)
-                    mma_ss(t + 64, v_lo + kstep_kmajor(k, CH128), do_lo0 + st_off + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
+                    mma_ss(t, a_lo + kstep_kmajor(k, CH128), b_lo + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
                 commit(smem_u32(&s_full[it & 1]));
             };
             ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, &g_attn_bwd_ws_status);
@@ -477,34 +529,17 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 ok = mbar_wait(smem_u32(&q_full[it % NS]), 0, abort_flag, &g_attn_bwd_ws_status);
                 if (ok) {
                     fence_after();
-                    issue_scores(it);
+                    issue(it);
                 }
             }
-            for (int it = 0; it < nit && ok; ++it) {
-                const int bsel = it & 1;
-                ok = mbar_wait(smem_u32(&p_full[bsel]), (it >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+            for (int it = 0; it + 2 < nit && ok; ++it) {
+                // the packed P^T / dS^T of tile `it` live in this buffer until dV / dK of that tile are done
+                ok = mbar_wait(smem_u32(&g_done[it & 1]), (it >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (ok) ok = mbar_wait(smem_u32(&q_full[(it + 2) % NS]), ((it + 2) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
                 fence_after();
-                const uint32_t st_off = (it % NS) * (L::TILEQ >> 4);
-                const uint32_t a_p = tmem + bsel * 128, a_ds = a_p + 64;
-                const uint32_t acc = it > 0 ? 1u : 0u;
-#pragma unroll
-                for (int k = 0; k < BW_COLS / 16; ++k)   // dV += P^T dO   (contraction over the 64 queries)
-                    mma_ts(tmem + L::T_DV, a_p + (k >> 1) * 32 + (k & 1) * 8, domn_lo0 + st_off + kstep_mnmajor(k), idesc_g,
-                           k > 0 ? 1u : acc);
-#pragma unroll
-                for (int k = 0; k < BW_COLS / 16; ++k)   // dK += dS^T Q
-                    mma_ts(tmem + L::T_DK, a_ds + (k >> 1) * 32 + (k & 1) * 8, qmn_lo0 + st_off + kstep_mnmajor(k), idesc_g,
-                           k > 0 ? 1u : acc);
-                commit(smem_u32(&q_empty[it % NS]));
-                if (it + 2 < nit) {
-                    ok = mbar_wait(smem_u32(&q_full[(it + 2) % NS]), ((it + 2) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
-                    if (!ok) break;
-                    fence_after();
-                    issue_scores(it + 2);
-                }
+                issue(it + 2);
             }
-            if (ok) commit(smem_u32(done));
         }
         __syncwarp();
       }
