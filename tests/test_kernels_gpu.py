@@ -408,6 +408,57 @@ def test_attention(pk, dtype, cfg):
     close(dv, vf.grad, gtol)
 
 
+@pytest.mark.parametrize("cfg", [(2, 200, 2, 2, 64, True), (1, 640, 4, 1, 64, True), (2, 333, 2, 2, 128, False),
+                                 (1, 1100, 2, 2, 128, True)])
+def test_attention_tensor_core_variants(pk, cfg):
+    """The two tensor-core forward kernels (one 128-query tile per CTA / two slots per CTA with O
+    kept in tensor memory and rescaled only when a row maximum grows by more than 2^8) and the
+    two backward kernels agree with the fp32 restatement of ops::fused_attention
+    (src/ops.cpp:863-934). Queries are scaled up so that row maxima keep growing along the keys
+    and the in-place rescale of the running output is exercised."""
+    B, S, Hq, Hkv, dk, causal = cfg
+    R = B * S
+    q = rnd(R, Hq * dk, seed=11, lo=-1, hi=1, dtype=torch.bfloat16) * 6
+    k = rnd(R, Hkv * dk, seed=12, lo=-1, hi=1, dtype=torch.bfloat16)
+    # keys grow along the sequence: later tiles raise the running row maximum again and again
+    ramp = torch.linspace(0.2, 3.0, S, device="cuda").repeat(B).unsqueeze(1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    v = rnd(R, Hkv * dk, seed=13, lo=-1, hi=1, dtype=torch.bfloat16)
+    do = rnd(R, Hq * dk, seed=14, lo=-1, hi=1, dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(dk)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    ref = attn_ref(qf, kf, vf, B, S, Hq, Hkv, dk, scale, causal)
+    ref.backward(do.float())
+    outs = {}
+    try:
+        for variant in (0, 1):
+            pkt.check(pk.pk_attn_fwd_variant(variant))
+            pkt.check(pk.pk_attn_bwd_variant(variant))
+            out = torch.empty_like(q)
+            lse = torch.empty(R, Hq, device="cuda")
+            pkt.check(pk.pk_attn_fwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
+                                     Hq * dk, ptr(lse), B, S, Hq, Hkv, dk, scale, int(causal)))
+            assert pk.pk_attn_last_path() == 1
+            dq, dkk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            sc = scratch(pk.pk_attn_bwd_scratch_bytes(B, S, Hq))
+            pkt.check(pk.pk_attn_bwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
+                                     Hq * dk, ptr(lse), ptr(do), Hq * dk, ptr(dq), Hq * dk, ptr(dkk), Hkv * dk,
+                                     ptr(dv), Hkv * dk, ptr(sc), B, S, Hq, Hkv, dk, scale, int(causal)))
+            st = ctypes.c_int(0)
+            pkt.check(pk.pk_attn_tc_status(ctypes.byref(st), 1))
+            assert st.value == 0, f"variant {variant}: a bounded wait gave up"
+            close(out, ref, 2e-2, 2 ** -6)
+            close(dq, qf.grad, 6e-2, 2 ** -5)
+            close(dkk, kf.grad, 6e-2, 2 ** -5)
+            close(dv, vf.grad, 6e-2, 2 ** -5)
+            outs[variant] = (out, lse, dq, dkk, dv)
+    finally:
+        pkt.check(pk.pk_attn_fwd_variant(1))
+        pkt.check(pk.pk_attn_bwd_variant(1))
+    # the log-sum-exp does not depend on how often the running output was rescaled
+    close(outs[0][1], outs[1][1], 1e-3)
+
+
 def test_attention_batch_isolation(pk):
     """Perturbing sequence 2 leaves sequence 1's output bitwise unchanged
     (tests/test_batching.cpp:108-120 of the reference asserts exactly 0.0)."""
