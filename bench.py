@@ -401,6 +401,15 @@ def main():
     step_flops = (L * 4 * (f_blk + f_attn) + 3 * f_head) * tokens_global
     model_flops = 3 * (L * (f_blk + f_attn) + f_head) * tokens_global
     launches = sum(p["launches"] for p in prof.values())
+    # DRAM bytes of one launch of the dominant GEMM shape (the gate / up projection, M x dff x d):
+    # dram__bytes_read + dram__bytes_write of an ncu capture at M = 16384 (105.1 + 230.1 MB for
+    # d 2048, dff 8192; see profiles/), scaled to this run's rows per GPU -- traffic grows in
+    # proportion to M. Only quoted for the shape that was captured.
+    traffic, traffic_note = None, None
+    if args.workload == "c4":
+        traffic = 335.25e6 * (n_local / 16384.0)
+        traffic_note = ("gate/up projection launch (rows x 8192 x 2048): ncu capture at 16384 rows scaled by rows; "
+                        "algorithmic bytes of that launch are 369 MB per 16384 rows")
     line = dict(base)
     line["value"] = tokens_global / (res_ms / args.steps * 1e-3)
     line["ms_per_step"] = res_ms / args.steps
@@ -412,7 +421,7 @@ def main():
     line["gpu_launches"] = int(launches)
     line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM)", "achieved": achieved,
                         "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf if peak_tf else None,
-                        "peak_source": peak_src, "traffic": None,
+                        "peak_source": peak_src, "traffic": traffic, "traffic_note": traffic_note,
                         "share_of_step": g["ms"] / e2e_ms if e2e_ms else None, "launches_timed": g["launches"]}
     line["kernels"] = {k: {"ms_per_step": v["ms"] / args.steps,
                            "tflops": (v["flops"] / (v["ms"] * 1e-3) / 1e12) if v["ms"] > 0 else None,
