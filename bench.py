@@ -11,6 +11,8 @@ the task's baseline file:
   c2  GPT-2-small shape, bf16, batch 16 x 1024
   c3  Qwen2.5-0.5B-shape QLoRA (Q8_0 frozen base, LoRA r=16), bf16, batch 8 x 2048
   c4  Llama-1B shape, bf16, global batch 64 x 4096 (default; sharded by batch over N GPUs)
+  c5  one checkpointed Llama block (d 2048, 16 heads of 128, SwiGLU 5632), bf16, batch 4, --seq S:
+      a step = the recompute + backward of the block (its forward runs untimed before it)
 Keys of the JSON line: metric/value (tokens/s, whole job, inputs resident on the device),
 e2e (same through the public step API with host token buffers), roofline (tcgen05 GEMM:
 achieved TFLOP/s from CUDA events around every launch in the timed region), cpu_baseline
@@ -52,6 +54,9 @@ WORKLOADS = {
                nctx=4096, theta=500000.0, rope_all=1, qlora=0, batch=64, seq=4096,
                name="Llama-1B shape (16L d2048 Hq32/Hkv8 dff8192 V32000), bf16 + fp32 master/AdamW, "
                     "global batch 64 x 4096"),
+    "c5": dict(family="block", dtype="bf16", d=2048, heads=16, kv_heads=16, dff=5632, theta=10000.0, batch=4, seq=4096,
+               layers=1, vocab=0,
+               name="one checkpointed Llama block (d2048, 16 heads of 128, dff5632), bf16, batch 4: recompute + backward"),
 }
 
 
@@ -202,6 +207,7 @@ def main():
     ap.add_argument("--workload", default=os.environ.get("PK_BENCH_WORKLOAD", "c4"), choices=sorted(WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="override the global batch (sequences)")
     ap.add_argument("--layers", type=int, default=0, help="override the number of blocks (small profiling cases)")
+    ap.add_argument("--seq", type=int, default=0, help="override the sequence length (c5 sweep)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=0)
     ap.add_argument("--skip-nockpt", action="store_true", help="do not measure the un-checkpointed step")
@@ -210,13 +216,16 @@ def main():
     w = dict(WORKLOADS[args.workload])
     if args.batch:
         w["batch"] = args.batch
+    if args.seq:
+        w["seq"] = args.seq
+        w["name"] += f" [seq {args.seq}]"
     if args.layers:
         w["layers"] = args.layers
         w["name"] += f" [reduced to {args.layers} block(s)]"
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    sample_tokens = args.cpu_sample_tokens or {"c1": 2048, "c2": 64, "c3": 32, "c4": 32}[args.workload]
+    sample_tokens = args.cpu_sample_tokens or {"c1": 2048, "c2": 64, "c3": 32, "c4": 32, "c5": 32}[args.workload]
     if args.workload == "c1":
         sample_tokens = 256  # per sequence; the harness batches 8 of them below
 
@@ -229,6 +238,10 @@ def main():
     # ------------------------------------------------------------------ reference arm
     if args.impl == "reference":
         if rank != 0:
+            return 0
+        if args.workload == "c5":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference harness has no single-block mode; "
+                              "c5 is checked against a PyTorch fp32 restatement in tests/test_block_gpu.py"}))
             return 0
         if args.workload == "c1":
             # bounded: at most 3 full-size steps (each ~20 s of CPU work)
@@ -267,8 +280,18 @@ def main():
 
     pk = libpk()
     mt.init(local_rank, mt.BF16 if w["dtype"] == "bf16" else mt.FP32)
-    stream = torch.cuda.current_stream()
+    # One explicit (non-default) stream carries everything: the library's kernels, the CUDA events of
+    # the timed regions, and -- as torch's current stream -- the point NCCL's all-reduces wait on
+    # and are waited for. (Handing the library the default stream's null handle would make it fall
+    # back to a private non-blocking stream that nothing else is ordered against.)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
     mt.set_stream(stream.cuda_stream)
+    if w["family"] == "block":
+        rc = run_block(args, w, mt, pk, stream, base, world, rank, torch, np)
+        if world > 1:
+            dist.destroy_process_group()
+        return rc
 
     B, S = w["batch"], w["seq"]
     if B % world:
@@ -448,6 +471,96 @@ def main():
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    return 0
+
+
+def run_block(args, w, mt, pk, stream, base, world, rank, torch, np):
+    """c5: recompute + backward of one checkpointed Llama block; inputs N(0,1), upstream gradient
+    N(0, 1e-3), weights N(0, 0.02) from the library's seeds. Every rank runs an independent replica."""
+    import ctypes
+    B, S, d, H, F = w["batch"], w["seq"], w["d"], w["heads"], w["dff"]
+    R = B * S
+    rng = np.random.RandomState(99 + rank)
+    x = rng.randn(R, d).astype(np.float32)
+    dy = (rng.randn(R, d) * 1e-3).astype(np.float32)
+    m = mt.Model(family="block", d=d, heads=H, kv_heads=w["kv_heads"], dff=F, theta=w["theta"], rope_all=1, seed=0, ckpt=1)
+    m.block_set_input(x, dy, S)
+    for _ in range(args.warmup):
+        m.block_forward()
+        m.block_backward()
+    torch.cuda.synchronize()
+    mt.reset_peak()
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    bwd_ms, fwd_ms = 0.0, 0.0
+    prof_total = {}
+    for _ in range(args.steps):
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record(stream)
+        m.block_forward()
+        e1.record(stream)
+        pk.pk_prof_reset()
+        pk.pk_prof_enable(1)
+        m.block_backward()
+        pk.pk_prof_enable(0)
+        e2.record(stream)
+        torch.cuda.synchronize()
+        fwd_ms += e0.elapsed_time(e1)
+        bwd_ms += e1.elapsed_time(e2)
+        for kind, name in ((0, "gemm_tc"), (1, "gemm_simt"), (2, "attn_fwd"), (3, "attn_bwd")):
+            ms_, work_, n_ = ctypes.c_double(0), ctypes.c_double(0), ctypes.c_int64(0)
+            pk.pk_prof_summary(kind, ctypes.byref(ms_), ctypes.byref(work_), ctypes.byref(n_))
+            t = prof_total.setdefault(name, [0.0, 0.0, 0])
+            t[0] += ms_.value
+            t[1] += work_.value
+            t[2] += n_.value
+    clocks = sampler.stop()
+    # e2e: host arrays in, block output gradient out, every step
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(args.steps):
+        m.block_set_input(x, dy, S)
+        m.block_forward()
+        m.block_backward()
+        dx = m.block_input_grad()
+    t1.record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = t0.elapsed_time(t1) / args.steps
+    peak = mt.mem_stats()["activation_peak"]
+    m.close()
+    if rank != 0:
+        return 0
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak_tf = peaks.get("bf16_tflops", 1676.5)
+    step_ms = bwd_ms / args.steps
+    dk = d // H
+    f_blk = 2 * (4 * d * d + 3 * d * F)
+    f_attn = 4 * (S / 2) * d
+    flops = 3 * (f_blk + f_attn) * R          # recompute (1x) + backward (2x)
+    g = prof_total["gemm_tc"]
+    line = dict(base)
+    line["metric"] = "tokens/s through recompute + backward of one checkpointed block"
+    line["scaling"] = "weak"
+    line["value"] = R * world / (step_ms * 1e-3)
+    line["ms_per_step"] = step_ms
+    line["e2e"] = {"value": R * world / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * R * d * 4 * world,
+                   "d2h_bytes_per_step": R * d * 4 * world, "ms_per_step": e2e_ms,
+                   "note": "block_set_input (host fp32 x and dy) + forward + backward + input gradient read back"}
+    line["clocks"] = clocks
+    line["gpu_launches"] = int(sum(t[2] for t in prof_total.values()))
+    achieved = g[1] / (g[0] * 1e-3) / 1e12 if g[0] > 0 else 0.0
+    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM)", "achieved": achieved, "peak": peak_tf,
+                        "unit": "TFLOP/s", "frac": achieved / peak_tf, "peak_source": "measured (MEASURED_PEAKS.json, burst cuBLAS bf16: "
+                        "the block is timed alone)" if peaks else "fallback", "traffic": None,
+                        "share_of_step": g[0] / bwd_ms if bwd_ms else None}
+    line["kernels"] = {k: {"ms_per_step": v[0] / args.steps, "tflops": (v[1] / (v[0] * 1e-3) / 1e12) if v[0] > 0 else None,
+                           "frac_of_peak": (v[1] / (v[0] * 1e-3) / 1e12 / peak_tf) if v[0] > 0 else None,
+                           "launches_per_step": v[2] / args.steps} for k, v in prof_total.items()}
+    line["step_tflops_executed"] = flops / (step_ms * 1e-3) / 1e12
+    line["config"].update({"forward_ms_untimed": fwd_ms / args.steps, "peak_activation_gib_checkpointed": peak / 2 ** 30,
+                           "head_dim": dk})
+    print(json.dumps(line))
     return 0
 
 

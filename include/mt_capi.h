@@ -60,6 +60,20 @@ int mt_model_step(void* model, const int32_t* ids_h, const int32_t* targets_h, i
                   float loss_scale, int do_backward, float* loss_h);
 /* Variables alive between forward and backward of the last mt_model_step (the
  * reference's memory receipt for checkpointing, include/microtorch/autograd.hpp:61-64). */
+/* ---- one Llama block on its own (spec family=block; keys d, heads, kv_heads, dff, theta,
+ * rope_all, seed, ckpt, pack): the single-block microbenchmark configuration. The block is
+ * include/microtorch/llama.hpp:14-33 / src/llama.cpp:9-60 of the reference; checkpointing is
+ * checkpoint(fn, x) around its forward (src/autograd.cpp:68-102). Parameters are reached
+ * through the mt_model_param_* / mt_model_grad_get calls above.
+ * set_input uploads x [rows, d] and the upstream gradient dy [rows, d] (host fp32; rows =
+ * sequences x seq_len); forward runs y = block(x), keeping only x when checkpointing is on;
+ * backward seeds y with dy: recompute + backward when checkpointed. */
+int mt_block_set_input(void* model, const float* x_h, const float* dy_h, int64_t rows, int64_t seq_len);
+int mt_block_forward(void* model);
+int mt_block_backward(void* model);
+int mt_block_output(void* model, float* y_h);          /* between forward and backward */
+int mt_block_input_grad(void* model, float* dx_h);     /* after backward */
+
 int mt_model_live_after_forward(void* model, int64_t* n_h);
 
 /* AdamW with the reference's defaults unless set (lr 1e-3, betas 0.9/0.999, eps 1e-8, wd 0.01). */

@@ -135,6 +135,9 @@ void backward(const Var& root);
 void zero_grad(const std::vector<Var>& vars);
 
 Var checkpoint(const std::function<Var(const Var&)>& fn, const Var& x);
+// Extension (no counterpart in the reference, whose backward() needs a scalar root): reverse
+// pass from a root of any shape, seeded with an upstream gradient of the same shape.
+void backward_from(const Var& root, const Tensor& upstream);
 
 bool grad_enabled();
 class NoGrad {

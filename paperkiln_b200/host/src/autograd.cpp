@@ -251,6 +251,16 @@ void backward(const Var& root) {
     run_reverse(order, g_release_interior ? 1 : 0, root.get());
 }
 
+void backward_from(const Var& root, const Tensor& upstream) {
+    if (upstream.rows() != root->data.rows() || upstream.cols() != root->data.cols())
+        throw std::runtime_error("backward_from: upstream gradient shape differs from the root's");
+    root->accumulate(upstream);
+    g_segment_counter = 0;
+    std::vector<Var> order;
+    topo(root, order);
+    run_reverse(order, g_release_interior ? 1 : 0, root.get());
+}
+
 Var checkpoint(const std::function<Var(const Var&)>& fn, const Var& x) {
     if (!grad_enabled()) return fn(x);
     Value out_data;

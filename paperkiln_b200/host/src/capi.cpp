@@ -22,6 +22,12 @@ struct Model {
     std::shared_ptr<nn::Llama> llama;
     std::shared_ptr<nn::GPT2> gpt2;
     std::shared_ptr<parity::FlexLM> flex;
+    std::shared_ptr<nn::LlamaBlock> block;   // family "block": one Llama block, no embedding / head
+    Var bx, by;                               // its input leaf and pending output
+    Tensor bdy;                               // upstream gradient
+    std::vector<int> bpos;
+    size_t bseq = 0;
+    bool block_ckpt = false;
     std::vector<std::pair<std::string, Var>> named;   // registration order
     std::vector<Var> params;                          // packed order (blocks first)
     std::vector<std::pair<size_t, size_t>> buckets;   // [first, last] index into params
@@ -33,11 +39,13 @@ struct Model {
     size_t loss_chunk = 8192;
 
     Var forward(const std::vector<int>& ids, size_t seq_len) const {
+        if (block) throw std::runtime_error("a block has no token interface: use mt_block_set_input / forward / backward");
         if (llama) return llama->forward(ids, seq_len);
         if (gpt2) return gpt2->forward(ids, seq_len);
         return flex->forward(ids, seq_len);
     }
     Var loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len) const {
+        if (block) throw std::runtime_error("a block has no token interface: use mt_block_set_input / forward / backward");
         if (loss_chunk == 0) return ops::cross_entropy(forward(ids, seq_len), targets);
         if (llama) return llama->loss(ids, targets, seq_len, loss_chunk);
         if (gpt2) return gpt2->loss(ids, targets, seq_len, loss_chunk);
@@ -47,6 +55,7 @@ struct Model {
         if (llama) llama->checkpoint_blocks = on;
         if (gpt2) gpt2->checkpoint_blocks = on;
         if (flex) flex->checkpoint_blocks = on;
+        block_ckpt = on;
     }
 };
 
@@ -193,8 +202,19 @@ int mt_model_create(const char* spec, void** out) {
             r.finish();
             m->flex = std::make_shared<parity::FlexLM>(c, seed);
             m->named = m->flex->named_parameters();
+        } else if (m->family == "block") {
+            nn::LlamaConfig c;
+            c.d = r.num("d", 128);
+            c.n_heads = r.num("heads", 4);
+            c.n_kv_heads = r.num("kv_heads", 0);
+            c.d_ff = r.num("dff", 512);
+            c.rope_theta = static_cast<float>(r.real("theta", 10000.0));
+            c.rope_all_heads = r.num("rope_all", 1) != 0;
+            r.finish();
+            m->block = std::make_shared<nn::LlamaBlock>(c, seed);
+            m->named = m->block->named_parameters();
         } else {
-            throw std::runtime_error("model spec: family must be llama, gpt2 or flex");
+            throw std::runtime_error("model spec: family must be llama, gpt2, flex or block");
         }
         m->set_ckpt(ckpt);
         // Packed order: block 0, block 1, ..., then everything else.
@@ -298,6 +318,68 @@ int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64
         }
         device::step_end();
         if (loss_h) *loss_h = loss_value;
+    });
+}
+
+// ---- single block (family "block") ----------------------------------------------------
+int mt_block_set_input(void* h, const float* x_h, const float* dy_h, int64_t rows, int64_t seq_len) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!m->block) throw std::runtime_error("mt_block_set_input: the model is not a block");
+        if (rows <= 0 || seq_len <= 0 || rows % seq_len != 0) throw std::runtime_error("rows must be a positive multiple of seq_len");
+        const size_t R = static_cast<size_t>(rows), d = m->block->ln1_w->data.cols();
+        Matrix x(R, d), dy(R, d);
+        std::memcpy(x.data(), x_h, R * d * sizeof(float));
+        std::memcpy(dy.data(), dy_h, R * d * sizeof(float));
+        m->by.reset();
+        m->bx = make_var(Tensor::from_host(x, device::compute_dtype(), device::Pool::Persistent), true);
+        m->bdy = Tensor::from_host(dy, device::compute_dtype(), device::Pool::Persistent);
+        m->bpos.resize(R);
+        for (size_t i = 0; i < R; ++i) m->bpos[i] = static_cast<int>(i % static_cast<size_t>(seq_len));
+        m->bseq = static_cast<size_t>(seq_len);
+    });
+}
+int mt_block_forward(void* h) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!m->block || !m->bx) throw std::runtime_error("mt_block_forward: no block input set");
+        device::step_begin();
+        zero_grad(m->params);
+        m->bx->grad = Value();
+        auto blk = m->block;
+        auto pos = m->bpos;
+        const size_t seq = m->bseq;
+        const size_t live0 = live_variables();
+        m->by = m->block_ckpt ? checkpoint([blk, pos, seq](const Var& in) { return blk->forward(in, pos, seq); }, m->bx)
+                              : blk->forward(m->bx, pos, seq);
+        m->live_after_fwd = static_cast<int64_t>(live_variables() - live0);
+    });
+}
+int mt_block_backward(void* h) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!m->by) throw std::runtime_error("mt_block_backward: no pending forward");
+        Var y = m->by;
+        m->by.reset();
+        backward_from(y, m->bdy);
+        y.reset();
+        device::step_end();
+    });
+}
+int mt_block_output(void* h, float* y_h) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!m->by) throw std::runtime_error("mt_block_output: no pending forward");
+        const Matrix& v = m->by->data.host();
+        std::memcpy(y_h, v.data(), v.size() * sizeof(float));
+    });
+}
+int mt_block_input_grad(void* h, float* dx_h) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!m->bx || m->bx->grad.empty()) throw std::runtime_error("mt_block_input_grad: no gradient yet");
+        const Matrix& v = m->bx->grad.host();
+        std::memcpy(dx_h, v.data(), v.size() * sizeof(float));
     });
 }
 

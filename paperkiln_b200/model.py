@@ -144,6 +144,33 @@ class Model:
     def set_checkpoint(self, on: bool):
         _check(libmt().mt_model_set_checkpoint(self._h, int(on)), "mt_model_set_checkpoint")
 
+    # ---- a single block (family="block") ----
+    def block_set_input(self, x: np.ndarray, dy: np.ndarray, seq_len: int):
+        """x, dy: [rows, d] fp32 host arrays (block input and upstream gradient of its output)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        dy = np.ascontiguousarray(dy, dtype=np.float32)
+        assert x.shape == dy.shape and x.ndim == 2
+        self._block_shape = x.shape
+        _check(libmt().mt_block_set_input(self._h, x.ctypes.data_as(ctypes.c_void_p), dy.ctypes.data_as(ctypes.c_void_p),
+                                          x.shape[0], int(seq_len)), "mt_block_set_input")
+
+    def block_forward(self):
+        _check(libmt().mt_block_forward(self._h), "mt_block_forward")
+
+    def block_backward(self):
+        """Backward of the pending forward: recompute + backward when checkpointing is on."""
+        _check(libmt().mt_block_backward(self._h), "mt_block_backward")
+
+    def block_output(self) -> np.ndarray:
+        out = np.empty(self._block_shape, dtype=np.float32)
+        _check(libmt().mt_block_output(self._h, out.ctypes.data_as(ctypes.c_void_p)), "mt_block_output")
+        return out
+
+    def block_input_grad(self) -> np.ndarray:
+        out = np.empty(self._block_shape, dtype=np.float32)
+        _check(libmt().mt_block_input_grad(self._h, out.ctypes.data_as(ctypes.c_void_p)), "mt_block_input_grad")
+        return out
+
     def set_loss_chunk(self, rows: int):
         """rows > 0: fused head + cross entropy over row chunks (default 8192); 0: separate ops."""
         _check(libmt().mt_model_set_loss_chunk(self._h, int(rows)), "mt_model_set_loss_chunk")
