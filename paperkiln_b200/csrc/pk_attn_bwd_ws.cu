@@ -88,32 +88,44 @@ __device__ __forceinline__ void st16_global(bf16* dst, const uint32_t (&r)[16]) 
 }
 
 // stats[0][bh][s] = -lse log2 e (-inf for padding), stats[1][bh][s] = -delta scale (0 for padding);
-// delta[row, h] = sum_c dout[row, h, c] out[row, h, c]. One warp per (sequence, head, position).
+// delta[row, h] = sum_c dout[row, h, c] out[row, h, c]. dk / 8 lanes per (position, head), 16 bytes
+// of out and of dout per lane; a warp covers consecutive heads of one position, i.e. contiguous memory.
+template <int DK>
 __global__ void __launch_bounds__(256)
 attn_bwd_stats_kernel(const bf16* __restrict__ out, int64_t ldo, const bf16* __restrict__ dout, int64_t lddo,
                       const float* __restrict__ lse, float* __restrict__ lneg, float* __restrict__ dneg, int64_t B,
-                      int64_t S, int64_t S_pad, int Hq, int dk, float scale) {
+                      int64_t S, int64_t S_pad, int Hq, float scale) {
+    constexpr int LPH = DK / 8;              // lanes per (position, head): 8 or 16
+    constexpr int HPW = 32 / LPH;            // heads per warp and iteration
     const int lane = threadIdx.x & 31;
+    const int sub = lane / LPH, li = lane % LPH;
+    const int groups = (Hq + HPW - 1) / HPW;  // warp iterations per position
     const int64_t w = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (w >= B * S_pad * Hq) return;
-    const int h = static_cast<int>(w % Hq);
-    const int64_t s = (w / Hq) % S_pad, b = w / Hq / S_pad;
-    const int64_t o = (b * Hq + h) * S_pad + s;
-    if (s >= S) {
-        if (lane == 0) {
+    if (w >= B * S_pad * groups) return;
+    const int g = static_cast<int>(w % groups);
+    const int64_t s = (w / groups) % S_pad, b = w / groups / S_pad;
+    const int h = g * HPW + sub;
+    const bool live = h < Hq;
+    float acc = 0.0f;
+    if (live && s < S) {
+        const int64_t row = b * S + s;
+        float a[8], d[8];
+        Vec<bf16>::load(out + row * ldo + h * DK + li * 8, a);
+        Vec<bf16>::load(dout + row * lddo + h * DK + li * 8, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc += a[e] * d[e];
+    }
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (live && li == 0) {
+        const int64_t o = (b * Hq + h) * S_pad + s;
+        if (s < S) {
+            lneg[o] = -lse[(b * S + s) * Hq + h] * BW_LOG2E;
+            dneg[o] = -acc * scale;
+        } else {
             lneg[o] = -INFINITY;
             dneg[o] = 0.0f;
         }
-        return;
-    }
-    const int64_t row = b * S + s;
-    float acc = 0.0f;
-    for (int c = lane; c < dk; c += 32)
-        acc += __bfloat162float(out[row * ldo + h * dk + c]) * __bfloat162float(dout[row * lddo + h * dk + c]);
-    acc = warp_sum(acc);
-    if (lane == 0) {
-        lneg[o] = -lse[row * Hq + h] * BW_LOG2E;
-        dneg[o] = -acc * scale;
     }
 }
 
@@ -673,10 +685,18 @@ int attn_bwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int6
     float* lneg = scratch;
     float* dneg = scratch + B * Hq * S_pad;
     PK_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 15u) == 0, "scratch must be 16-byte aligned");
-    const int64_t nw = B * S_pad * Hq;
-    attn_bwd_stats_kernel<<<static_cast<unsigned>((nw + 7) / 8), 256, 0, st>>>(
-        static_cast<const bf16*>(out), ldo, static_cast<const bf16*>(dout), lddo, lse, lneg, dneg, B, S, S_pad, Hq, dk, scale);
-    PK_LAUNCH_CHECK();
+    {
+        const int hpw = 32 / (dk / 8);
+        const int64_t nw = B * S_pad * ((Hq + hpw - 1) / hpw);
+        const unsigned blocks = static_cast<unsigned>((nw + 7) / 8);
+        if (dk == 64)
+            attn_bwd_stats_kernel<64><<<blocks, 256, 0, st>>>(static_cast<const bf16*>(out), ldo, static_cast<const bf16*>(dout),
+                                                              lddo, lse, lneg, dneg, B, S, S_pad, Hq, scale);
+        else
+            attn_bwd_stats_kernel<128><<<blocks, 256, 0, st>>>(static_cast<const bf16*>(out), ldo, static_cast<const bf16*>(dout),
+                                                               lddo, lse, lneg, dneg, B, S, S_pad, Hq, scale);
+        PK_LAUNCH_CHECK();
+    }
 
     CUtensorMap mq128, mdo128, mk64, mv64, mq64, mdo64, mk128, mv128;
     const int64_t R = B * S;

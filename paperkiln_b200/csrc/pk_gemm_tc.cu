@@ -455,7 +455,14 @@ int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int6
     // trans_a == 0: A is [M,K], K contiguous  -> K-major.   trans_a == 1: stored [K,M] -> MN-major.
     // trans_b == 0: B is [K,N], N contiguous  -> MN-major.  trans_b == 1: stored [N,K] -> K-major.
     const int a_mn = ta ? 1 : 0, b_mn = tb ? 0 : 1;
-    const int bn = N > 128 ? 256 : 128;
+    // 128 x 256 tiles unless they would leave SMs without a tile while 128 x 128 tiles would not
+    // (weight gradients of narrow projections: few output tiles, a very long k loop each)
+    const int64_t sms = sm_count();
+    const int64_t rows_t = (M + TC_BM - 1) / TC_BM;
+    const int64_t tiles256 = rows_t * ((N + 255) / 256), tiles128 = rows_t * ((N + 127) / 128);
+    const double fill256 = static_cast<double>(tiles256) / static_cast<double>((tiles256 + sms - 1) / sms * sms);
+    const double fill128 = static_cast<double>(tiles128) / static_cast<double>((tiles128 + sms - 1) / sms * sms);
+    const int bn = (N > 128 && fill256 >= 0.7 * fill128) ? 256 : 128;  // narrow tiles cost more operand traffic: only when the gain is large
     CUtensorMap ma, mb;
     int rc;
     if (!a_mn) rc = make_map(&ma, A, K, M, lda, TC_BK, TC_BM);

@@ -430,6 +430,40 @@ rope_kernel(T* __restrict__ x, int64_t ld, int64_t col0, int n_heads, int half, 
     }
 }
 
+// bf16, 8 elements (4 rotation pairs, 16 bytes) per thread and iteration: same arithmetic per pair
+// as rope_kernel, with 16-byte accesses and 32-bit index arithmetic inside a row.
+__global__ void __launch_bounds__(256)
+rope_vec8_kernel(bf16* __restrict__ x, int64_t ld, int64_t col0, int n_heads, int half, const int32_t* __restrict__ pos,
+                 const float* __restrict__ cs, int64_t n_pos, int64_t R, float sin_sign) {
+    const int vec_per_head = half / 4;                       // 4 pairs per vector
+    const int vec_per_row = n_heads * vec_per_head;
+    const int64_t total = R * vec_per_row;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * 256) {
+        const int64_t row = i / vec_per_row;
+        const int rem = static_cast<int>(i - row * vec_per_row);
+        const int h = rem / vec_per_head, j4 = (rem - h * vec_per_head) * 4;   // first pair of this vector
+        int64_t p = pos[row];
+        if (p < 0) p = 0;
+        if (p >= n_pos) p = n_pos - 1;
+        const float4* c4 = reinterpret_cast<const float4*>(cs + (p * half + j4) * 2);
+        const float4 ca = c4[0], cb = c4[1];                 // (cos, sin) of pairs j4 .. j4+3
+        bf16* px = x + row * ld + col0 + static_cast<int64_t>(h) * (2 * half) + 2 * j4;
+        float v[8];
+        Vec<bf16>::load(px, v);
+        const float cc[4] = {ca.x, ca.z, cb.x, cb.z};
+        const float ss[4] = {ca.y * sin_sign, ca.w * sin_sign, cb.y * sin_sign, cb.w * sin_sign};
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float x0 = v[2 * e], x1 = v[2 * e + 1];
+            o[2 * e] = x0 * cc[e] - x1 * ss[e];
+            o[2 * e + 1] = x0 * ss[e] + x1 * cc[e];
+        }
+        Vec<bf16>::store(px, o);
+    }
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -579,6 +613,16 @@ int pk_rope(void* stream, int dtype, void* x, int64_t ld, int64_t col0, int n_he
     const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
     if (blocks > cap) blocks = cap;
     const float sgn = inverse ? -1.0f : 1.0f;
+    if (dtype == PK_BF16 && half % 4 == 0 && ld % 8 == 0 && col0 % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+        (reinterpret_cast<uintptr_t>(cos_sin) & 15u) == 0) {
+        const int64_t vtotal = total / 4;
+        int64_t vblocks = (vtotal + 255) / 256;
+        if (vblocks > cap) vblocks = cap;
+        rope_vec8_kernel<<<static_cast<unsigned>(vblocks), 256, 0, as_stream(stream)>>>(
+            static_cast<bf16*>(x), ld, col0, n_heads, half, pos, cos_sin, n_pos, R, sgn);
+        PK_LAUNCH_CHECK();
+        return PK_OK;
+    }
     if (dtype == PK_F32)
         rope_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
             static_cast<float*>(x), ld, col0, n_heads, half, pos, cos_sin, n_pos, R, sgn);
