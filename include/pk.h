@@ -106,6 +106,10 @@ int pk_gemm_tc_status(int* status_h, int clear);
 /* Force the SIMT kernels (1) or restore automatic selection (0); used by the
  * parity tests to compare the tensor-core kernel with the SIMT one. */
 int pk_gemm_force_simt(int on);
+/* 1: shapes with enough 256 x 256 output tiles run on CTA pairs (tcgen05 cta_group::2: two SMs
+ * per tile, each loading half of B; default); 0: always one CTA per 128 x 256 tile. pk_gemm_last_path
+ * reports 3 for the pair kernel. Results are identical bit for bit. */
+int pk_gemm_pair_mode(int on);
 
 /* ---- normalisation ----------------------------------------------------------
  * RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w; rinv[R] is saved for backward.

@@ -17,8 +17,14 @@ int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int6
                    const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
                    int accumulate, const float* bias, const void* residual, int64_t ldr);
 
+// CTA-pair kernel (pk_gemm_tc2.cu)
+int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                    const void* B, int64_t ldb, void* C, int64_t ldc, int accumulate, const float* bias, const void* residual,
+                    int64_t ldr);
+
 static thread_local int g_last_path = -1;
 static int g_force_simt = 0;
+static int g_pair_mode = 1;  // 1: 256 x 256 tiles on CTA pairs where the shape has enough of them
 
 constexpr int BM = 64, BN = 64, BK = 16;
 
@@ -151,8 +157,19 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
     cudaStream_t st = as_stream(stream);
     if (ab_dtype == PK_BF16 && !g_force_simt &&
         gemm_tc_supported(c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, residual, ldr, bias)) {
-        g_last_path = 2;
         ProfScope prof(PROF_GEMM_TC, 2.0 * M * N * K, st);
+        if (g_pair_mode) {
+            // worth it only when the 256 x 256 tiles keep the SM pairs busy (same fill rule as the tile width)
+            const int64_t pairs = sm_count() / 2;
+            const int64_t t2 = ((M + 255) / 256) * ((N + 255) / 256);
+            const double fill = static_cast<double>(t2) / static_cast<double>((t2 + pairs - 1) / pairs * pairs);
+            if (N >= 256 && M >= 256 && fill >= 0.8) {
+                g_last_path = 3;
+                return gemm_tc2_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate, bias,
+                                       residual, ldr);
+            }
+        }
+        g_last_path = 2;
         return gemm_tc_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate,
                               bias, residual, ldr);
     }
@@ -173,6 +190,10 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
 int pk_gemm_last_path(void) { return g_last_path; }
 int pk_gemm_force_simt(int on) {
     g_force_simt = on ? 1 : 0;
+    return PK_OK;
+}
+int pk_gemm_pair_mode(int on) {
+    g_pair_mode = on ? 1 : 0;
     return PK_OK;
 }
 

@@ -151,6 +151,8 @@ __host__ __device__ inline uint32_t make_idesc(int n, int a_mn_major, int b_mn_m
     return d;
 }
 
+int gemm_tc2_status(int* status_h, int clear);  // pk_gemm_tc2.cu
+
 template <int BN>
 struct TcCfg {
     static constexpr int A_BYTES = TC_BM * TC_BK * 2;  // 16 KiB
@@ -499,6 +501,10 @@ int pk_gemm_tc_status(int* status_h, int clear) {
         const int zero = 0;
         PK_CHECK_CUDA(cudaMemcpyToSymbol(pk::g_gemm_tc_status, &zero, sizeof(int)));
     }
+    int pair = 0;  // the CTA-pair kernel (pk_gemm_tc2.cu) keeps its own word
+    const int rc = pk::gemm_tc2_status(&pair, clear);
+    if (rc != PK_OK) return rc;
+    *status_h |= pair;
     return PK_OK;
 }
 

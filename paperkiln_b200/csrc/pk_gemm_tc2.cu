@@ -1,0 +1,401 @@
+// bf16 GEMM on a pair of SMs per output tile (tcgen05 cta_group::2).
+//
+// A cluster of two CTAs computes one 256 x 256 tile: CTA r owns rows r*128 .. r*128+127 of the
+// tile (its A slice and its half of the fp32 accumulator, 128 lanes x 256 columns of its own
+// tensor memory) and loads only HALF of the B slice (128 of the 256 columns); one
+// tcgen05.mma.cta_group::2 issued by the leader CTA (rank 0) drives both tensor cores and takes
+// the two halves of B from the two CTAs' shared memories. Per 64-wide k slice a CTA therefore
+// receives 32 KB instead of the 48 KB of the one-CTA kernel (pk_gemm_tc.cu) and its tensor core
+// reads 8 KB instead of 12 KB of operands per MMA, which is what keeps that kernel's tensor pipe
+// near 70 % busy.
+//
+// Roles in each CTA (192 threads):
+//   warp 0      TMA producer: its A slice and its half of B into a 6-stage ring; the loads of
+//               both CTAs complete on the LEADER's "full" barrier (cta_group::2 form of the load,
+//               no multicast)
+//   warp 1      allocates tensor memory (both CTAs); in the leader, one thread issues the MMAs
+//               and signals "stage free" / "accumulator full" in both CTAs with multicast commits
+//   warps 2..5  epilogue: tcgen05.ld of the CTA's own rows, bias / residual / accumulate, stores;
+//               "accumulator free" arrives at the leader's barrier (8 warps of the pair)
+// The k order is fixed and every accumulator column has one issuer: reproducible bit for bit,
+// and identical to the one-CTA kernel's result (same products, same order).
+// Every mbarrier wait is bounded (status word shared with pk_gemm_tc.cu's convention, no trap);
+// both CTAs always reach the two cluster-wide barriers at the start and the end.
+#include <cuda.h>
+
+#include "pk_common.cuh"
+#include "pk_tc.cuh"
+
+namespace pk {
+
+__device__ int g_gemm_tc2_status = 0;
+
+namespace {
+
+using namespace tc;
+
+constexpr int T2_BM = 128;         // rows per CTA; the pair covers 256
+constexpr int T2_BN = 256;
+constexpr int T2_BK = 64;
+constexpr int T2_THREADS = 192;
+constexpr int T2_STAGES = 6;
+constexpr int T2_A_BYTES = T2_BM * T2_BK * 2;          // 16 KiB
+constexpr int T2_B_BYTES = (T2_BN / 2) * T2_BK * 2;    // 16 KiB: this CTA's half of B
+constexpr int T2_STAGE_BYTES = T2_A_BYTES + T2_B_BYTES;
+constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
+
+struct T2Params {
+    int64_t M, N, K;
+    void* C;
+    int64_t ldc;
+    const float* bias;
+    const void* residual;
+    int64_t ldr;
+    int accumulate;
+    int a_mn_major, b_mn_major;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load whose completion is counted on a barrier of the pair's leader
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar)
+        : "memory");
+}
+__device__ __forceinline__ void mma2_ss(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives (once all MMAs issued so far are complete) on the barrier at this offset in BOTH CTAs
+__device__ __forceinline__ void commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
+__host__ __device__ inline uint32_t idesc_pair(int n, int a_mn_major, int b_mn_major) {
+    uint32_t d = 0;
+    d |= 1u << 4;
+    d |= 1u << 7;
+    d |= 1u << 10;
+    d |= static_cast<uint32_t>(a_mn_major & 1) << 15;
+    d |= static_cast<uint32_t>(b_mn_major & 1) << 16;
+    d |= static_cast<uint32_t>(n >> 3) << 17;
+    d |= static_cast<uint32_t>(256 >> 4) << 24;  // M of the pair
+    return d;
+}
+__device__ __forceinline__ bool wait2(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait(bar, parity, abort_flag, &g_gemm_tc2_status);
+}
+
+template <typename TC>
+__device__ __forceinline__ void store8(TC* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<bf16>(bf16* p, const float (&v)[8]) {
+    Vec<bf16>::store(p, v);
+}
+template <typename TC>
+__device__ __forceinline__ void load8(const TC* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
+    Vec<bf16>::load(p, v);
+}
+
+template <typename TC>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const T2Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T2_STAGES * T2_STAGE_BYTES);
+    uint64_t* full_bar = bars;                        // [STAGES]  used in the leader
+    uint64_t* empty_bar = bars + T2_STAGES;           // [STAGES]  one per CTA, both signalled by the leader
+    uint64_t* acc_full = bars + 2 * T2_STAGES;        // [2]       one per CTA, both signalled by the leader
+    uint64_t* acc_empty = bars + 2 * T2_STAGES + 2;   // [2]       used in the leader: 8 epilogue warps of the pair
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * T2_STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+    const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int64_t tiles_m = (p.M + 2 * T2_BM - 1) / (2 * T2_BM), tiles_n = (p.N + T2_BN - 1) / T2_BN;
+    const int64_t n_tiles = tiles_m * tiles_n;
+    const int k_blocks = static_cast<int>((p.K + T2_BK - 1) / T2_BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T2_STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&acc_full[a]), 1);
+            mbar_init(smem_u32(&acc_empty[a]), 8);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+    }
+    fence_before();
+    __syncthreads();
+    cluster_sync_all();   // both CTAs' barriers are initialised before anything remote touches them
+    fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                const int32_t m0 = static_cast<int32_t>((tile / tiles_n) * (2 * T2_BM) + rank * T2_BM);
+                const int32_t n0 = static_cast<int32_t>((tile % tiles_n) * T2_BN + rank * (T2_BN / 2));
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!wait2(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t fb_local = smem_u32(&full_bar[stage]);
+                    const uint32_t fb = map_to_rank(fb_local, 0);   // the leader's barrier counts both CTAs' bytes
+                    if (leader) mbar_expect_tx(fb_local, 2 * T2_STAGE_BYTES);
+                    const uint32_t sa = smem_u32(smem + stage * T2_STAGE_BYTES);
+                    const uint32_t sb = sa + T2_A_BYTES;
+                    const int32_t k0 = kb * T2_BK;
+                    if (!p.a_mn_major) {
+                        tma_load_2d_pair(sa, &map_a, k0, m0, fb);                 // box 64(k) x 128(m)
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < T2_BM / 64; ++c)                      // boxes 64(m) x 64(k)
+                            tma_load_2d_pair(sa + c * 8192, &map_a, m0 + c * 64, k0, fb);
+                    }
+                    if (!p.b_mn_major) {
+                        tma_load_2d_pair(sb, &map_b, k0, n0, fb);                 // box 64(k) x 128(n)
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < (T2_BN / 2) / 64; ++c)                // boxes 64(n) x 64(k)
+                            tma_load_2d_pair(sb + c * 8192, &map_b, n0 + c * 64, k0, fb);
+                    }
+                    if (++stage == T2_STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            const uint32_t idesc = idesc_pair(T2_BN, p.a_mn_major, p.b_mn_major);
+            const uint32_t a_flags = ((p.a_mn_major ? 8192u : 16u) >> 4) << 16, b_flags = ((p.b_mn_major ? 8192u : 16u) >> 4) << 16;
+            const uint32_t a_step = (p.a_mn_major ? 2048u : 32u) >> 4, b_step = (p.b_mn_major ? 2048u : 32u) >> 4;
+            const uint32_t a_lo0 = ((smem_u32(smem) & 0x3ffffu) >> 4) | a_flags;
+            const uint32_t b_lo0 = (((smem_u32(smem) + T2_A_BYTES) & 0x3ffffu) >> 4) | b_flags;
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+                if (!wait2(smem_u32(&acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * T2_BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!wait2(smem_u32(&full_bar[stage]), phase, abort_flag)) { ok = false; break; }
+                    fence_after();
+                    const uint32_t a_lo = a_lo0 + stage * (T2_STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (T2_STAGE_BYTES >> 4);
+#pragma unroll
+                    for (int k = 0; k < T2_BK / 16; ++k)
+                        mma2_ss(d_tmem, a_lo + k * a_step, b_lo + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+                    commit_pair(smem_u32(&empty_bar[stage]));   // frees the stage in both CTAs
+                    if (++stage == T2_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                commit_pair(smem_u32(&acc_full[acc]));          // accumulator complete, both CTAs
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue (warps 2..5, both CTAs)
+        const int quad = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        TC* C = static_cast<TC*>(p.C);
+        const TC* Rsd = static_cast<const TC*>(p.residual);
+        bool ok = true;
+        for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            const int64_t m0 = (tile / tiles_n) * (2 * T2_BM) + rank * T2_BM, n0 = (tile % tiles_n) * T2_BN;
+            ok = wait2(smem_u32(&acc_full[acc]), acc_phase, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fence_after();
+            const int64_t m = m0 + quad * 32 + lane;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * T2_BN);
+#pragma unroll 1
+            for (int ch = 0; ch < T2_BN / 32; ++ch) {
+                const int64_t c0 = n0 + ch * 32;
+                if (c0 >= p.N) break;  // uniform across the warp
+                uint32_t r[32];
+                tmem_ld32(t_row + static_cast<uint32_t>(ch * 32), r);
+                tmem_wait_ld();
+                if (m < p.M) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int64_t c = c0 + g * 8;
+                        if (c < p.N && c + 8 > p.N) {
+                            for (int e = 0; e < 8 && c + e < p.N; ++e) {   // ragged last group
+                                float x = __uint_as_float(r[g * 8 + e]);
+                                if (p.bias) x += p.bias[c + e];
+                                if (Rsd) x += to_f32(Rsd[m * p.ldr + c + e]);
+                                if (p.accumulate) x += to_f32(C[m * p.ldc + c + e]);
+                                C[m * p.ldc + c + e] = from_f32<TC>(x);
+                            }
+                        } else if (c < p.N) {
+                            float v[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]);
+                            if (p.bias) {
+                                float b[8];
+                                load8<float>(p.bias + c, b);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] += b[e];
+                            }
+                            if (Rsd) {
+                                float q[8];
+                                load8<TC>(Rsd + m * p.ldr + c, q);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] += q[e];
+                            }
+                            if (p.accumulate) {
+                                float q[8];
+                                load8<TC>(C + m * p.ldc + c, q);
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) v[e] += q[e];
+                            }
+                            store8<TC>(C + m * p.ldc + c, v);
+                        }
+                    }
+                }
+            }
+            fence_before();
+            __syncwarp();
+            if (lane == 0) remote_arrive(map_to_rank(smem_u32(&acc_empty[acc]), 0));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+    fence_before();
+    __syncthreads();
+    cluster_sync_all();   // no CTA leaves while the other may still signal its barriers or read its shared memory
+    if (warp == 1) {
+        fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
+    }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+template <typename TC>
+int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const T2Params& p) {
+    auto kern = gemm_tc2_kernel<TC>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        PK_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES));
+        attr_set = true;
+    }
+    // how many CTA pairs the GPU can hold at once (SM pairs are formed inside GPCs, so this may be
+    // fewer than half the SM count)
+    static int max_pairs = 0;
+    if (max_pairs == 0) {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3(static_cast<unsigned>(sm_count() / 2 * 2));
+        probe.blockDim = dim3(T2_THREADS);
+        probe.dynamicSmemBytes = T2_SMEM_BYTES;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        probe.attrs = &attr;
+        probe.numAttrs = 1;
+        int n = 0;
+        PK_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &probe));
+        PK_REQUIRE(n > 0, "no CTA pair fits on this GPU");
+        max_pairs = n;
+    }
+    const int64_t tiles = ((p.M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((p.N + T2_BN - 1) / T2_BN);
+    int64_t pairs = max_pairs;
+    if (pairs > tiles) pairs = tiles;
+    kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, p);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+}  // namespace
+
+int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                    const void* B, int64_t ldb, void* C, int64_t ldc, int accumulate, const float* bias, const void* residual,
+                    int64_t ldr) {
+    const int a_mn = ta ? 1 : 0, b_mn = tb ? 0 : 1;
+    CUtensorMap ma, mb;
+    int rc;
+    // same boxes as the one-CTA kernel, except that a CTA takes 128 of the tile's 256 B columns
+    if (!a_mn) rc = make_tensor_map(&ma, A, K, M, lda, T2_BK, T2_BM);
+    else rc = make_tensor_map(&ma, A, M, K, lda, 64, T2_BK);
+    if (rc != PK_OK) return rc;
+    if (!b_mn) rc = make_tensor_map(&mb, B, K, N, ldb, T2_BK, T2_BN / 2);
+    else rc = make_tensor_map(&mb, B, N, K, ldb, 64, T2_BK);
+    if (rc != PK_OK) return rc;
+    T2Params p;
+    p.M = M; p.N = N; p.K = K;
+    p.C = C; p.ldc = ldc;
+    p.bias = bias; p.residual = residual; p.ldr = ldr;
+    p.accumulate = accumulate;
+    p.a_mn_major = a_mn; p.b_mn_major = b_mn;
+    if (c_dtype == PK_F32) return launch2<float>(st, ma, mb, p);
+    return launch2<bf16>(st, ma, mb, p);
+}
+
+int gemm_tc2_status(int* status_h, int clear) {
+    PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, g_gemm_tc2_status, sizeof(int)));
+    if (clear) {
+        const int zero = 0;
+        PK_CHECK_CUDA(cudaMemcpyToSymbol(g_gemm_tc2_status, &zero, sizeof(int)));
+    }
+    return PK_OK;
+}
+
+}  // namespace pk

@@ -281,7 +281,7 @@ def test_gemm_bf16_tensor_core(pk, ta, tb, mnk):
     B = rnd(N, K, seed=2, lo=-1, hi=1, dtype=bf) if tb else rnd(K, N, seed=2, lo=-1, hi=1, dtype=bf)
     ref = (A.t() if ta else A).float() @ (B.t() if tb else B).float()
     C = pkt.gemm(A, B, ta=ta, tb=tb, out_dtype=torch.float32)
-    assert pk.pk_gemm_last_path() == 2, "tensor-core kernel was not selected"
+    assert pk.pk_gemm_last_path() in (2, 3), "tensor-core kernel was not selected"
     st = ctypes.c_int(0)
     pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
     assert st.value == 0, "tensor-core kernel reported a wait that gave up"
@@ -328,7 +328,7 @@ def test_gemm_bf16_tensor_core_ragged(pk, ta, tb, mnk):
     C = padded(M, N, 3, dtype=torch.float32)
     C0 = C.clone()
     pkt.gemm(A, B, ta=ta, tb=tb, C=C, accumulate=True)
-    assert pk.pk_gemm_last_path() == 2, "tensor-core kernel was not selected"
+    assert pk.pk_gemm_last_path() in (2, 3), "tensor-core kernel was not selected"
     close(C, ref + C0, 2e-3 * math.sqrt(max(K, 64) / 64), 1e-3)
     Cb = padded(M, N, 4)
     pkt.gemm(A, B, ta=ta, tb=tb, C=Cb)
@@ -336,6 +336,38 @@ def test_gemm_bf16_tensor_core_ragged(pk, ta, tb, mnk):
     st = ctypes.c_int(0)
     pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
     assert st.value == 0
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096, 512), (4096, 2048 + 40, 304), (3000, 4096, 2048)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False)])
+def test_gemm_cta_pair_kernel(pk, shape, ta, tb):
+    """The CTA-pair kernel (tcgen05 cta_group::2, 256 x 256 tiles, each CTA loading half of B) gives
+    the one-CTA kernel's result bit for bit -- same products, same k order -- for bf16 and fp32
+    outputs, with bias / residual / accumulate epilogues and ragged extents."""
+    M, N, K = shape
+    A = rnd(K, M, seed=1, lo=-1, hi=1, dtype=torch.bfloat16) if ta else rnd(M, K, seed=1, lo=-1, hi=1, dtype=torch.bfloat16)
+    B = rnd(N, K, seed=2, lo=-1, hi=1, dtype=torch.bfloat16) if tb else rnd(K, N, seed=2, lo=-1, hi=1, dtype=torch.bfloat16)
+    bias = rnd(1, N, seed=3).reshape(N)
+    res = rnd(M, N, seed=4, dtype=torch.bfloat16)
+    outs = {}
+    try:
+        for mode in (0, 1):
+            pkt.check(pk.pk_gemm_pair_mode(mode))
+            Cb = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            pkt.gemm(A, B, ta=ta, tb=tb, C=Cb, bias=bias, residual=res)
+            path = pk.pk_gemm_last_path()
+            Cf = torch.ones(M, N, device="cuda")
+            pkt.gemm(A, B, ta=ta, tb=tb, C=Cf, accumulate=True)
+            outs[mode] = (Cb, Cf, path)
+    finally:
+        pkt.check(pk.pk_gemm_pair_mode(1))
+    st = ctypes.c_int(0)
+    pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
+    assert st.value == 0
+    assert outs[0][2] == 2 and outs[1][2] == 3, "the pair kernel was not selected"
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    ref = (A.t() if ta else A).float() @ (B.t() if tb else B).float()
+    close(outs[1][1], ref + 1.0, 2e-3 * math.sqrt(max(K, 64) / 64), 1e-3)
 
 
 def attn_ref(q, k, v, B, S, Hq, Hkv, dk, scale, causal):
