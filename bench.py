@@ -442,7 +442,7 @@ def main():
     line["loss"] = loss
     line["clocks"] = clocks
     line["gpu_launches"] = int(launches)
-    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM)", "achieved": achieved,
+    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM; CTA pairs where the tiles suffice)", "achieved": achieved,
                         "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf if peak_tf else None,
                         "peak_source": peak_src, "traffic": traffic, "traffic_note": traffic_note,
                         "share_of_step": g["ms"] / e2e_ms if e2e_ms else None, "launches_timed": g["launches"]}
@@ -550,7 +550,7 @@ def run_block(args, w, mt, pk, stream, base, world, rank, torch, np):
     line["clocks"] = clocks
     line["gpu_launches"] = int(sum(t[2] for t in prof_total.values()))
     achieved = g[1] / (g[0] * 1e-3) / 1e12 if g[0] > 0 else 0.0
-    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM)", "achieved": achieved, "peak": peak_tf,
+    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM; CTA pairs where the tiles suffice)", "achieved": achieved, "peak": peak_tf,
                         "unit": "TFLOP/s", "frac": achieved / peak_tf, "peak_source": "measured (MEASURED_PEAKS.json, burst cuBLAS bf16: "
                         "the block is timed alone)" if peaks else "fallback", "traffic": None,
                         "share_of_step": g[0] / bwd_ms if bwd_ms else None}
