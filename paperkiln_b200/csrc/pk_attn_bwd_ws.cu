@@ -5,20 +5,23 @@
 // order, so the result is reproducible bit for bit.
 //
 //   dQ kernel     CTA = (128-query tile, head, sequence); streams key tiles of 64:
-//                   S = Q K^T, dP = dO V^T          [128 q x 64 keys], tensor memory, 2 buffers
-//                   dS = P (dP - delta) scale        packed bf16, written back to tensor memory
+//                   S = Q K^T, dP = dO V^T          [128 q x 64 keys], tensor memory, 3 buffers
+//                   dS = P (dP - delta) scale        packed bf16 over the thread's own S columns
 //                   dQ += dS K                        A operand from tensor memory, K MN-major
 //   dK/dV kernel  CTA = (128-key tile, kv head, sequence); streams 64-query tiles of every
 //                 query head of the group, in the transposed form (rows are keys):
-//                   S^T = K Q^T, dP^T = V dO^T       [128 keys x 64 q], tensor memory, 2 buffers
+//                   S^T = K Q^T, dP^T = V dO^T       [128 keys x 64 q], tensor memory, 3 buffers
+//                                                     (2 at head_dim 128, where dV and dK need 256 columns)
 //                   P^T, dS^T                         packed bf16 over the thread's own columns
 //                   dV += P^T dO,  dK += dS^T Q      A from tensor memory, dO / Q MN-major
 //   P is recomputed from the saved log-sum-exp: p = exp2(s c - lse log2 e).
 //
 // Roles in a CTA of 640 threads (one CTA per SM):
-//   warps 0-7    element-wise work on the even streamed tiles (tensor-memory buffer 0)
-//   warps 8-15   the same on the odd tiles (buffer 1); warps w and w+4 of a group share lane
-//                quadrant w & 3 and split the 64 columns
+//   warps 0-7    element-wise work on the even streamed tiles
+//   warps 8-15   the same on the odd tiles; warps w and w+4 of a group share lane quadrant
+//                w & 3 and split the 64 columns. Tile t lives in score buffer t mod 3: the
+//                scores of tile t+3 are issued as soon as tile t is finished, so in steady state
+//                a group finds its next tile's scores already computed
 //   warps 16, 18, 19  issue the tcgen05.mma instructions, one kind each (gradient products /
 //                S / dP): the scores of tile t+2 are computed while the other group still
 //                works on tile t+1. An issuing thread cannot run ahead of the tensor pipe, so
@@ -159,9 +162,12 @@ struct DqLayout {
     static constexpr int OFF_V = OFF_K + NS * TILEK;
     static constexpr int OFF_BAR = OFF_V + NS * TILEK;
     static constexpr int BYTES = OFF_BAR + 256 + 1024;
-    // tensor memory columns: buffer b holds S at b*128 and dP at b*128 + 64
-    static constexpr int T_DQ = 256;
-    static constexpr int T_DS = 256 + DK;                  // + b*32: dS of buffer b, packed bf16
+    // Score buffers in tensor memory: buffer b holds S at b*128 and dP at b*128 + 64. With three of
+    // them the scores of tile j+3 are issued as soon as tile j is finished, so an element-wise group
+    // never waits for the tensor pipe in steady state. dS is packed over the first 16 of each
+    // thread's own 32 S columns.
+    static constexpr int NB = 3;
+    static constexpr int T_DQ = NB * 128;
 };
 
 template <int DK>
@@ -171,16 +177,17 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const WsBwdParams p) {
     using L = DqLayout<DK>;
     constexpr int NS = L::NS;
+    constexpr int NB = L::NB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
     uint64_t* qdo_full = bars;            // Q and dO
     uint64_t* kv_full = bars + 1;         // [NS]
     uint64_t* kv_empty = kv_full + NS;    // [NS]
-    uint64_t* s_full = kv_empty + NS;     // [2]
-    uint64_t* ds_full = s_full + 2;       // [2]
-    uint64_t* dq_done = ds_full + 2;      // [2]  dQ of a buffer's tile complete: its dS may be overwritten
-    uint64_t* done = dq_done + 2;
+    uint64_t* s_full = kv_empty + NS;     // [NB]
+    uint64_t* ds_full = s_full + NB;      // [NB]
+    uint64_t* dq_done = ds_full + NB;     // [NB]  dQ of a buffer's tile complete: the buffer may be overwritten
+    uint64_t* done = dq_done + NB;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -199,7 +206,7 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             mbar_init(smem_u32(&kv_full[i]), 1);
             mbar_init(smem_u32(&kv_empty[i]), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NB; ++i) {
             mbar_init(smem_u32(&s_full[i]), 2);   // S issuer + dP issuer
             mbar_init(smem_u32(&ds_full[i]), BW_SOFT_WARPS / 2);
             mbar_init(smem_u32(&dq_done[i]), 1);
@@ -245,17 +252,18 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint32_t kmn_lo0 = desc_lo_mnmajor(sK, CH64);
             bool ok = true;
             for (int j = 0; j < nkv && ok; ++j) {
-                const int bsel = j & 1;
-                ok = mbar_wait(smem_u32(&ds_full[bsel]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                const int bsel = j % NB;
+                ok = mbar_wait(smem_u32(&ds_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
                 // K_j landed long ago (S(j) used it); this thread observes its barrier too before reading it
                 if (ok) ok = mbar_wait(smem_u32(&kv_full[j % NS]), (j / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
                 fence_after();
                 const uint32_t kmn = kmn_lo0 + (j % NS) * (L::TILEK >> 4);
-                const uint32_t a = tmem + L::T_DS + bsel * 32;
+                const uint32_t a = tmem + bsel * 128;   // packed dS: 16 columns at the start of each half's 32
 #pragma unroll
                 for (int k = 0; k < BW_COLS / 16; ++k)   // contraction over the 64 keys
-                    mma_ts(tmem + L::T_DQ, a + k * 8, kmn + kstep_mnmajor(k), idesc_q, (j > 0 || k > 0) ? 1u : 0u);
+                    mma_ts(tmem + L::T_DQ, a + (k >> 1) * 32 + (k & 1) * 8, kmn + kstep_mnmajor(k), idesc_q,
+                           (j > 0 || k > 0) ? 1u : 0u);
                 commit(smem_u32(&kv_empty[j % NS]));  // last use of K_j; V_j was last read by dP(j), complete long before
                 commit(smem_u32(&dq_done[bsel]));
             }
@@ -274,33 +282,30 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const uint32_t b_lo0 = desc_lo_kmajor(is_s ? sK : sV);
             const uint32_t t_off = is_s ? 0u : 64u;
             bool ok = true;
-            auto issue = [&](int j) {  // S(j) or dP(j) into buffer j & 1
+            auto issue = [&](int j) {  // S(j) or dP(j) into buffer j % NB
                 const uint32_t b_lo = b_lo0 + (j % NS) * (L::TILEK >> 4);
-                const uint32_t t = tmem + (j & 1) * 128 + t_off;
+                const uint32_t t = tmem + (j % NB) * 128 + t_off;
 #pragma unroll
                 for (int k = 0; k < DK / 16; ++k)
                     mma_ss(t, a_lo + kstep_kmajor(k, CH128), b_lo + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
-                commit(smem_u32(&s_full[j & 1]));
+                commit(smem_u32(&s_full[j % NB]));
             };
             ok = mbar_wait(smem_u32(qdo_full), 0, abort_flag, &g_attn_bwd_ws_status);
-            for (int j = 0; j < 2 && j < nkv && ok; ++j) {
+            for (int j = 0; j < NB && j < nkv && ok; ++j) {
                 ok = mbar_wait(smem_u32(&kv_full[j % NS]), 0, abort_flag, &g_attn_bwd_ws_status);
                 if (ok) {
                     fence_after();
                     issue(j);
                 }
             }
-            for (int j = 0; j + 2 < nkv && ok; ++j) {
-                // buffer j & 1 is free once the element-wise group has read S(j) and dP(j)
-                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 0, j);
-                ok = mbar_wait(smem_u32(&ds_full[j & 1]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 1, j);
-                if (ok) ok = mbar_wait(smem_u32(&kv_full[(j + 2) % NS]), ((j + 2) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+            for (int j = 0; j + NB < nkv && ok; ++j) {
+                // buffer j % NB is free once dQ of tile j has consumed the dS packed into it (which also
+                // means that the element-wise group has read S(j) and dP(j))
+                ok = mbar_wait(smem_u32(&dq_done[j % NB]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (ok) ok = mbar_wait(smem_u32(&kv_full[(j + NB) % NS]), ((j + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
-                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 2, j);
                 fence_after();
-                issue(j + 2);
-                if (is_s) BWS_T(0, 2, (j & 1) * 4 + 3, j);
+                issue(j + NB);
             }
         }
         __syncwarp();
@@ -315,9 +320,7 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const int qi = q0 + row;
         const bool row_ok = qi < p.S;
         const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-        const uint32_t t_s = tmem + lane_off + grp * 128 + hf * 32;   // this thread's 32 score columns
-        const uint32_t t_dp = t_s + 64;
-        const uint32_t t_ds = tmem + lane_off + L::T_DS + grp * 32 + hf * 16;
+        const uint32_t t_col = tmem + lane_off + hf * 32;   // + buffer * 128: this thread's 32 score columns
         const int64_t srow = (static_cast<int64_t>(b) * p.Hq + h) * p.S_pad + (row_ok ? qi : 0);
         // rows past the end of the sequence: p = 0 everywhere
         const float neg_lse2 = row_ok ? p.lneg[srow] : -INFINITY;
@@ -326,10 +329,9 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int j = grp; j < nkv; j += 2) {
             const int kv0 = j * BW_COLS;
             if (wl == 0 && lane == 0) BWS_T(0, grp, 0, j);
-            // dS of this group's previous tile must have been consumed by its dQ MMAs (issued by
-            // another thread than the scores) before it is overwritten below
-            if (j >= 2) ok = mbar_wait(smem_u32(&dq_done[grp]), ((j - 2) >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
-            if (ok) ok = mbar_wait(smem_u32(&s_full[grp]), (j >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+            const int bsel = j % NB;
+            const uint32_t t_s = t_col + bsel * 128, t_dp = t_s + 64;
+            ok = mbar_wait(smem_u32(&s_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
             ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tensor-memory accesses are warp-wide
             if (!ok) break;
             if (wl == 0 && lane == 0) BWS_T(0, grp, 1, j);
@@ -356,11 +358,11 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                               p1 * fmaf(__uint_as_float(rd[2 * e + 1]), p.scale, neg_delta_s));
             }
             if (wl == 0 && lane == 0) BWS_T(0, grp, 3, j);
-            tmem_st16(t_ds, pk);
+            tmem_st16(t_s, pk);   // over this thread's own (already read) S columns
             tmem_wait_st();
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ds_full[grp]));
+            if (lane == 0) mbar_arrive(smem_u32(&ds_full[bsel]));
             if (wl == 0 && lane == 0) BWS_T(0, grp, 4, j);
         }
         if (ok) ok = mbar_wait(smem_u32(done), 0, abort_flag, &g_attn_bwd_ws_status);
@@ -403,9 +405,11 @@ struct DkvLayout {
     static constexpr int OFF_BAR = OFF_X + NS * 512;
     static constexpr int BYTES = OFF_BAR + 256 + 1024;
     // tensor memory columns: buffer b holds S^T at b*128 and dP^T at b*128 + 64; P^T / dS^T are
-    // packed over the first 16 of each thread's own 32 columns
-    static constexpr int T_DV = 256;
-    static constexpr int T_DK = 256 + DK;
+    // packed over the first 16 of each thread's own 32 columns. Three buffers where they fit
+    // (head_dim 64), so that the scores of tile t+3 are issued as soon as tile t is finished.
+    static constexpr int NB = DK == 64 ? 3 : 2;
+    static constexpr int T_DV = NB * 128;
+    static constexpr int T_DK = NB * 128 + DK;
 };
 
 template <int DK>
@@ -415,16 +419,17 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const WsBwdParams p) {
     using L = DkvLayout<DK>;
     constexpr int NS = L::NS;
+    constexpr int NB = L::NB;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
     uint64_t* kv_full = bars;
     uint64_t* q_full = bars + 1;          // [NS]  Q_i, dO_i and the statistics of tile i
     uint64_t* q_empty = q_full + NS;      // [NS]
-    uint64_t* s_full = q_empty + NS;      // [2]
-    uint64_t* p_full = s_full + 2;        // [2]
-    uint64_t* g_done = p_full + 2;        // [2]  dV / dK of a buffer's tile issued and complete
-    uint64_t* done = g_done + 2;
+    uint64_t* s_full = q_empty + NS;      // [NB]
+    uint64_t* p_full = s_full + NB;       // [NB]
+    uint64_t* g_done = p_full + NB;       // [NB]  dV / dK of a buffer's tile issued and complete
+    uint64_t* done = g_done + NB;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const float* xs_base = reinterpret_cast<const float*>(smem + L::OFF_X);
@@ -446,7 +451,7 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(smem_u32(&q_full[i]), 1);
             mbar_init(smem_u32(&q_empty[i]), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NB; ++i) {
             mbar_init(smem_u32(&s_full[i]), 2);   // S^T issuer + dP^T issuer
             mbar_init(smem_u32(&p_full[i]), BW_SOFT_WARPS / 2);
             mbar_init(smem_u32(&g_done[i]), 1);
@@ -496,8 +501,8 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint32_t qmn_lo0 = desc_lo_mnmajor(sQ, CH64), domn_lo0 = desc_lo_mnmajor(sDO, CH64);
             bool ok = true;
             for (int it = 0; it < nit && ok; ++it) {
-                const int bsel = it & 1;
-                ok = mbar_wait(smem_u32(&p_full[bsel]), (it >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                const int bsel = it % NB;
+                ok = mbar_wait(smem_u32(&p_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
                 // Q_i / dO_i landed long ago (the scores used them); observe their barrier too
                 if (ok) ok = mbar_wait(smem_u32(&q_full[it % NS]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
@@ -528,29 +533,29 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const uint32_t b_lo0 = desc_lo_kmajor(is_s ? sQ : sDO);
             const uint32_t t_off = is_s ? 0u : 64u;
             bool ok = true;
-            auto issue = [&](int it) {  // S^T or dP^T of tile `it` into buffer it & 1
+            auto issue = [&](int it) {  // S^T or dP^T of tile `it` into buffer it % NB
                 const uint32_t b_lo = b_lo0 + (it % NS) * (L::TILEQ >> 4);
-                const uint32_t t = tmem + (it & 1) * 128 + t_off;
+                const uint32_t t = tmem + (it % NB) * 128 + t_off;
 #pragma unroll
                 for (int k = 0; k < DK / 16; ++k)
                     mma_ss(t, a_lo + kstep_kmajor(k, CH128), b_lo + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
-                commit(smem_u32(&s_full[it & 1]));
+                commit(smem_u32(&s_full[it % NB]));
             };
             ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, &g_attn_bwd_ws_status);
-            for (int it = 0; it < 2 && it < nit && ok; ++it) {
+            for (int it = 0; it < NB && it < nit && ok; ++it) {
                 ok = mbar_wait(smem_u32(&q_full[it % NS]), 0, abort_flag, &g_attn_bwd_ws_status);
                 if (ok) {
                     fence_after();
                     issue(it);
                 }
             }
-            for (int it = 0; it + 2 < nit && ok; ++it) {
+            for (int it = 0; it + NB < nit && ok; ++it) {
                 // the packed P^T / dS^T of tile `it` live in this buffer until dV / dK of that tile are done
-                ok = mbar_wait(smem_u32(&g_done[it & 1]), (it >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (ok) ok = mbar_wait(smem_u32(&q_full[(it + 2) % NS]), ((it + 2) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&g_done[it % NB]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (ok) ok = mbar_wait(smem_u32(&q_full[(it + NB) % NS]), ((it + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
                 fence_after();
-                issue(it + 2);
+                issue(it + NB);
             }
         }
         __syncwarp();
@@ -565,13 +570,14 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int kj = k0 + row;  // this thread's key
         const bool key_ok = kj < p.S;
         const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-        const uint32_t t_s = tmem + lane_off + grp * 128 + hf * 32;   // this thread's 32 columns of S^T
-        const uint32_t t_dp = t_s + 64;
+        const uint32_t t_col = tmem + lane_off + hf * 32;   // + buffer * 128: this thread's 32 columns of S^T
         bool ok = true;
         for (int it = grp; it < nit; it += 2) {
             const int st = it % NS;
             const int q0 = (i_begin + it % per_head) * BW_COLS;
-            ok = mbar_wait(smem_u32(&s_full[grp]), (it >> 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+            const int bsel = it % NB;
+            const uint32_t t_s = t_col + bsel * 128, t_dp = t_s + 64;
+            ok = mbar_wait(smem_u32(&s_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
             // the statistics arrived with Q_i / dO_i: observe that barrier too before reading them
             if (ok) ok = mbar_wait(smem_u32(&q_full[st]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
             ok = __all_sync(0xffffffffu, ok);
@@ -602,7 +608,7 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tmem_wait_st();
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_full[grp]));
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[bsel]));
         }
         if (ok) ok = mbar_wait(smem_u32(done), 0, abort_flag, &g_attn_bwd_ws_status);
         ok = __all_sync(0xffffffffu, ok);
