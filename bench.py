@@ -425,12 +425,12 @@ def main():
     model_flops = 3 * (L * (f_blk + f_attn) + f_head) * tokens_global
     launches = sum(p["launches"] for p in prof.values())
     # DRAM bytes of one launch of the dominant GEMM shape (the gate / up projection, M x dff x d):
-    # dram__bytes_read + dram__bytes_write of an ncu capture at M = 16384 (105.1 + 230.1 MB for
+    # dram__bytes_read + dram__bytes_write of an ncu capture at M = 16384 (113.1 + 231.1 MB for
     # d 2048, dff 8192; see profiles/), scaled to this run's rows per GPU -- traffic grows in
     # proportion to M. Only quoted for the shape that was captured.
     traffic, traffic_note = None, None
     if args.workload == "c4":
-        traffic = 335.25e6 * (n_local / 16384.0)
+        traffic = 344.2e6 * (n_local / 16384.0)
         traffic_note = ("gate/up projection launch (rows x 8192 x 2048): ncu capture at 16384 rows scaled by rows; "
                         "algorithmic bytes of that launch are 369 MB per 16384 rows")
     line = dict(base)
