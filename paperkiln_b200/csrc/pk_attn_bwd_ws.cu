@@ -253,9 +253,10 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             bool ok = true;
             for (int j = 0; j < nkv && ok; ++j) {
                 const int bsel = j % NB;
-                ok = mbar_wait(smem_u32(&ds_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
-                // K_j landed long ago (S(j) used it); this thread observes its barrier too before reading it
-                if (ok) ok = mbar_wait(smem_u32(&kv_full[j % NS]), (j / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                // K_j landed long ago (S(j) used it); this thread observes its barrier too before reading it --
+                // first, so that only the wait on the critical path follows the group's arrival
+                ok = mbar_wait(smem_u32(&kv_full[j % NS]), (j / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (ok) ok = mbar_wait(smem_u32(&ds_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
                 fence_after();
                 const uint32_t kmn = kmn_lo0 + (j % NS) * (L::TILEK >> 4);
@@ -301,8 +302,8 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int j = 0; j + NB < nkv && ok; ++j) {
                 // buffer j % NB is free once dQ of tile j has consumed the dS packed into it (which also
                 // means that the element-wise group has read S(j) and dP(j))
-                ok = mbar_wait(smem_u32(&dq_done[j % NB]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (ok) ok = mbar_wait(smem_u32(&kv_full[(j + NB) % NS]), ((j + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&kv_full[(j + NB) % NS]), ((j + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (ok) ok = mbar_wait(smem_u32(&dq_done[j % NB]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
                 fence_after();
                 issue(j + NB);
@@ -502,9 +503,9 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             bool ok = true;
             for (int it = 0; it < nit && ok; ++it) {
                 const int bsel = it % NB;
-                ok = mbar_wait(smem_u32(&p_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
-                // Q_i / dO_i landed long ago (the scores used them); observe their barrier too
-                if (ok) ok = mbar_wait(smem_u32(&q_full[it % NS]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                // Q_i / dO_i landed long ago (the scores used them); observe their barrier too, first
+                ok = mbar_wait(smem_u32(&q_full[it % NS]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (ok) ok = mbar_wait(smem_u32(&p_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
                 fence_after();
                 const uint32_t st_off = (it % NS) * (L::TILEQ >> 4);
@@ -551,8 +552,8 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             for (int it = 0; it + NB < nit && ok; ++it) {
                 // the packed P^T / dS^T of tile `it` live in this buffer until dV / dK of that tile are done
-                ok = mbar_wait(smem_u32(&g_done[it % NB]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (ok) ok = mbar_wait(smem_u32(&q_full[(it + NB) % NS]), ((it + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&q_full[(it + NB) % NS]), ((it + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (ok) ok = mbar_wait(smem_u32(&g_done[it % NB]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
                 if (!ok) break;
                 fence_after();
                 issue(it + NB);
