@@ -66,7 +66,7 @@ public:
     Var hidden(const std::vector<int>& ids, size_t seq_len = 0) const;
     // cross_entropy(forward(ids), targets) with the head and the loss fused over row chunks.
     Var loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len = 0,
-             size_t chunk_rows = 8192) const;
+             size_t chunk_rows = 16384) const;
 
     LlamaConfig cfg;
     bool checkpoint_blocks = false;

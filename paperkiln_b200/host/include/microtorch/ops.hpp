@@ -34,7 +34,7 @@ Var cross_entropy(const Var& logits, const std::vector<int>& targets);
 // mean cross entropy of (h W) or (h W^T) against targets, computed over row chunks so that the
 // [rows, vocab] logits never exist as a whole; W is [in, out], or [out, in] when transposed_w.
 Var linear_cross_entropy(const Var& h, const Var& W, bool transposed_w, const std::vector<int>& targets,
-                         size_t chunk_rows = 8192);
+                         size_t chunk_rows = 16384);
 // qk is the fused [T, 3d] q|k|v layout. Like the reference (src/ops.cpp:495-511) this
 // rotates the first head_dim columns of q and of k only.
 Var apply_rope(const Var& qk, const std::vector<int>& pos, float theta_base, size_t head_dim);

@@ -36,7 +36,7 @@ struct Model {
     std::unique_ptr<nn::AdamW> opt;
     float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, wd = 0.01f;
     int64_t live_after_fwd = 0;
-    size_t loss_chunk = 8192;
+    size_t loss_chunk = 16384;
 
     Var forward(const std::vector<int>& ids, size_t seq_len) const {
         if (block) throw std::runtime_error("a block has no token interface: use mt_block_set_input / forward / backward");

@@ -686,7 +686,7 @@ Var linear_cross_entropy(const Var& h, const Var& W, bool transposed_w, const st
     if (targets.size() != R) throw std::runtime_error("cross_entropy: one target per row");
     for (int t : targets)
         if (t < 0 || static_cast<size_t>(t) >= V) throw std::runtime_error("cross_entropy: target out of range");
-    if (chunk_rows == 0) chunk_rows = 8192;
+    if (chunk_rows == 0) chunk_rows = 16384;
     const Tensor& ht = h->compute();
     const Tensor& wt = W->compute();
     Tensor dtg = device_ints(targets);

@@ -172,7 +172,7 @@ class Model:
         return out
 
     def set_loss_chunk(self, rows: int):
-        """rows > 0: fused head + cross entropy over row chunks (default 8192); 0: separate ops."""
+        """rows > 0: fused head + cross entropy over row chunks (default 16384); 0: separate ops."""
         _check(libmt().mt_model_set_loss_chunk(self._h, int(rows)), "mt_model_set_loss_chunk")
 
     def step(self, ids, targets, seq_len: int = 0, loss_scale: float = 1.0, backward: bool = True) -> float:
