@@ -1,26 +1,19 @@
-// Flash attention on the tcgen05 tensor cores (bf16 operands, fp32 accumulation in tensor
-// memory), head_dim 64 or 128, causal or full, grouped-query head mapping, B stacked
-// sequences. The score matrix lives only in tensor memory and registers.
+// Flash attention forward on the tcgen05 tensor cores, one 128-query tile per CTA (bf16 operands,
+// fp32 accumulation in tensor memory), head_dim 64 or 128, causal or full, grouped-query head
+// mapping, B stacked sequences. This is forward variant 0 (pk_attn_fwd_variant); the default is
+// the warp-specialised kernel in pk_attn_fwd_ws.cu. The file also holds the tensor-map helper
+// shared by the attention kernels and the combined status word.
 //
-// All three kernels use CTAs of 256 threads working on a 128-row tile: warps w and w+4
-// share tensor-memory lane quadrant w (rows 32w..32w+31) and split the COLUMNS of every
-// tile between them, so thread (row r, half hf) owns row r of the tile and 64 of its 128
-// score columns / half of its head_dim output columns. Thread 0 additionally issues the
-// TMA loads and the MMAs.
-//
-// Forward, per (128-query tile, head, sequence), per 128-key tile:
+// CTAs have 256 threads working on a 128-row tile: warps w and w+4 share tensor-memory lane
+// quadrant w (rows 32w..32w+31) and split the COLUMNS of every tile between them, so thread
+// (row r, half hf) owns row r of the tile and 64 of its 128 score columns / half of its
+// head_dim output columns. Thread 0 additionally issues the TMA loads and the MMAs.
+// Per (128-query tile, head, sequence), per 128-key tile:
 //     S = Q K^T                tcgen05.mma, operands TMA-loaded into 128B-swizzled smem
 //     p = exp2(S*c - m)        one sweep over the thread's 64 columns held in registers; the
 //                              row maximum is combined with the partner thread through smem
 //     O_tile = P V             P written as a bf16 operand tile; V read MN-major (no transpose)
 //     o = o*corr + O_tile      running output in registers, rescaled per tile
-// Backward, two kernels, no atomics (every gradient element has one owner, fixed order):
-//     dQ kernel     per query tile, loops over key tiles: S = Q K^T, dP = dO V^T in tensor
-//                   memory; dS = P (dP - delta) scale -> bf16 smem; dQ += dS K (K MN-major)
-//     dK/dV kernel  per key tile, loops over the query heads of the group and their query
-//                   tiles; dV += P^T dO and dK += dS^T Q take P / dS as MN-major A operands
-//                   (the transpose is a descriptor bit) and dO / Q as MN-major B operands
-//     P is recomputed from the saved log-sum-exp: p = exp2(s*c - lse*log2 e).
 // Every mbarrier wait is bounded (status word, no trap).
 //
 // Semantics: ops::fused_attention of the reference (src/ops.cpp:863-934) applied per head.
