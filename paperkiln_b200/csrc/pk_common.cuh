@@ -79,11 +79,24 @@ template <> struct Vec<float> {
     __device__ __forceinline__ static void store(float* p, const float (&f)[4]) {
         *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
     }
+    // The 16 bytes as loaded, and their conversion: lets a kernel keep a row packed in registers.
+    __device__ __forceinline__ static uint4 load_raw(const float* p) {
+        return *reinterpret_cast<const uint4*>(p);
+    }
+    __device__ __forceinline__ static void unpack(const uint4& v, float (&f)[4]) {
+        f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+        f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+    }
 };
 template <> struct Vec<bf16> {
     static constexpr int N = 8;
+    __device__ __forceinline__ static uint4 load_raw(const bf16* p) {
+        return *reinterpret_cast<const uint4*>(p);
+    }
     __device__ __forceinline__ static void load(const bf16* p, float (&f)[8]) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        unpack(load_raw(p), f);
+    }
+    __device__ __forceinline__ static void unpack(const uint4& v, float (&f)[8]) {
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {

@@ -166,8 +166,12 @@ norm_fwd_generic(const T* __restrict__ x, const float* __restrict__ w, const flo
 }
 
 // ---------------------------------------------------------------- backward, warp per row
-// Shared memory: NORM_WPB x (LN ? 2 : 1) x C floats of per-warp column accumulators,
-// laid out [warp][which][vec-slot][element][lane] so that lanes hit distinct banks.
+// A warp keeps its row packed as loaded (x and dy, 16 bytes per vector) and converts it twice:
+// once for the row sums and the parameter gradients, once for dx. A lane sees the same columns
+// in every row, so its share of dw / dgamma / dbeta accumulates in registers over the warp's
+// rows (row order ascending) when that fits (ACC_REG), else in shared memory; at the end the
+// warps of a block are combined in warp order through shared memory:
+// NORM_WPB x (LN ? 2 : 1) x SLOTS floats, laid out [warp][which][vec-slot][element][lane].
 template <typename T, int VPL, bool LN>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_warp(const T* __restrict__ dy, const T* __restrict__ x, const float* __restrict__ w,
@@ -176,56 +180,75 @@ norm_bwd_warp(const T* __restrict__ dy, const T* __restrict__ x, const float* __
               int64_t R, int64_t C) {
     constexpr int N = Vec<T>::N;
     constexpr int SLOTS = VPL * N * 32;  // >= C
+    constexpr bool ACC_REG = (LN ? 2 : 1) * VPL * N <= 64;
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* acc_w = smem + static_cast<size_t>(warp) * (LN ? 2 : 1) * SLOTS;
     float* acc_b = acc_w + SLOTS;  // only when LN
-    if (want_dparam) {
+    float rw[ACC_REG ? VPL : 1][N], rb[ACC_REG && LN ? VPL : 1][N];
+    if (ACC_REG) {
+#pragma unroll
+        for (int i = 0; i < (ACC_REG ? VPL : 1); ++i)
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                rw[i][e] = 0.0f;
+                if (LN) rb[i][e] = 0.0f;
+            }
+    } else if (want_dparam) {
         for (int i = lane; i < (LN ? 2 : 1) * SLOTS; i += 32) acc_w[i] = 0.0f;
+        __syncwarp();
     }
-    __syncwarp();
     const int64_t total_warps = static_cast<int64_t>(gridDim.x) * NORM_WPB;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * NORM_WPB + warp; row < R; row += total_warps) {
         const T* xr = x + row * C;
         const T* gr = dy + row * C;
-        float xv[VPL][N], gv[VPL][N];
+        uint4 xq[VPL], gq[VPL];
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             const int64_t col = (static_cast<int64_t>(i) * 32 + lane) * N;
             if (col < C) {
-                Vec<T>::load(xr + col, xv[i]);
-                Vec<T>::load(gr + col, gv[i]);
+                xq[i] = Vec<T>::load_raw(xr + col);
+                gq[i] = Vec<T>::load_raw(gr + col);
             } else {
-#pragma unroll
-                for (int e = 0; e < N; ++e) { xv[i][e] = 0.0f; gv[i][e] = 0.0f; }
+                xq[i] = make_uint4(0u, 0u, 0u, 0u);
+                gq[i] = make_uint4(0u, 0u, 0u, 0u);
             }
         }
         const float rs = LN ? stat1[row] : stat0[row];
         const float mu = LN ? stat0[row] : 0.0f;
-        // gv <- dy * w (the gradient reaching the normalised value); xv <- xhat (LN) or x
+        // gw = dy * w is the gradient reaching the normalised value; xh = xhat (LN) or x
         float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
         for (int i = 0; i < VPL; ++i) {
             const int64_t col = (static_cast<int64_t>(i) * 32 + lane) * N;
             if (col < C) {
-                float ww[N];
+                float ww[N], xv[N], gv[N];
                 load_param<N>(w + col, ww);
+                Vec<T>::unpack(xq[i], xv);
+                Vec<T>::unpack(gq[i], gv);
 #pragma unroll
                 for (int e = 0; e < N; ++e) {
-                    const float g = gv[i][e];
-                    const float xh = LN ? (xv[i][e] - mu) * rs : xv[i][e];
+                    const float g = gv[e];
+                    const float xh = LN ? (xv[e] - mu) * rs : xv[e];
                     if (want_dparam) {
-                        const int slot = (i * N + e) * 32 + lane;
-                        if (LN) {
-                            acc_w[slot] += g * xh;
-                            acc_b[slot] += g;
+                        if (ACC_REG) {
+                            if (LN) {
+                                rw[ACC_REG ? i : 0][e] += g * xh;
+                                rb[ACC_REG && LN ? i : 0][e] += g;
+                            } else {
+                                rw[ACC_REG ? i : 0][e] += g * xh * rs;
+                            }
                         } else {
-                            acc_w[slot] += g * xh * rs;
+                            const int slot = (i * N + e) * 32 + lane;
+                            if (LN) {
+                                acc_w[slot] += g * xh;
+                                acc_b[slot] += g;
+                            } else {
+                                acc_w[slot] += g * xh * rs;
+                            }
                         }
                     }
                     const float gw = g * ww[e];
-                    xv[i][e] = xh;
-                    gv[i][e] = gw;
                     if (LN) s1 += gw;
                     s2 += gw * xh;
                 }
@@ -242,11 +265,16 @@ norm_bwd_warp(const T* __restrict__ dy, const T* __restrict__ x, const float* __
             for (int i = 0; i < VPL; ++i) {
                 const int64_t col = (static_cast<int64_t>(i) * 32 + lane) * N;
                 if (col < C) {
-                    float o[N];
+                    float ww[N], xv[N], gv[N], o[N];
+                    load_param<N>(w + col, ww);
+                    Vec<T>::unpack(xq[i], xv);
+                    Vec<T>::unpack(gq[i], gv);
 #pragma unroll
                     for (int e = 0; e < N; ++e) {
-                        if (LN) o[e] = rs * (gv[i][e] - m1 - xv[i][e] * m2);
-                        else o[e] = rs * (gv[i][e] - xv[i][e] * rr * s2 * inv_c);
+                        const float xh = LN ? (xv[e] - mu) * rs : xv[e];
+                        const float gw = gv[e] * ww[e];
+                        if (LN) o[e] = rs * (gw - m1 - xh * m2);
+                        else o[e] = rs * (gw - xh * rr * s2 * inv_c);
                     }
                     Vec<T>::store(dr + col, o);
                 }
@@ -254,6 +282,16 @@ norm_bwd_warp(const T* __restrict__ dy, const T* __restrict__ x, const float* __
         }
     }
     if (!want_dparam) return;
+    if (ACC_REG) {
+#pragma unroll
+        for (int i = 0; i < (ACC_REG ? VPL : 1); ++i)
+#pragma unroll
+            for (int e = 0; e < N; ++e) {
+                const int slot = (i * N + e) * 32 + lane;
+                acc_w[slot] = rw[i][e];
+                if (LN) acc_b[slot] = rb[ACC_REG && LN ? i : 0][e];
+            }
+    }
     __syncthreads();
     // Combine the warps of this block in warp order and write the block's partial row(s).
     float* pw = partial + static_cast<size_t>(blockIdx.x) * (LN ? 2 : 1) * C;
@@ -323,15 +361,39 @@ norm_bwd_generic(const T* __restrict__ dy, const T* __restrict__ x, const float*
     }
 }
 
-// out[c] += sum over blocks of partial[b, which, c], ascending b.
+// out[c] += sum over blocks of partial[b, which, c]. A block of 8 warps owns 32 columns; warp j
+// adds blocks j, j+8, ... in ascending order with four independent running sums (blocks
+// j+8(4i+k) go to sum k), then the four sums and the eight warps are combined in a fixed
+// order, so the result depends only on nblocks.
 __global__ void __launch_bounds__(256)
 norm_dparam_stage2(const float* __restrict__ partial, int nblocks, int nwhich, int which,
                    float* __restrict__ out, int64_t C) {
-    const int64_t c = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-    if (c >= C) return;
-    float acc = 0.0f;
-    for (int b = 0; b < nblocks; ++b) acc += partial[(static_cast<size_t>(b) * nwhich + which) * C + c];
-    out[c] += acc;
+    __shared__ float part[8][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + lane;
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    if (c < C) {
+        const size_t pitch = static_cast<size_t>(nwhich) * C;
+        const float* p = partial + static_cast<size_t>(which) * C + c;
+        int b = warp;
+        for (; b + 24 < nblocks; b += 32) {
+            a0 += p[static_cast<size_t>(b) * pitch];
+            a1 += p[static_cast<size_t>(b + 8) * pitch];
+            a2 += p[static_cast<size_t>(b + 16) * pitch];
+            a3 += p[static_cast<size_t>(b + 24) * pitch];
+        }
+        if (b < nblocks) a0 += p[static_cast<size_t>(b) * pitch];
+        if (b + 8 < nblocks) a1 += p[static_cast<size_t>(b + 8) * pitch];
+        if (b + 16 < nblocks) a2 += p[static_cast<size_t>(b + 16) * pitch];
+    }
+    part[warp][lane] = (a0 + a1) + (a2 + a3);
+    __syncthreads();
+    if (warp == 0 && c < C) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc += part[j][lane];
+        out[c] += acc;
+    }
 }
 
 template <typename T, bool LN>
@@ -357,11 +419,23 @@ int norm_fwd_dispatch(cudaStream_t st, const T* x, const float* w, const float* 
 
 template <typename T, int VPL, bool LN>
 int launch_bwd_warp(cudaStream_t st, const T* dy, const T* x, const float* w, const float* s0,
-                    const float* s1, T* dx, float* partial, int want, int64_t R, int64_t C, int grid) {
+                    const float* s1, T* dx, float* partial, int want, int64_t R, int64_t C, int grid,
+                    int* grid_out) {
     const size_t smem = static_cast<size_t>(NORM_WPB) * (LN ? 2 : 1) * VPL * Vec<T>::N * 32 * sizeof(float);
     auto kern = norm_bwd_warp<T, VPL, LN>;
     if (smem > 48 * 1024)
         PK_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    // The rows are dealt out evenly over the grid, so a grid of more blocks than fit on the
+    // GPU at once ends in a thin second wave: keep it to one wave of resident blocks.
+    static int resident = 0;  // per instantiation; the same on every device of one machine
+    if (resident == 0) {
+        int per_sm = 0;
+        PK_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NORM_THREADS, smem));
+        resident = per_sm > 0 ? per_sm : 1;
+    }
+    const int64_t wave = static_cast<int64_t>(resident) * sm_count();
+    if (grid > wave) grid = static_cast<int>(wave);
+    *grid_out = grid;
     kern<<<grid, NORM_THREADS, smem, st>>>(dy, x, w, s0, s1, dx, partial, want, R, C);
     PK_LAUNCH_CHECK();
     return PK_OK;
@@ -384,10 +458,10 @@ int norm_bwd_dispatch(cudaStream_t st, const T* dy, const T* x, const float* w, 
         if (g > need) g = need;
         grid = static_cast<int>(g);
         switch (vpl) {
-            case 1: rc = launch_bwd_warp<T, 1, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid); break;
-            case 2: rc = launch_bwd_warp<T, 2, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid); break;
-            case 4: rc = launch_bwd_warp<T, 4, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid); break;
-            default: rc = launch_bwd_warp<T, 8, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid); break;
+            case 1: rc = launch_bwd_warp<T, 1, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid, &grid); break;
+            case 2: rc = launch_bwd_warp<T, 2, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid, &grid); break;
+            case 4: rc = launch_bwd_warp<T, 4, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid, &grid); break;
+            default: rc = launch_bwd_warp<T, 8, LN>(st, dy, x, w, s0, s1, dx, partial, want, R, C, grid, &grid); break;
         }
         if (rc != PK_OK) return rc;
     } else {
@@ -398,7 +472,7 @@ int norm_bwd_dispatch(cudaStream_t st, const T* dy, const T* x, const float* w, 
         PK_LAUNCH_CHECK();
     }
     if (want) {
-        const unsigned g2 = static_cast<unsigned>((C + 255) / 256);
+        const unsigned g2 = static_cast<unsigned>((C + 31) / 32);
         if (out0) norm_dparam_stage2<<<g2, 256, 0, st>>>(partial, grid, LN ? 2 : 1, 0, out0, C);
         if (LN && out1) norm_dparam_stage2<<<g2, 256, 0, st>>>(partial, grid, 2, 1, out1, C);
         PK_LAUNCH_CHECK();
