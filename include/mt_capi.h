@@ -79,6 +79,24 @@ int mt_model_live_after_forward(void* model, int64_t* n_h);
 /* AdamW with the reference's defaults unless set (lr 1e-3, betas 0.9/0.999, eps 1e-8, wd 0.01). */
 int mt_model_set_adamw(void* model, float lr, float beta1, float beta2, float eps, float weight_decay);
 int mt_model_optimizer_step(void* model);
+
+/* Gradient accumulation over micro-batches (the reference's trainer loop,
+ * tools/mtstudio.cpp:456-474: zero_grad once, `accum` backward passes pre-scaled by 1/accum,
+ * one optimizer step). With accumulate on, mt_model_step no longer clears the gradients it
+ * finds; the caller clears them with mt_model_zero_grad before the first micro-step and passes
+ * loss_scale = 1/accum. A data-parallel launcher all-reduces on the last micro-step only. */
+int mt_model_set_accumulate(void* model, int on);
+int mt_model_zero_grad(void* model);
+
+/* Optimizer state for checkpoint / resume. The reference saves weights only
+ * (tools/mtstudio.cpp:437-441), so there a resumed run starts its moments from zero; with
+ * these entries a run restored from (parameters, step count, both moments of every parameter)
+ * continues bit-identically. `index` is the index of mt_model_param_info; m_h / v_h hold
+ * rows*cols floats on the host. Moments read as zero before the first optimizer step. */
+int mt_model_optimizer_steps_get(void* model, int64_t* t_h);
+int mt_model_optimizer_steps_set(void* model, int64_t t);
+int mt_model_optimizer_state_get(void* model, int64_t index, float* m_h, float* v_h);
+int mt_model_optimizer_state_set(void* model, int64_t index, const float* m_h, const float* v_h);
 int mt_model_clip_grad_norm(void* model, float max_norm, float* norm_h);
 
 /* Gradient ranges for data parallelism: bucket i < n-1 is the contiguous fp32 gradient

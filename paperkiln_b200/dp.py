@@ -57,8 +57,13 @@ class BucketAllReducer:
         self.n_blocks = len(self.buckets) - 1
         self.pending: List = []
         self.order: List[int] = []  # bucket indices in launch order (for tests)
+        # Under gradient accumulation the buckets are complete only after the last
+        # micro-step: the launcher clears this for the earlier ones.
+        self.enabled = True
 
     def on_segment(self, k: int):
+        if not self.enabled:
+            return
         i = self.n_blocks - 1 - k
         if 0 <= i < self.n_blocks:
             self._launch(i)

@@ -164,6 +164,15 @@ public:
     void zero_grad();
     float lr;
     long steps_taken() const { return t_; }
+    // Checkpointing of the optimizer: the step counter and the two moment estimates of
+    // parameter `index` (position in the constructor's list), `numel` floats each, on the host.
+    // The reference's trainer saves weights only (tools/mtstudio.cpp:437-441), so a resumed
+    // run restarts its moments; these entries let a resumed run continue bit-identically.
+    // Before the first step the moments read as zero, and imported moments are held on the
+    // host until the step that creates the device state.
+    void set_steps_taken(long t) { t_ = t; }
+    void export_state(size_t index, float* m_h, float* v_h);
+    void import_state(size_t index, const float* m_h, const float* v_h);
 
 private:
     struct Run {  // parameters whose data, grad (and shadow) are adjacent in memory
@@ -175,6 +184,9 @@ private:
         Tensor m, v;
     };
     void build_runs();
+    bool locate(size_t index, size_t* run, size_t* offset) const;
+    struct Pending { std::vector<float> m, v; };
+    std::map<size_t, Pending> pending_;
     std::vector<Var> params_;
     std::vector<Run> runs_;
     bool runs_built_ = false;

@@ -37,6 +37,7 @@ struct Model {
     float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, wd = 0.01f;
     int64_t live_after_fwd = 0;
     size_t loss_chunk = 16384;
+    bool accumulate = false;   // mt_model_step keeps the gradients it finds
 
     Var forward(const std::vector<int>& ids, size_t seq_len) const {
         if (block) throw std::runtime_error("a block has no token interface: use mt_block_set_input / forward / backward");
@@ -304,7 +305,7 @@ int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64
         device::step_begin();
         float loss_value = 0.0f;
         if (do_backward) {
-            zero_grad(m->params);
+            if (!m->accumulate) zero_grad(m->params);
             const size_t live0 = live_variables();
             Var loss = m->loss(ids, targets, static_cast<size_t>(seq_len));
             m->live_after_fwd = static_cast<int64_t>(live_variables() - live0);
@@ -394,11 +395,47 @@ int mt_model_set_adamw(void* h, float lr, float b1, float b2, float eps, float w
         m->lr = lr; m->b1 = b1; m->b2 = b2; m->eps = eps; m->wd = wd;
     });
 }
+static nn::AdamW& optimizer(Model* m) {
+    if (!m->opt) m->opt = std::make_unique<nn::AdamW>(m->params, m->lr, m->b1, m->b2, m->eps, m->wd);
+    return *m->opt;
+}
+// The optimizer is built over the packed order; the state entries use the registration
+// order of mt_model_param_info like every other per-parameter entry.
+static size_t optimizer_index(Model* m, int64_t i) {
+    if (i < 0 || static_cast<size_t>(i) >= m->named.size()) throw std::runtime_error("parameter index out of range");
+    const Var& p = m->named[i].second;
+    for (size_t k = 0; k < m->params.size(); ++k)
+        if (m->params[k] == p) return k;
+    throw std::runtime_error("parameter is not trainable");
+}
 int mt_model_optimizer_step(void* h) {
+    return guard([&] { optimizer(M(h)).step(); });
+}
+int mt_model_set_accumulate(void* h, int on) {
+    return guard([&] { M(h)->accumulate = on != 0; });
+}
+int mt_model_zero_grad(void* h) {
+    return guard([&] { zero_grad(M(h)->params); });
+}
+int mt_model_optimizer_steps_get(void* h, int64_t* t) {
+    return guard([&] { *t = M(h)->opt ? static_cast<int64_t>(M(h)->opt->steps_taken()) : 0; });
+}
+int mt_model_optimizer_steps_set(void* h, int64_t t) {
+    return guard([&] {
+        if (t < 0) throw std::runtime_error("negative step count");
+        optimizer(M(h)).set_steps_taken(static_cast<long>(t));
+    });
+}
+int mt_model_optimizer_state_get(void* h, int64_t i, float* m_h, float* v_h) {
     return guard([&] {
         Model* m = M(h);
-        if (!m->opt) m->opt = std::make_unique<nn::AdamW>(m->params, m->lr, m->b1, m->b2, m->eps, m->wd);
-        m->opt->step();
+        optimizer(m).export_state(optimizer_index(m, i), m_h, v_h);
+    });
+}
+int mt_model_optimizer_state_set(void* h, int64_t i, const float* m_h, const float* v_h) {
+    return guard([&] {
+        Model* m = M(h);
+        optimizer(m).import_state(optimizer_index(m, i), m_h, v_h);
     });
 }
 int mt_model_clip_grad_norm(void* h, float max_norm, float* norm) {

@@ -276,8 +276,62 @@ void AdamW::build_runs() {
         r.m = Tensor::zeros(1, r.n, DType::F32, device::Pool::Persistent);
         r.v = Tensor::zeros(1, r.n, DType::F32, device::Pool::Persistent);
         runs_.push_back(std::move(r));
+        // moments imported before this state existed
+        const Run& made = runs_.back();
+        for (size_t k = made.first; k <= made.last; ++k) {
+            auto it = pending_.find(k);
+            if (it == pending_.end()) continue;
+            const size_t off = static_cast<size_t>(params_[k]->data.device().f32() - made.p);
+            const size_t bytes = it->second.m.size() * sizeof(float);
+            check(pk_memcpy_h2d(made.m.f32() + off, it->second.m.data(), bytes, device::stream()), "pk_memcpy_h2d");
+            check(pk_memcpy_h2d(made.v.f32() + off, it->second.v.data(), bytes, device::stream()), "pk_memcpy_h2d");
+            device::synchronize();  // the host vectors go away below
+            pending_.erase(it);
+        }
         i = j;
     }
+}
+
+bool AdamW::locate(size_t index, size_t* run, size_t* offset) const {
+    for (size_t r = 0; r < runs_.size(); ++r) {
+        if (index < runs_[r].first || index > runs_[r].last) continue;
+        *run = r;
+        *offset = static_cast<size_t>(params_[index]->data.device().f32() - runs_[r].p);
+        return true;
+    }
+    return false;
+}
+
+void AdamW::export_state(size_t index, float* m_h, float* v_h) {
+    if (index >= params_.size()) throw std::runtime_error("AdamW: parameter index out of range");
+    const size_t n = params_[index]->data.rows() * params_[index]->data.cols();
+    size_t run = 0, off = 0;
+    if (locate(index, &run, &off)) {
+        check(pk_memcpy_d2h(m_h, runs_[run].m.f32() + off, n * sizeof(float), device::stream()), "pk_memcpy_d2h");
+        check(pk_memcpy_d2h(v_h, runs_[run].v.f32() + off, n * sizeof(float), device::stream()), "pk_memcpy_d2h");
+        device::synchronize();
+        return;
+    }
+    auto it = pending_.find(index);
+    for (size_t k = 0; k < n; ++k) {
+        m_h[k] = it == pending_.end() ? 0.0f : it->second.m[k];
+        v_h[k] = it == pending_.end() ? 0.0f : it->second.v[k];
+    }
+}
+
+void AdamW::import_state(size_t index, const float* m_h, const float* v_h) {
+    if (index >= params_.size()) throw std::runtime_error("AdamW: parameter index out of range");
+    const size_t n = params_[index]->data.rows() * params_[index]->data.cols();
+    size_t run = 0, off = 0;
+    if (locate(index, &run, &off)) {
+        check(pk_memcpy_h2d(runs_[run].m.f32() + off, m_h, n * sizeof(float), device::stream()), "pk_memcpy_h2d");
+        check(pk_memcpy_h2d(runs_[run].v.f32() + off, v_h, n * sizeof(float), device::stream()), "pk_memcpy_h2d");
+        device::synchronize();
+        return;
+    }
+    Pending& pd = pending_[index];
+    pd.m.assign(m_h, m_h + n);
+    pd.v.assign(v_h, v_h + n);
 }
 
 void AdamW::step() {

@@ -203,6 +203,41 @@ class Model:
     def optimizer_step(self):
         _check(libmt().mt_model_optimizer_step(self._h), "mt_model_optimizer_step")
 
+    # ---- gradient accumulation (tools/mtstudio.cpp:456-474 of the reference) ----
+    def set_accumulate(self, on: bool):
+        """With accumulation on, step() adds to the gradients instead of clearing them first."""
+        _check(libmt().mt_model_set_accumulate(self._h, 1 if on else 0), "mt_model_set_accumulate")
+
+    def zero_grad(self):
+        _check(libmt().mt_model_zero_grad(self._h), "mt_model_zero_grad")
+
+    # ---- optimizer state for checkpoint / resume ----
+    def optimizer_steps(self) -> int:
+        t = ctypes.c_int64(0)
+        _check(libmt().mt_model_optimizer_steps_get(self._h, ctypes.byref(t)), "mt_model_optimizer_steps_get")
+        return int(t.value)
+
+    def optimizer_state(self) -> dict:
+        """{"t": steps taken, "m": {name: array}, "v": {name: array}} on the host."""
+        out = {"t": self.optimizer_steps(), "m": {}, "v": {}}
+        for name, i in self._index.items():
+            m = np.empty(self.shapes[i], dtype=np.float32)
+            v = np.empty(self.shapes[i], dtype=np.float32)
+            rc = libmt().mt_model_optimizer_state_get(self._h, i, m.ctypes.data_as(ctypes.c_void_p),
+                                                      v.ctypes.data_as(ctypes.c_void_p))
+            _check(rc, "mt_model_optimizer_state_get")
+            out["m"][name], out["v"][name] = m, v
+        return out
+
+    def load_optimizer_state(self, state: dict):
+        _check(libmt().mt_model_optimizer_steps_set(self._h, int(state["t"])), "mt_model_optimizer_steps_set")
+        for name, i in self._index.items():
+            m = np.ascontiguousarray(state["m"][name], dtype=np.float32).reshape(self.shapes[i])
+            v = np.ascontiguousarray(state["v"][name], dtype=np.float32).reshape(self.shapes[i])
+            rc = libmt().mt_model_optimizer_state_set(self._h, i, m.ctypes.data_as(ctypes.c_void_p),
+                                                      v.ctypes.data_as(ctypes.c_void_p))
+            _check(rc, "mt_model_optimizer_state_set")
+
     def clip_grad_norm(self, max_norm: float) -> float:
         n = ctypes.c_float(0.0)
         _check(libmt().mt_model_clip_grad_norm(self._h, max_norm, ctypes.byref(n)), "mt_model_clip_grad_norm")

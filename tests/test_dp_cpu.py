@@ -91,3 +91,58 @@ def test_two_rank_data_parallel_equals_full_batch(tmp_path):
         # and against the reference's own full-batch gradients
         gold = np.concatenate([z["grad." + n].ravel() for n in order[lo:hi]])
         assert float(np.abs(got[f"b{i}"] - gold).max()) < 1e-4
+
+
+def _accum_stream(vocab, n):
+    return np.random.RandomState(4321).randint(0, vocab, size=n + 1).astype(np.int32)
+
+
+def _worker_accum(rank, world, port, out_dir):
+    """Two micro-batches per rank: gradients add up locally, the hook is muted for the first
+    micro-batch and the buckets are exchanged once, during the last one."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        z = np.load(GOLDEN / "llama_tiny_ckpt.npz")
+        a = json.loads(bytes(z["meta_json"]).decode())["args"]
+        params = {k[len("param."):]: z[k] for k in z.files if k.startswith("param.")}
+        B, S, accum = 4, a["seq"], 2
+        ids, targets = dp.shard_tokens(_accum_stream(a["vocab"], B * S), B, S, rank, world)
+        orc = O.StepOracle("llama", params, heads=a["heads"], layers=a["layers"])
+        order, bounds = _bucket_layout(sorted(params), None, a["layers"])
+        buckets = [torch.zeros(sum(params[n].size for n in order[lo:hi]), dtype=torch.float32) for lo, hi in bounds]
+        red = dp.BucketAllReducer(buckets)
+        n_micro = len(ids) // accum
+        for k in range(accum):
+            red.enabled = k == accum - 1
+            sl = slice(k * n_micro, (k + 1) * n_micro)
+            _, grads = orc.step(ids[sl], targets[sl], seq_len=S)
+            for b, (lo, hi) in zip(buckets, bounds):
+                flat = np.concatenate([grads[n].ravel() for n in order[lo:hi]]) / (world * accum)
+                b += torch.from_numpy(flat.astype(np.float32))
+            for seg in range(a["layers"]):
+                red.on_segment(seg)
+            assert len(red.order) == (a["layers"] if red.enabled else 0)
+        red.finish()
+        if rank == 0:
+            np.savez(Path(out_dir) / "dp_accum.npz", **{f"b{i}": b.numpy() for i, b in enumerate(buckets)})
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(180)
+def test_two_rank_accumulation_exchanges_once_and_equals_full_batch(tmp_path):
+    world = 2
+    mp.spawn(_worker_accum, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    got = np.load(tmp_path / "dp_accum.npz")
+    z = np.load(GOLDEN / "llama_tiny_ckpt.npz")
+    a = json.loads(bytes(z["meta_json"]).decode())["args"]
+    params = {k[len("param."):]: z[k] for k in z.files if k.startswith("param.")}
+    stream = _accum_stream(a["vocab"], 4 * a["seq"])
+    orc = O.StepOracle("llama", params, heads=a["heads"], layers=a["layers"])
+    _, grads = orc.step(stream[:-1], stream[1:], seq_len=a["seq"])
+    order, bounds = _bucket_layout(sorted(params), None, a["layers"])
+    for i, (lo, hi) in enumerate(bounds):
+        ref = np.concatenate([grads[n].ravel() for n in order[lo:hi]])
+        assert float(np.abs(got[f"b{i}"] - ref).max()) < 1e-5
