@@ -47,6 +47,111 @@ embedding_bwd_kernel(const T* __restrict__ dy, const int32_t* __restrict__ order
     }
 }
 
+// One block per row, the row read ONCE: thread t keeps vectors t, t + blockDim, ... (at most
+// CE_VPT of them, packed as loaded) in registers across the three phases (max, sum of exp,
+// write). Used when the row fits: V / N <= blockDim * CE_VPT; longer rows take the sweep kernel
+// below (same arithmetic per element; the threads' partial sums group differently).
+constexpr int CE_VPT = 8;
+
+// exp(x - mx): fp32 logits take expf (the reference's std::exp to within an ulp or two); bf16
+// logits carry 8 bits, so ex2.approx of the pre-scaled difference is far inside their noise.
+template <typename T> struct CeExp {
+    float mx;
+    __device__ __forceinline__ explicit CeExp(float m) : mx(m) {}
+    __device__ __forceinline__ float operator()(float x) const { return expf(x - mx); }
+};
+template <> struct CeExp<bf16> {
+    float neg_mx2;
+    __device__ __forceinline__ explicit CeExp(float m) : neg_mx2(-m * 1.4426950408889634f) {}
+    __device__ __forceinline__ float operator()(float x) const {
+        float y;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fmaf(x, 1.4426950408889634f, neg_mx2)));
+        return y;
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(512, 2)
+cross_entropy_row_kernel(T* __restrict__ logits, int64_t ld, const int32_t* __restrict__ targets,
+                         float* __restrict__ row_loss, int64_t R, int64_t V, float gscale, int want_grad,
+                         int32_t* status) {
+    constexpr int N = Vec<T>::N;
+    __shared__ float red[32];
+    const int64_t nv = V / N;
+    for (int64_t row = blockIdx.x; row < R; row += gridDim.x) {
+        T* lr = logits + row * ld;
+        uint4 raw[CE_VPT];
+#pragma unroll
+        for (int k = 0; k < CE_VPT; ++k) {
+            const int64_t i = threadIdx.x + static_cast<int64_t>(k) * blockDim.x;
+            if (i < nv) raw[k] = Vec<T>::load_raw(lr + i * N);
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int k = 0; k < CE_VPT; ++k) {
+            const int64_t i = threadIdx.x + static_cast<int64_t>(k) * blockDim.x;
+            if (i < nv) {
+                float f[N];
+                Vec<T>::unpack(raw[k], f);
+#pragma unroll
+                for (int e = 0; e < N; ++e) mx = fmaxf(mx, f[e]);
+            }
+        }
+        for (int64_t c = nv * N + threadIdx.x; c < V; c += blockDim.x) mx = fmaxf(mx, to_f32(lr[c]));
+        mx = block_max(mx, red);
+        const CeExp<T> ex(mx);
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < CE_VPT; ++k) {
+            const int64_t i = threadIdx.x + static_cast<int64_t>(k) * blockDim.x;
+            if (i < nv) {
+                float f[N];
+                Vec<T>::unpack(raw[k], f);
+#pragma unroll
+                for (int e = 0; e < N; ++e) sum += ex(f[e]);
+            }
+        }
+        for (int64_t c = nv * N + threadIdx.x; c < V; c += blockDim.x) sum += ex(to_f32(lr[c]));
+        sum = block_sum(sum, red);
+        int64_t t = targets[row];
+        const bool ok = t >= 0 && t < V;
+        if (!ok) {
+            if (threadIdx.x == 0 && status) atomicOr(status, PK_ERR_INDEX);
+            t = 0;
+        }
+        if (threadIdx.x == 0) {
+            const float pt = ex(to_f32(lr[t])) / sum;
+            row_loss[row] = ok ? -logf(fmaxf(pt, 1e-12f)) : 0.0f;
+        }
+        if (want_grad) {
+            __syncthreads();  // lr[t] has been read before anyone overwrites it
+            const float inv = 1.0f / sum;
+#pragma unroll
+            for (int k = 0; k < CE_VPT; ++k) {
+                const int64_t i = threadIdx.x + static_cast<int64_t>(k) * blockDim.x;
+                if (i < nv) {
+                    float f[N];
+                    Vec<T>::unpack(raw[k], f);
+                    const int64_t te = t - i * N;  // the target's slot in this vector, if any
+#pragma unroll
+                    for (int e = 0; e < N; ++e) {
+                        float p = ex(f[e]) * inv;
+                        if (te == e) p -= 1.0f;
+                        f[e] = p * gscale;
+                    }
+                    Vec<T>::store(lr + i * N, f);
+                }
+            }
+            for (int64_t c = nv * N + threadIdx.x; c < V; c += blockDim.x) {
+                float p = ex(to_f32(lr[c])) * inv;
+                if (c == t) p -= 1.0f;
+                lr[c] = from_f32<T>(p * gscale);
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // One block per row. Three sweeps over the row (max, sum of exp, write), the last two
 // served from L2. p = exp(l - max) / sum; loss = -log(max(p_t, 1e-12)).
 template <typename T>
@@ -68,14 +173,15 @@ cross_entropy_kernel(T* __restrict__ logits, int64_t ld, const int32_t* __restri
         }
         for (int64_t c = nv * N + threadIdx.x; c < V; c += blockDim.x) mx = fmaxf(mx, to_f32(lr[c]));
         mx = block_max(mx, red);
+        const CeExp<T> ex(mx);
         float sum = 0.0f;
         for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) {
             float f[N];
             Vec<T>::load(lr + i * N, f);
 #pragma unroll
-            for (int e = 0; e < N; ++e) sum += expf(f[e] - mx);
+            for (int e = 0; e < N; ++e) sum += ex(f[e]);
         }
-        for (int64_t c = nv * N + threadIdx.x; c < V; c += blockDim.x) sum += expf(to_f32(lr[c]) - mx);
+        for (int64_t c = nv * N + threadIdx.x; c < V; c += blockDim.x) sum += ex(to_f32(lr[c]));
         sum = block_sum(sum, red);
         int64_t t = targets[row];
         const bool ok = t >= 0 && t < V;
@@ -84,24 +190,25 @@ cross_entropy_kernel(T* __restrict__ logits, int64_t ld, const int32_t* __restri
             t = 0;
         }
         if (threadIdx.x == 0) {
-            const float pt = expf(to_f32(lr[t]) - mx) / sum;
+            const float pt = ex(to_f32(lr[t])) / sum;
             row_loss[row] = ok ? -logf(fmaxf(pt, 1e-12f)) : 0.0f;
         }
         if (want_grad) {
             __syncthreads();  // lr[t] has been read before anyone overwrites it
+            const float inv = 1.0f / sum;
             for (int64_t i = threadIdx.x; i < nv; i += blockDim.x) {
                 float f[N];
                 Vec<T>::load(lr + i * N, f);
 #pragma unroll
                 for (int e = 0; e < N; ++e) {
-                    float p = expf(f[e] - mx) / sum;
+                    float p = ex(f[e]) * inv;
                     if (i * N + e == t) p -= 1.0f;
                     f[e] = p * gscale;
                 }
                 Vec<T>::store(lr + i * N, f);
             }
             for (int64_t c = nv * N + threadIdx.x; c < V; c += blockDim.x) {
-                float p = expf(to_f32(lr[c]) - mx) / sum;
+                float p = ex(to_f32(lr[c])) * inv;
                 if (c == t) p -= 1.0f;
                 lr[c] = from_f32<T>(p * gscale);
             }
@@ -205,11 +312,23 @@ int pk_cross_entropy(void* stream, int dtype, void* logits, int64_t ld, const in
     if (R == 0) return PK_OK;
     PK_REQUIRE(logits && targets && row_loss, "null pointer");
     const int nvec = dtype == PK_F32 ? 4 : 8;
-    const bool vec = V % nvec == 0 && ld % nvec == 0 && aligned16(logits);
+    // rows start on 16-byte boundaries when ld is a multiple of the vector width; a ragged
+    // tail of V is handled element by element
+    const bool vec = ld % nvec == 0 && aligned16(logits);
     int64_t blocks = R;
     const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
     if (blocks > cap) blocks = cap;
     const int threads = V >= 4096 ? 512 : (V >= 1024 ? 256 : 128);
+    if (vec && V / nvec <= static_cast<int64_t>(threads) * CE_VPT) {
+        if (dtype == PK_F32)
+            cross_entropy_row_kernel<float><<<static_cast<unsigned>(blocks), threads, 0, as_stream(stream)>>>(
+                static_cast<float*>(logits), ld, targets, row_loss, R, V, grad_scale, want_grad, status);
+        else
+            cross_entropy_row_kernel<bf16><<<static_cast<unsigned>(blocks), threads, 0, as_stream(stream)>>>(
+                static_cast<bf16*>(logits), ld, targets, row_loss, R, V, grad_scale, want_grad, status);
+        PK_LAUNCH_CHECK();
+        return PK_OK;
+    }
     if (dtype == PK_F32)
         cross_entropy_kernel<float><<<static_cast<unsigned>(blocks), threads, 0, as_stream(stream)>>>(
             static_cast<float*>(logits), ld, targets, row_loss, R, V, grad_scale, want_grad, status, vec);
