@@ -110,6 +110,17 @@ int pk_gemm_force_simt(int on);
  * per tile, each loading half of B; default); 0: always one CTA per 128 x 256 tile. pk_gemm_last_path
  * reports 3 for the pair kernel. Results are identical bit for bit. */
 int pk_gemm_pair_mode(int on);
+/* Split-K for products with few output tiles and a long k extent (the weight gradients of
+ * narrow projections: dW[d, dkv] = X^T dY over all rows): the k range is cut into up to 8 parts
+ * that run side by side, each writing an fp32 partial tile into the caller's workspace, and a
+ * second kernel adds the partials in ascending order (so the result is reproducible) together
+ * with bias / residual / accumulate. Off until a workspace is given (ptr 16-byte aligned, device
+ * memory; null switches it off); 128 MiB covers every shape of the configurations in this repo.
+ * The workspace is shared by all calls: they must be issued on one stream. No counterpart in the
+ * reference, whose device::gemm is a single SIMT kernel (src/cuda_resident.cu:226-263).
+ * pk_gemm_last_splits: parts used by the last tensor-core launch of this thread (1 = not split). */
+int pk_gemm_set_workspace(void* ptr, size_t bytes);
+int pk_gemm_last_splits(void);
 
 /* ---- normalisation ----------------------------------------------------------
  * RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w; rinv[R] is saved for backward.

@@ -59,6 +59,16 @@ struct ProfScope {
 // kernels are sized in multiples of it.
 int sm_count();
 
+// Split-K support shared by the two tensor-core GEMM kernels (defined with the one-CTA kernel):
+// the caller's workspace, the second stage that adds `splits` fp32 partial slabs in ascending
+// order and applies bias / residual / accumulate, and the count reported by pk_gemm_last_splits.
+float* gemm_splitk_workspace(size_t* bytes);
+int gemm_splitk_reduce(cudaStream_t st, int c_dtype, const float* partial, int splits, int64_t slab, int64_t pstride,
+                       int64_t M, int64_t N, void* C, int64_t ldc, int accumulate, const float* bias,
+                       const void* residual, int64_t ldr);
+void gemm_note_splits(int splits);
+
+
 typedef __nv_bfloat16 bf16;
 
 // ---- scalar conversions -----------------------------------------------------

@@ -41,6 +41,13 @@ struct TcParams {
     int64_t ldr;
     int accumulate;
     int a_mn_major, b_mn_major;  // 0: K-major, 1: MN-major
+    // Split-K (few output tiles, long k loop): work item w covers tile w % n_tiles and k blocks
+    // [split * kb_per_split, ...) with split = w / n_tiles, and writes its fp32 partial tile to
+    // partial + split * slab (row stride pstride); splitk_reduce_kernel adds the partials in
+    // ascending split order and applies bias / residual / accumulate. splits == 1: off.
+    int splits, kb_per_split;
+    float* partial;
+    int64_t slab, pstride;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------
@@ -205,6 +212,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t tiles_m = (p.M + TC_BM - 1) / TC_BM, tiles_n = (p.N + BN - 1) / BN;
     const int64_t n_tiles = tiles_m * tiles_n;
+    const int64_t n_work = n_tiles * p.splits;
     const int k_blocks = static_cast<int>((p.K + TC_BK - 1) / TC_BK);
 
     if (threadIdx.x == 0) {
@@ -234,10 +242,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+                const int64_t tile = w % n_tiles;
+                const int kb0 = static_cast<int>(w / n_tiles) * p.kb_per_split;
+                const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
                 const int32_t m0 = static_cast<int32_t>((tile / tiles_n) * TC_BM);
                 const int32_t n0 = static_cast<int32_t>((tile % tiles_n) * BN);
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t fb = smem_u32(&full_bar[stage]);
                     mbar_expect_tx(fb, Cfg::STAGE_BYTES);
@@ -276,11 +287,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+            for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+                const int kb0 = static_cast<int>(w / n_tiles) * p.kb_per_split;
+                const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
                 if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
@@ -289,7 +302,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int k = 0; k < TC_BK / 16; ++k) {
                         const uint64_t ad = make_smem_desc(sa + k * a_step, a_lbo, 1024u);
                         const uint64_t bd = make_smem_desc(sb + k * b_step, b_lbo, 1024u);
-                        tc_mma_bf16(d_tmem, ad, bd, idesc, (kb | k) != 0 ? 1u : 0u);
+                        tc_mma_bf16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(smem_u32(&empty_bar[stage]));  // frees the stage when these MMAs retire
                     if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1u; }
@@ -308,12 +321,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         TC* C = static_cast<TC*>(p.C);
         const TC* Rsd = static_cast<const TC*>(p.residual);
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        for (int64_t w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+            const int64_t tile = w % n_tiles;
             const int64_t m0 = (tile / tiles_n) * TC_BM, n0 = (tile % tiles_n) * BN;
             if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int64_t m = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
+            float* part = p.splits > 1 ? p.partial + (w / n_tiles) * p.slab + m * p.pstride : nullptr;
 #pragma unroll 1
             for (int ch = 0; ch < BN / 32; ++ch) {
                 const int64_t c0 = n0 + ch * 32;
@@ -321,7 +336,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t r[32];
                 tc_ld32(t_row + static_cast<uint32_t>(ch * 32), r);
                 tc_wait_ld();
-                if (m < p.M) {
+                if (part != nullptr) {
+                    // raw fp32 partial; pstride is a multiple of 32 columns, so whole chunks fit
+                    if (m < p.M) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            *reinterpret_cast<uint4*>(part + c0 + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+                    }
+                } else if (m < p.M) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const int64_t c = c0 + g * 8;
@@ -374,6 +396,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
     }
+}
+
+// out[m, c] = sum over splits (ascending) of partial[s][m, c] (+ bias[c]) (+ residual[m, c])
+// (+ out[m, c] when accumulating): the second stage of a split-K launch. One thread per 4 columns.
+template <typename TC>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t slab, int64_t pstride, TcParams p) {
+    const int64_t groups = (p.N + 3) / 4;
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (idx >= p.M * groups) return;
+    const int64_t m = idx / groups, c = (idx % groups) * 4;
+    float4 acc = *reinterpret_cast<const float4*>(partial + m * pstride + c);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(partial + s * slab + m * pstride + c);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float v[4] = {acc.x, acc.y, acc.z, acc.w};
+    TC* C = static_cast<TC*>(p.C);
+    const TC* Rsd = static_cast<const TC*>(p.residual);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (c + e >= p.N) break;
+        float x = v[e];
+        if (p.bias) x += p.bias[c + e];
+        if (Rsd) x += to_f32(Rsd[m * p.ldr + c + e]);
+        if (p.accumulate) x += to_f32(C[m * p.ldc + c + e]);
+        C[m * p.ldc + c + e] = from_f32<TC>(x);
+    }
+}
+
+static float* g_splitk_ws = nullptr;    // caller-owned workspace for split-K partials
+static size_t g_splitk_ws_bytes = 0;
+static thread_local int g_last_splits = 1;
+
+float* gemm_splitk_workspace(size_t* bytes) {
+    *bytes = g_splitk_ws_bytes;
+    return g_splitk_ws;
+}
+void gemm_note_splits(int splits) { g_last_splits = splits; }
+int gemm_splitk_reduce(cudaStream_t st, int c_dtype, const float* partial, int splits, int64_t slab, int64_t pstride,
+                       int64_t M, int64_t N, void* C, int64_t ldc, int accumulate, const float* bias,
+                       const void* residual, int64_t ldr) {
+    TcParams p = {};
+    p.M = M; p.N = N;
+    p.C = C; p.ldc = ldc;
+    p.bias = bias; p.residual = residual; p.ldr = ldr;
+    p.accumulate = accumulate;
+    const int64_t n = M * ((N + 3) / 4);
+    const unsigned grid = static_cast<unsigned>((n + 255) / 256);
+    if (c_dtype == PK_F32) splitk_reduce_kernel<float><<<grid, 256, 0, st>>>(partial, splits, slab, pstride, p);
+    else splitk_reduce_kernel<bf16><<<grid, 256, 0, st>>>(partial, splits, slab, pstride, p);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
 }
 
 // ---- host side --------------------------------------------------------------------
@@ -443,11 +518,17 @@ static int launch_cfg(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap&
         PK_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set = true;
     }
-    const int64_t tiles = ((p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN);
+    const int64_t tiles = ((p.M + TC_BM - 1) / TC_BM) * ((p.N + BN - 1) / BN) * p.splits;
     int64_t grid = sm_count();
     if (grid > tiles) grid = tiles;
     kern<<<static_cast<unsigned>(grid), TC_THREADS, Cfg::SMEM_BYTES, st>>>(ma, mb, p);
     PK_LAUNCH_CHECK();
+    if (p.splits > 1) {
+        const int64_t n = p.M * ((p.N + 3) / 4);
+        splitk_reduce_kernel<TC><<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(p.partial, p.splits, p.slab,
+                                                                                       p.pstride, p);
+        PK_LAUNCH_CHECK();
+    }
     return PK_OK;
 }
 
@@ -464,7 +545,25 @@ int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int6
     const int64_t tiles256 = rows_t * ((N + 255) / 256), tiles128 = rows_t * ((N + 127) / 128);
     const double fill256 = static_cast<double>(tiles256) / static_cast<double>((tiles256 + sms - 1) / sms * sms);
     const double fill128 = static_cast<double>(tiles128) / static_cast<double>((tiles128 + sms - 1) / sms * sms);
-    const int bn = (N > 128 && fill256 >= 0.7 * fill128) ? 256 : 128;  // narrow tiles cost more operand traffic: only when the gain is large
+    int bn = (N > 128 && fill256 >= 0.7 * fill128) ? 256 : 128;  // narrow tiles cost more operand traffic: only when the gain is large
+    // Split-K: when even the narrow tiles leave more than half of the SMs idle and the k loop is
+    // long (weight gradients of narrow projections), the k range is cut into `splits` parts that
+    // run side by side on wide tiles; needs the caller's workspace (pk_gemm_set_workspace).
+    int splits = 1;
+    const int64_t k_blocks = (K + TC_BK - 1) / TC_BK;
+    const int64_t pstride = (N + 255) / 256 * 256;
+    if (g_splitk_ws != nullptr && 2 * tiles128 <= sms && k_blocks >= 64) {
+        const int bn_s = N > 128 ? 256 : 128;
+        const int64_t tiles_s = bn_s == 256 ? tiles256 : tiles128;
+        int64_t sp = sms / tiles_s;
+        if (sp > 8) sp = 8;
+        if (sp > k_blocks / 16) sp = k_blocks / 16;
+        while (sp > 1 && static_cast<size_t>(sp) * M * pstride * sizeof(float) > g_splitk_ws_bytes) --sp;
+        if (sp > 1) {
+            splits = static_cast<int>(sp);
+            bn = bn_s;
+        }
+    }
     CUtensorMap ma, mb;
     int rc;
     if (!a_mn) rc = make_map(&ma, A, K, M, lda, TC_BK, TC_BM);
@@ -479,6 +578,16 @@ int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int6
     p.bias = bias; p.residual = residual; p.ldr = ldr;
     p.accumulate = accumulate;
     p.a_mn_major = a_mn; p.b_mn_major = b_mn;
+    p.splits = splits;
+    p.kb_per_split = static_cast<int>((k_blocks + splits - 1) / splits);
+    p.partial = g_splitk_ws;
+    p.pstride = pstride;
+    p.slab = M * pstride;
+    if (splits > 1 && static_cast<int64_t>(p.kb_per_split) * (splits - 1) >= k_blocks) {
+        // the last split would be empty: fewer, equal parts
+        p.splits = static_cast<int>((k_blocks + p.kb_per_split - 1) / p.kb_per_split);
+    }
+    g_last_splits = p.splits;
     if (bn == 256) {
         if (c_dtype == PK_F32) return launch_cfg<256, float>(st, ma, mb, p);
         return launch_cfg<256, bf16>(st, ma, mb, p);
@@ -490,6 +599,14 @@ int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int6
 }  // namespace pk
 
 extern "C" {
+
+int pk_gemm_set_workspace(void* ptr, size_t bytes) {
+    PK_REQUIRE(ptr == nullptr || pk::aligned16(ptr), "workspace must be 16-byte aligned");
+    pk::g_splitk_ws = static_cast<float*>(ptr);
+    pk::g_splitk_ws_bytes = ptr ? bytes : 0;
+    return PK_OK;
+}
+int pk_gemm_last_splits(void) { return pk::g_last_splits; }
 
 // Reads (and clears when `clear` != 0) the status word the tensor-core GEMM writes when
 // a bounded wait gives up. Synchronises the device.

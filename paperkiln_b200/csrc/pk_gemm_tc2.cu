@@ -53,6 +53,11 @@ struct T2Params {
     int64_t ldr;
     int accumulate;
     int a_mn_major, b_mn_major;
+    // split-K, as in the one-CTA kernel: work item w = (tile w % n_tiles, k part w / n_tiles),
+    // fp32 partial tiles in partial + part * slab (row stride pstride); splits == 1: off
+    int splits, kb_per_split;
+    float* partial;
+    int64_t slab, pstride;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -154,6 +159,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int64_t tiles_m = (p.M + 2 * T2_BM - 1) / (2 * T2_BM), tiles_n = (p.N + T2_BN - 1) / T2_BN;
     const int64_t n_tiles = tiles_m * tiles_n;
+    const int64_t n_work = n_tiles * p.splits;
     const int k_blocks = static_cast<int>((p.K + T2_BK - 1) / T2_BK);
 
     if (threadIdx.x == 0) {
@@ -184,10 +190,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            for (int64_t w = pair; w < n_work && ok; w += n_pairs) {
+                const int64_t tile = w % n_tiles;
+                const int kb0 = static_cast<int>(w / n_tiles) * p.kb_per_split;
+                const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
                 const int32_t m0 = static_cast<int32_t>((tile / tiles_n) * (2 * T2_BM) + rank * T2_BM);
                 const int32_t n0 = static_cast<int32_t>((tile % tiles_n) * T2_BN + rank * (T2_BN / 2));
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait2(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t fb_local = smem_u32(&full_bar[stage]);
                     const uint32_t fb = map_to_rank(fb_local, 0);   // the leader's barrier counts both CTAs' bytes
@@ -226,17 +235,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+            for (int64_t w = pair; w < n_work && ok; w += n_pairs) {
+                const int kb0 = static_cast<int>(w / n_tiles) * p.kb_per_split;
+                const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
                 if (!wait2(smem_u32(&acc_empty[acc]), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
                 fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * T2_BN);
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait2(smem_u32(&full_bar[stage]), phase, abort_flag)) { ok = false; break; }
                     fence_after();
                     const uint32_t a_lo = a_lo0 + stage * (T2_STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (T2_STAGE_BYTES >> 4);
 #pragma unroll
                     for (int k = 0; k < T2_BK / 16; ++k)
-                        mma2_ss(d_tmem, a_lo + k * a_step, b_lo + k * b_step, idesc, (kb | k) != 0 ? 1u : 0u);
+                        mma2_ss(d_tmem, a_lo + k * a_step, b_lo + k * b_step, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     commit_pair(smem_u32(&empty_bar[stage]));   // frees the stage in both CTAs
                     if (++stage == T2_STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -254,7 +265,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         TC* C = static_cast<TC*>(p.C);
         const TC* Rsd = static_cast<const TC*>(p.residual);
         bool ok = true;
-        for (int64_t tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        for (int64_t w = pair; w < n_work && ok; w += n_pairs) {
+            const int64_t tile = w % n_tiles;
             const int64_t m0 = (tile / tiles_n) * (2 * T2_BM) + rank * T2_BM, n0 = (tile % tiles_n) * T2_BN;
             ok = wait2(smem_u32(&acc_full[acc]), acc_phase, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
@@ -262,6 +274,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             fence_after();
             const int64_t m = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * T2_BN);
+            float* part = p.splits > 1 ? p.partial + (w / n_tiles) * p.slab + m * p.pstride : nullptr;
 #pragma unroll 1
             for (int ch = 0; ch < T2_BN / 32; ++ch) {
                 const int64_t c0 = n0 + ch * 32;
@@ -269,7 +282,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 uint32_t r[32];
                 tmem_ld32(t_row + static_cast<uint32_t>(ch * 32), r);
                 tmem_wait_ld();
-                if (m < p.M) {
+                if (part != nullptr) {
+                    // raw fp32 partial; pstride is a multiple of 256 columns, so whole chunks fit
+                    if (m < p.M) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g)
+                            *reinterpret_cast<uint4*>(part + c0 + g * 4) = make_uint4(r[g * 4], r[g * 4 + 1], r[g * 4 + 2], r[g * 4 + 3]);
+                    }
+                } else if (m < p.M) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const int64_t c = c0 + g * 8;
@@ -329,7 +349,7 @@ typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 template <typename TC>
-int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const T2Params& p) {
+int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, T2Params p, int c_dtype) {
     auto kern = gemm_tc2_kernel<TC>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -357,10 +377,38 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const
         max_pairs = n;
     }
     const int64_t tiles = ((p.M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((p.N + T2_BN - 1) / T2_BN);
+    // Split-K when the last wave of tiles would leave many SM pairs idle and the k loop is long
+    // (weight gradients: a few hundred tiles, tens of thousands of rows): the smallest number of
+    // k parts whose work items fill the waves to 95 %, if the caller's workspace holds them.
+    const int64_t k_blocks = (p.K + T2_BK - 1) / T2_BK;
+    p.splits = 1;
+    p.pstride = (p.N + T2_BN - 1) / T2_BN * T2_BN;
+    p.slab = p.M * p.pstride;
+    size_t ws_bytes = 0;
+    p.partial = gemm_splitk_workspace(&ws_bytes);
+    auto fill = [&](int64_t items) {
+        return static_cast<double>(items) / static_cast<double>((items + max_pairs - 1) / max_pairs * max_pairs);
+    };
+    if (p.partial != nullptr && k_blocks >= 256 && fill(tiles) < 0.9) {
+        for (int sp = 2; sp <= 4; ++sp) {
+            if (static_cast<size_t>(sp) * p.slab * sizeof(float) > ws_bytes) break;
+            if (fill(tiles * sp) >= 0.95) {
+                p.splits = sp;
+                break;
+            }
+        }
+    }
+    p.kb_per_split = static_cast<int>((k_blocks + p.splits - 1) / p.splits);
+    if (p.splits > 1 && static_cast<int64_t>(p.kb_per_split) * (p.splits - 1) >= k_blocks)
+        p.splits = static_cast<int>((k_blocks + p.kb_per_split - 1) / p.kb_per_split);
+    gemm_note_splits(p.splits);
     int64_t pairs = max_pairs;
-    if (pairs > tiles) pairs = tiles;
+    if (pairs > tiles * p.splits) pairs = tiles * p.splits;
     kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, p);
     PK_LAUNCH_CHECK();
+    if (p.splits > 1)
+        return gemm_splitk_reduce(st, c_dtype, p.partial, p.splits, p.slab, p.pstride, p.M, p.N, p.C, p.ldc, p.accumulate,
+                                  p.bias, p.residual, p.ldr);
     return PK_OK;
 }
 
@@ -385,8 +433,8 @@ int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int
     p.bias = bias; p.residual = residual; p.ldr = ldr;
     p.accumulate = accumulate;
     p.a_mn_major = a_mn; p.b_mn_major = b_mn;
-    if (c_dtype == PK_F32) return launch2<float>(st, ma, mb, p);
-    return launch2<bf16>(st, ma, mb, p);
+    if (c_dtype == PK_F32) return launch2<float>(st, ma, mb, p, c_dtype);
+    return launch2<bf16>(st, ma, mb, p, c_dtype);
 }
 
 int gemm_tc2_status(int* status_h, int clear) {

@@ -113,6 +113,16 @@ void init(int ordinal) {
     if (ordinal < 0 || ordinal >= n) throw std::runtime_error("GPU ordinal out of range");
     check(pk_set_device(ordinal), "pk_set_device");
     if (!r.own_stream) check(pk_stream_create(&r.own_stream), "pk_stream_create");
+    {
+        // Workspace for the split-K partial tiles of weight-gradient GEMMs with few output tiles
+        // (one per process: every GEMM of this library runs on the one compute stream).
+        static void* gemm_ws = nullptr;
+        constexpr size_t kGemmWsBytes = size_t(128) << 20;
+        if (gemm_ws) pk_free(gemm_ws);
+        gemm_ws = nullptr;
+        check(pk_malloc(&gemm_ws, kGemmWsBytes), "pk_malloc");
+        check(pk_gemm_set_workspace(gemm_ws, kGemmWsBytes), "pk_gemm_set_workspace");
+    }
     r.ordinal = ordinal;
     r.inited = true;
     r.dev = Device::CUDA;

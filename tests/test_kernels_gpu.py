@@ -370,6 +370,46 @@ def test_gemm_cta_pair_kernel(pk, shape, ta, tb):
     close(outs[1][1], ref + 1.0, 2e-3 * math.sqrt(max(K, 64) / 64), 1e-3)
 
 
+@pytest.mark.parametrize("shape,ta,tb", [((2048, 512, 16384), True, False), ((768, 768, 8192), True, False),
+                                         ((300, 200, 8192), False, False), ((896, 16, 8192), True, False),
+                                         ((256, 264, 4096 + 64), False, True),
+                                         ((2048, 8192, 16384), True, False)])  # the last one: CTA-pair kernel
+def test_gemm_split_k(pk, shape, ta, tb):
+    """Few output tiles and a long k extent (weight gradients of narrow projections): with a
+    workspace the k range is cut into parts whose fp32 partial tiles are added in a fixed order.
+    Same result as the unsplit kernel up to the grouping of the sum, reproducible bit for bit,
+    with bias / residual / accumulate applied once, ragged extents included."""
+    M, N, K = shape
+    A = rnd(K, M, seed=1, lo=-1, hi=1, dtype=torch.bfloat16) if ta else rnd(M, K, seed=1, lo=-1, hi=1, dtype=torch.bfloat16)
+    B = rnd(N, K, seed=2, lo=-1, hi=1, dtype=torch.bfloat16) if tb else rnd(K, N, seed=2, lo=-1, hi=1, dtype=torch.bfloat16)
+    bias = rnd(1, N, seed=3).reshape(N)
+    res = rnd(M, N, seed=4, dtype=torch.bfloat16)
+    ws = torch.empty(128 << 20, dtype=torch.uint8, device="cuda")
+    outs = {}
+    try:
+        for split in (0, 1, 2):
+            pkt.check(pk.pk_gemm_set_workspace(ptr(ws) if split else None, ws.numel() if split else 0))
+            Cb = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            pkt.gemm(A, B, ta=ta, tb=tb, C=Cb, bias=bias, residual=res)
+            n1 = pk.pk_gemm_last_splits()
+            Cf = torch.ones(M, N, device="cuda")
+            pkt.gemm(A, B, ta=ta, tb=tb, C=Cf, accumulate=True)
+            outs[split] = (Cb, Cf, n1, pk.pk_gemm_last_splits())
+    finally:
+        pkt.check(pk.pk_gemm_set_workspace(None, 0))
+    st = ctypes.c_int(0)
+    pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
+    assert st.value == 0
+    assert outs[0][2] == 1 and outs[0][3] == 1
+    assert outs[1][2] > 1 and outs[1][3] > 1, "the k range was not split"
+    assert torch.equal(outs[1][0], outs[2][0]) and torch.equal(outs[1][1], outs[2][1])
+    ref = (A.t() if ta else A).float() @ (B.t() if tb else B).float()
+    tol = 2e-3 * math.sqrt(max(K, 64) / 64)
+    close(outs[1][1], ref + 1.0, tol, 1e-3)
+    close(outs[1][1], outs[0][1], tol, 1e-3)
+    close(outs[1][0].float(), (ref + bias + res.float()), tol + 0.05, 2 ** -7)
+
+
 def attn_ref(q, k, v, B, S, Hq, Hkv, dk, scale, causal):
     """fp32 restatement of ops::fused_attention per head (src/ops.cpp:863-934)."""
     q = q.float().view(B, S, Hq, dk).transpose(1, 2)
