@@ -345,18 +345,23 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             const bool need_mask = (p.causal && kv0 + BW_COLS - 1 > q0) || (kv0 + BW_COLS > p.S);
             const int key0 = kv0 + hf * 32;
             uint32_t pk[16];
+            // two elements per instruction (packed fp32 pairs):
+            // p = 2^(s c - lse2) (FFMA2 + 2 MUFU), ds = p (dp scale - delta scale) (FFMA2 + FMUL2)
+            const uint64_t sl2 = f2_pack(p.scale_log2, p.scale_log2), nl2 = f2_pack(neg_lse2, neg_lse2);
+            const uint64_t sc2 = f2_pack(p.scale, p.scale), nd2 = f2_pack(neg_delta_s, neg_delta_s);
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-                // p = 2^(s c - lse2) (FFMA + MUFU), ds = p (dp scale - delta scale) (FFMA + FMUL)
-                float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * e]), p.scale_log2, neg_lse2));
-                float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * e + 1]), p.scale_log2, neg_lse2));
+                float x0, x1;
+                f2_unpack(f2_fma(f2_pack_bits(rs[2 * e], rs[2 * e + 1]), sl2, nl2), x0, x1);
+                float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
                 if (need_mask) {
                     const int ka = key0 + 2 * e;
                     if (ka >= p.S || (p.causal && ka > qi)) p0 = 0.0f;
                     if (ka + 1 >= p.S || (p.causal && ka + 1 > qi)) p1 = 0.0f;
                 }
-                pk[e] = pack2(p0 * fmaf(__uint_as_float(rd[2 * e]), p.scale, neg_delta_s),
-                              p1 * fmaf(__uint_as_float(rd[2 * e + 1]), p.scale, neg_delta_s));
+                float d0, d1;
+                f2_unpack(f2_mul(f2_pack(p0, p1), f2_fma(f2_pack_bits(rd[2 * e], rd[2 * e + 1]), sc2, nd2)), d0, d1);
+                pk[e] = pack2(d0, d1);
             }
             if (wl == 0 && lane == 0) BWS_T(0, grp, 3, j);
             tmem_st16(t_s, pk);   // over this thread's own (already read) S columns
@@ -592,17 +597,22 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const float* xs = xs_base + st * 128 + hf * 32;   // [-lse2 x 64 | -delta scale x 64]
             const int qc0 = q0 + hf * 32;
             uint32_t pp[16], pd[16];
+            // two elements per instruction (packed fp32 pairs); the statistics come as pairs too
+            const uint64_t sl2 = f2_pack(p.scale_log2, p.scale_log2), sc2 = f2_pack(p.scale, p.scale);
+            const uint64_t* xs2 = reinterpret_cast<const uint64_t*>(xs);
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-                float p0 = ex2_approx(fmaf(__uint_as_float(rs[2 * e]), p.scale_log2, xs[2 * e]));
-                float p1 = ex2_approx(fmaf(__uint_as_float(rs[2 * e + 1]), p.scale_log2, xs[2 * e + 1]));
+                float x0, x1;
+                f2_unpack(f2_fma(f2_pack_bits(rs[2 * e], rs[2 * e + 1]), sl2, xs2[e]), x0, x1);
+                float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
                 if (need_mask) {  // queries past the end already have -lse2 = -inf
                     if (!key_ok || (p.causal && kj > qc0 + 2 * e)) p0 = 0.0f;
                     if (!key_ok || (p.causal && kj > qc0 + 2 * e + 1)) p1 = 0.0f;
                 }
                 pp[e] = pack2(p0, p1);
-                pd[e] = pack2(p0 * fmaf(__uint_as_float(rd[2 * e]), p.scale, xs[64 + 2 * e]),
-                              p1 * fmaf(__uint_as_float(rd[2 * e + 1]), p.scale, xs[64 + 2 * e + 1]));
+                float d0, d1;
+                f2_unpack(f2_mul(f2_pack(p0, p1), f2_fma(f2_pack_bits(rd[2 * e], rd[2 * e + 1]), sc2, xs2[32 + e])), d0, d1);
+                pd[e] = pack2(d0, d1);
             }
             tmem_st16(t_s, pp);    // over this thread's own (already read) columns
             tmem_st16(t_dp, pd);

@@ -292,9 +292,13 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     if (key0 + 32 + e >= p.S || (p.causal && key0 + 32 + e > qi)) r1[e] = 0xff800000u;
                 }
             }
-            float mx = -INFINITY;
+            float mx = -INFINITY, mx1 = -INFINITY;   // two chains of three-input maxima
 #pragma unroll
-            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[e]), __uint_as_float(r1[e])));
+            for (int e = 0; e < 32; e += 2) {
+                mx = fmax3(mx, __uint_as_float(r0[e]), __uint_as_float(r1[e]));
+                mx1 = fmax3(mx1, __uint_as_float(r0[e + 1]), __uint_as_float(r1[e + 1]));
+            }
+            mx = fmaxf(mx, mx1);
             *my_x = mx;
             *my_f = ok ? 1 : 0;
             named_sync64(bar_id);
@@ -328,19 +332,28 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             if (wl == 0 && lane == 0) WS_T(s, 4);
             const float neg_m = -m;
-            float sum = 0.0f;
+            // two scores per instruction (packed fp32 pairs): s c - m, then the row-sum partials
+            const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
+            uint64_t sum_a = f2_pack(0.0f, 0.0f), sum_b = sum_a;
             uint32_t pk[32];
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-                const float a0 = ex2_approx(fmaf(__uint_as_float(r0[2 * e]), p.scale_log2, neg_m));
-                const float a1 = ex2_approx(fmaf(__uint_as_float(r0[2 * e + 1]), p.scale_log2, neg_m));
-                const float b0 = ex2_approx(fmaf(__uint_as_float(r1[2 * e]), p.scale_log2, neg_m));
-                const float b1 = ex2_approx(fmaf(__uint_as_float(r1[2 * e + 1]), p.scale_log2, neg_m));
-                sum += (a0 + a1) + (b0 + b1);
+                float xa0, xa1, xb0, xb1;
+                f2_unpack(f2_fma(f2_pack_bits(r0[2 * e], r0[2 * e + 1]), sc2, nm2), xa0, xa1);
+                f2_unpack(f2_fma(f2_pack_bits(r1[2 * e], r1[2 * e + 1]), sc2, nm2), xb0, xb1);
+                const float a0 = ex2_approx(xa0), a1 = ex2_approx(xa1);
+                const float b0 = ex2_approx(xb0), b1 = ex2_approx(xb1);
+                sum_a = f2_add(sum_a, f2_pack(a0, a1));
+                sum_b = f2_add(sum_b, f2_pack(b0, b1));
                 pk[e] = pack2(a0, a1);
                 pk[16 + e] = pack2(b0, b1);
             }
-            l += sum;
+            {
+                float s0, s1, s2, s3;
+                f2_unpack(sum_a, s0, s1);
+                f2_unpack(sum_b, s2, s3);
+                l += (s0 + s1) + (s2 + s3);
+            }
             if (wl == 0 && lane == 0) WS_T(s, 5);
             tmem_st32(t_p, pk);
             tmem_wait_st();
