@@ -80,6 +80,21 @@ int mt_model_live_after_forward(void* model, int64_t* n_h);
 int mt_model_set_adamw(void* model, float lr, float beta1, float beta2, float eps, float weight_decay);
 int mt_model_optimizer_step(void* model);
 
+/* Checkpoint files in the safetensors layout of the reference (src/safetensors.cpp:12-94: 8-byte
+ * little-endian header length, JSON header, raw fp32 tensors in sorted name order, header padded
+ * to 8 bytes). mt_model_save writes every parameter under its mt_model_param_info name as F32
+ * [rows, cols] -- a file the reference's load_safetensors reads -- and, when optimizer_path is not
+ * null, a second file beside it with the AdamW state ("m.<name>", "v.<name>", and "t" = [low 24
+ * bits, high bits] of the step count), which the reference does not save
+ * (tools/mtstudio.cpp:437-441). mt_model_load is the inverse (either path may be null); it
+ * also accepts BF16 tensors, checks every name and shape before changing anything, and a run
+ * restored from both files continues bit-identically. mt_safetensors_copy loads a file and writes
+ * it back (no GPU needed): the loader's rules -- rank > 2 skipped, "transformer." stripped,
+ * "__metadata__" ignored, [n] -> [1, n] -- applied to any safetensors file. */
+int mt_model_save(void* model, const char* weights_path, const char* optimizer_path);
+int mt_model_load(void* model, const char* weights_path, const char* optimizer_path);
+int mt_safetensors_copy(const char* in_path, const char* out_path, int64_t* n_loaded_h, int64_t* n_skipped_h);
+
 /* Gradient accumulation over micro-batches (the reference's trainer loop,
  * tools/mtstudio.cpp:456-474: zero_grad once, `accum` backward passes pre-scaled by 1/accum,
  * one optimizer step). With accumulate on, mt_model_step no longer clears the gradients it

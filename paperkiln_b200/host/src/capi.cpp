@@ -10,6 +10,7 @@
 #include "microtorch/flex.hpp"
 #include "microtorch/llama.hpp"
 #include "microtorch/nn.hpp"
+#include "microtorch/safetensors.hpp"
 
 using namespace microtorch;
 
@@ -293,6 +294,84 @@ int mt_model_grad_get(void* h, int64_t i, float* out, int* has) {
         if (has) *has = 1;
         const Matrix& v = p->grad.host();
         std::memcpy(out, v.data(), v.size() * sizeof(float));
+    });
+}
+
+// ---- checkpoint files -------------------------------------------------------------------
+static nn::AdamW& optimizer(Model* m);
+static size_t optimizer_index(Model* m, int64_t i);
+
+int mt_safetensors_copy(const char* in_path, const char* out_path, int64_t* n_loaded, int64_t* n_skipped) {
+    return guard([&] {
+        std::map<std::string, std::string> skipped;
+        const auto tensors = load_safetensors(in_path, &skipped);
+        save_safetensors(out_path, tensors);
+        if (n_loaded) *n_loaded = static_cast<int64_t>(tensors.size());
+        if (n_skipped) *n_skipped = static_cast<int64_t>(skipped.size());
+    });
+}
+int mt_model_save(void* h, const char* weights_path, const char* optimizer_path) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!weights_path) throw std::runtime_error("null path");
+        std::map<std::string, Matrix> w;
+        for (auto& [name, p] : m->named) w[name] = p->data.host();
+        save_safetensors(weights_path, w);
+        if (!optimizer_path) return;
+        std::map<std::string, Matrix> o;
+        nn::AdamW& opt = optimizer(m);
+        for (size_t i = 0; i < m->named.size(); ++i) {
+            const Var& p = m->named[i].second;
+            Matrix mm(p->data.rows(), p->data.cols()), vv(p->data.rows(), p->data.cols());
+            opt.export_state(optimizer_index(m, static_cast<int64_t>(i)), mm.data(), vv.data());
+            o["m." + m->named[i].first] = std::move(mm);
+            o["v." + m->named[i].first] = std::move(vv);
+        }
+        // the step count as two fp32 halves (each below 2^24, so exact): t = hi * 2^24 + lo
+        Matrix t(1, 2);
+        const long steps = opt.steps_taken();
+        t(0, 0) = static_cast<float>(steps & 0xffffff);
+        t(0, 1) = static_cast<float>(steps >> 24);
+        o["t"] = std::move(t);
+        save_safetensors(optimizer_path, o);
+    });
+}
+int mt_model_load(void* h, const char* weights_path, const char* optimizer_path) {
+    return guard([&] {
+        Model* m = M(h);
+        auto fetch = [](const std::map<std::string, Matrix>& src, const std::string& name, size_t rows,
+                        size_t cols) -> const Matrix& {
+            auto it = src.find(name);
+            if (it == src.end()) throw std::runtime_error("checkpoint has no tensor " + name);
+            if (it->second.rows() != rows || it->second.cols() != cols)
+                throw std::runtime_error("checkpoint tensor " + name + " is [" + std::to_string(it->second.rows()) + ", " +
+                                         std::to_string(it->second.cols()) + "], the model wants [" +
+                                         std::to_string(rows) + ", " + std::to_string(cols) + "]");
+            return it->second;
+        };
+        if (weights_path) {
+            const auto w = load_safetensors(weights_path);
+            // every tensor is checked before the first one is written
+            for (auto& [name, p] : m->named) fetch(w, name, p->data.rows(), p->data.cols());
+            for (auto& [name, p] : m->named) p->data = fetch(w, name, p->data.rows(), p->data.cols());
+        }
+        if (optimizer_path) {
+            const auto o = load_safetensors(optimizer_path);
+            for (auto& [name, p] : m->named) {
+                fetch(o, "m." + name, p->data.rows(), p->data.cols());
+                fetch(o, "v." + name, p->data.rows(), p->data.cols());
+            }
+            const Matrix& t = fetch(o, "t", 1, 2);
+            nn::AdamW& opt = optimizer(m);
+            for (size_t i = 0; i < m->named.size(); ++i) {
+                const Var& p = m->named[i].second;
+                const std::string& name = m->named[i].first;
+                opt.import_state(optimizer_index(m, static_cast<int64_t>(i)),
+                                 fetch(o, "m." + name, p->data.rows(), p->data.cols()).data(),
+                                 fetch(o, "v." + name, p->data.rows(), p->data.cols()).data());
+            }
+            opt.set_steps_taken(static_cast<long>(t(0, 0)) + (static_cast<long>(t(0, 1)) << 24));
+        }
     });
 }
 

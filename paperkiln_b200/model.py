@@ -238,6 +238,15 @@ class Model:
                                                       v.ctypes.data_as(ctypes.c_void_p))
             _check(rc, "mt_model_optimizer_state_set")
 
+    # ---- checkpoint files (safetensors, the reference's layout) ----
+    def save(self, weights_path: str, optimizer_path: Optional[str] = None):
+        _check(libmt().mt_model_save(self._h, weights_path.encode(), optimizer_path.encode() if optimizer_path else None),
+               "mt_model_save")
+
+    def load(self, weights_path: Optional[str], optimizer_path: Optional[str] = None):
+        _check(libmt().mt_model_load(self._h, weights_path.encode() if weights_path else None,
+                                     optimizer_path.encode() if optimizer_path else None), "mt_model_load")
+
     def clip_grad_norm(self, max_norm: float) -> float:
         n = ctypes.c_float(0.0)
         _check(libmt().mt_model_clip_grad_norm(self._h, max_norm, ctypes.byref(n)), "mt_model_clip_grad_norm")
