@@ -94,6 +94,12 @@ int mt_model_optimizer_step(void* model);
 int mt_model_save(void* model, const char* weights_path, const char* optimizer_path);
 int mt_model_load(void* model, const char* weights_path, const char* optimizer_path);
 int mt_safetensors_copy(const char* in_path, const char* out_path, int64_t* n_loaded_h, int64_t* n_skipped_h);
+/* QLoRA models (spec qlora=1): replaces the frozen base -- the seven projections of every block,
+ * the embedding and the norm gains -- by the tensors of a dense model's weights file (F32 or
+ * BF16 safetensors, that model's parameter names); the projections are quantised to Q8_0 on the
+ * device, as the reference builds its QLoRA layers from fp32 weights (src/quant.cpp:102-110).
+ * Names and shapes are all checked first. The LoRA matrices are left as they are. */
+int mt_model_load_base(void* model, const char* weights_path);
 
 /* Gradient accumulation over micro-batches (the reference's trainer loop,
  * tools/mtstudio.cpp:456-474: zero_grad once, `accum` backward passes pre-scaled by 1/accum,

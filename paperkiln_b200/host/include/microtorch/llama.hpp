@@ -68,6 +68,14 @@ public:
     Var loss(const std::vector<int>& ids, const std::vector<int>& targets, size_t seq_len = 0,
              size_t chunk_rows = 16384) const;
 
+    // QLoRA mode: takes the frozen base (projections, embedding, norm gains) from the tensors of
+    // a DENSE model of the same shape, named as that model registers them ("layers.0.self_attn.
+    // q_proj.weight", "embed_tokens.weight", "norm.weight", ...); the projections are quantised
+    // to Q8_0 on the device. Every tensor is checked before the first one is replaced. The LoRA
+    // matrices are parameters and are not touched. The reference builds its QLoRA layers from
+    // fp32 weights the same way (QLoRALinear's constructor, src/quant.cpp:102-110).
+    void load_frozen_base(const std::map<std::string, Matrix>& dense);
+
     LlamaConfig cfg;
     bool checkpoint_blocks = false;
     std::shared_ptr<Embedding> embed_tokens;  // dense mode

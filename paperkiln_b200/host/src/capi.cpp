@@ -375,6 +375,15 @@ int mt_model_load(void* h, const char* weights_path, const char* optimizer_path)
     });
 }
 
+int mt_model_load_base(void* h, const char* weights_path) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!weights_path) throw std::runtime_error("null path");
+        if (!m->llama) throw std::runtime_error("load_base: only the llama family has a QLoRA mode");
+        m->llama->load_frozen_base(load_safetensors(weights_path));
+    });
+}
+
 int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64_t n, int64_t seq_len,
                   float loss_scale, int do_backward, float* loss_h) {
     return guard([&] {

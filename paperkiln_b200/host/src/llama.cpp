@@ -86,6 +86,51 @@ Llama::Llama(const LlamaConfig& cfg_, unsigned seed) : cfg(cfg_) {
     if (!cfg.tie_embeddings && !cfg.qlora) lm_head = mod<Linear>("lm_head", cfg.d, cfg.vocab, false, seed + 12);
 }
 
+void Llama::load_frozen_base(const std::map<std::string, Matrix>& dense) {
+    if (!cfg.qlora) throw std::runtime_error("load_frozen_base: the model was not built in QLoRA mode");
+    auto fetch = [&](const std::string& name, size_t rows, size_t cols) -> const Matrix& {
+        auto it = dense.find(name);
+        if (it == dense.end()) throw std::runtime_error("checkpoint has no tensor " + name);
+        if (it->second.rows() != rows || it->second.cols() != cols)
+            throw std::runtime_error("checkpoint tensor " + name + " is [" + std::to_string(it->second.rows()) + ", " +
+                                     std::to_string(it->second.cols()) + "], the model wants [" +
+                                     std::to_string(rows) + ", " + std::to_string(cols) + "]");
+        return it->second;
+    };
+    struct Proj {
+        const char* name;
+        std::shared_ptr<Projection> LlamaBlock::*member;
+    };
+    static const Proj projs[] = {
+        {"self_attn.q_proj", &LlamaBlock::q_proj}, {"self_attn.k_proj", &LlamaBlock::k_proj},
+        {"self_attn.v_proj", &LlamaBlock::v_proj}, {"self_attn.o_proj", &LlamaBlock::o_proj},
+        {"mlp.gate_proj", &LlamaBlock::gate_proj}, {"mlp.up_proj", &LlamaBlock::up_proj},
+        {"mlp.down_proj", &LlamaBlock::down_proj}};
+    for (int pass = 0; pass < 2; ++pass) {  // pass 0 checks, pass 1 replaces
+        const Matrix& e = fetch("embed_tokens.weight", cfg.vocab, cfg.d);
+        const Matrix& n = fetch("norm.weight", 1, cfg.d);
+        if (pass) {
+            embed_frozen = make_var(e, false);
+            norm_w = make_var(n, false);
+        }
+        for (size_t i = 0; i < blocks.size(); ++i) {
+            const std::string pre = "layers." + std::to_string(i) + ".";
+            LlamaBlock& b = *blocks[i];
+            const Matrix& g1 = fetch(pre + "input_layernorm.weight", 1, cfg.d);
+            const Matrix& g2 = fetch(pre + "post_attention_layernorm.weight", 1, cfg.d);
+            if (pass) {
+                b.ln1_w = make_var(g1, false);
+                b.ln2_w = make_var(g2, false);
+            }
+            for (const Proj& pr : projs) {
+                Projection& p = *(b.*(pr.member));
+                const Matrix& w = fetch(pre + pr.name + ".weight", p.Wq->rows, p.Wq->cols);
+                if (pass) p.Wq = std::make_shared<Q8Weight>(Q8Weight::from_matrix(w));
+            }
+        }
+    }
+}
+
 Var Llama::hidden(const std::vector<int>& ids, size_t seq_len) const {
     const size_t sl = seq_len == 0 ? ids.size() : seq_len;
     if (sl == 0 || ids.size() % sl != 0) throw std::runtime_error("ids not a multiple of seq_len");

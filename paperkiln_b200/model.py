@@ -247,6 +247,10 @@ class Model:
         _check(libmt().mt_model_load(self._h, weights_path.encode() if weights_path else None,
                                      optimizer_path.encode() if optimizer_path else None), "mt_model_load")
 
+    def load_base(self, weights_path: str):
+        """QLoRA models: frozen base from a dense model's weights file, quantised on the device."""
+        _check(libmt().mt_model_load_base(self._h, weights_path.encode()), "mt_model_load_base")
+
     def clip_grad_norm(self, max_norm: float) -> float:
         n = ctypes.c_float(0.0)
         _check(libmt().mt_model_clip_grad_norm(self._h, max_norm, ctypes.byref(n)), "mt_model_clip_grad_norm")
