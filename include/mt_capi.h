@@ -100,6 +100,10 @@ int mt_safetensors_copy(const char* in_path, const char* out_path, int64_t* n_lo
  * device, as the reference builds its QLoRA layers from fp32 weights (src/quant.cpp:102-110).
  * Names and shapes are all checked first. The LoRA matrices are left as they are. */
 int mt_model_load_base(void* model, const char* weights_path);
+/* The other direction: writes the weights file of the equivalent dense model, every projection
+ * merged as deq(Wq) + (alpha / r) A B in fp32 on the device (the reference's merged_weight,
+ * src/quant.cpp:82-89), under the dense model's names. */
+int mt_model_save_merged(void* model, const char* weights_path);
 
 /* Gradient accumulation over micro-batches (the reference's trainer loop,
  * tools/mtstudio.cpp:456-474: zero_grad once, `accum` backward passes pre-scaled by 1/accum,

@@ -75,6 +75,10 @@ public:
     // matrices are parameters and are not touched. The reference builds its QLoRA layers from
     // fp32 weights the same way (QLoRALinear's constructor, src/quant.cpp:102-110).
     void load_frozen_base(const std::map<std::string, Matrix>& dense);
+    // The inverse direction: the tensors of the equivalent DENSE model, under that model's names,
+    // with every projection merged as deq(Wq) + (alpha / r) A B in fp32 on the device (the
+    // reference's merged_weight, src/quant.cpp:82-89). Dense models return their parameters.
+    std::map<std::string, Matrix> merged_state() const;
 
     LlamaConfig cfg;
     bool checkpoint_blocks = false;

@@ -384,6 +384,15 @@ int mt_model_load_base(void* h, const char* weights_path) {
     });
 }
 
+int mt_model_save_merged(void* h, const char* weights_path) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!weights_path) throw std::runtime_error("null path");
+        if (!m->llama) throw std::runtime_error("save_merged: only the llama family has a QLoRA mode");
+        save_safetensors(weights_path, m->llama->merged_state());
+    });
+}
+
 int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64_t n, int64_t seq_len,
                   float loss_scale, int do_backward, float* loss_h) {
     return guard([&] {

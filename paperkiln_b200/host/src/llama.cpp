@@ -1,6 +1,8 @@
 // Llama-family model. Behavioural reference: src/llama.cpp of paperkiln
 // (LlamaBlock 9-60, Llama 62-89).
 #include "microtorch/llama.hpp"
+#include "microtorch/ops_detail.hpp"
+#include "pk.h"
 
 #include <cmath>
 #include <stdexcept>
@@ -129,6 +131,40 @@ void Llama::load_frozen_base(const std::map<std::string, Matrix>& dense) {
             }
         }
     }
+}
+
+std::map<std::string, Matrix> Llama::merged_state() const {
+    std::map<std::string, Matrix> out;
+    if (!cfg.qlora) {
+        for (const auto& [name, p] : named_parameters()) out[name] = p->data.host();
+        return out;
+    }
+    out["embed_tokens.weight"] = embed_frozen->data.host();
+    out["norm.weight"] = norm_w->data.host();
+    for (size_t i = 0; i < blocks.size(); ++i) {
+        const std::string pre = "layers." + std::to_string(i) + ".";
+        const LlamaBlock& b = *blocks[i];
+        out[pre + "input_layernorm.weight"] = b.ln1_w->data.host();
+        out[pre + "post_attention_layernorm.weight"] = b.ln2_w->data.host();
+        const std::pair<const char*, const Projection*> projs[] = {
+            {"self_attn.q_proj", b.q_proj.get()}, {"self_attn.k_proj", b.k_proj.get()},
+            {"self_attn.v_proj", b.v_proj.get()}, {"self_attn.o_proj", b.o_proj.get()},
+            {"mlp.gate_proj", b.gate_proj.get()}, {"mlp.up_proj", b.up_proj.get()},
+            {"mlp.down_proj", b.down_proj.get()}};
+        for (const auto& [pname, p] : projs) {
+            Tensor w = p->Wq->dequantize(DType::F32);
+            if (p->A) {
+                Tensor a = p->A->data.device().cast(DType::F32), bb = p->B->data.device().cast(DType::F32);
+                Tensor ab = Tensor::empty(a.rows(), bb.cols(), DType::F32);
+                ops::detail::gemm_raw(a, false, bb, false, ab, false);
+                device::check(pk_axpy(device::stream(), PK_F32, w.ptr(), PK_F32, ab.ptr(), p->scaling,
+                                      static_cast<int64_t>(ab.numel())),
+                              "pk_axpy");
+            }
+            out[pre + pname + ".weight"] = w.to_host();
+        }
+    }
+    return out;
 }
 
 Var Llama::hidden(const std::vector<int>& ids, size_t seq_len) const {

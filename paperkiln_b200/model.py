@@ -251,6 +251,10 @@ class Model:
         """QLoRA models: frozen base from a dense model's weights file, quantised on the device."""
         _check(libmt().mt_model_load_base(self._h, weights_path.encode()), "mt_model_load_base")
 
+    def save_merged(self, weights_path: str):
+        """QLoRA models: the equivalent dense model's weights file (base + merged LoRA)."""
+        _check(libmt().mt_model_save_merged(self._h, weights_path.encode()), "mt_model_save_merged")
+
     def clip_grad_norm(self, max_norm: float) -> float:
         n = ctypes.c_float(0.0)
         _check(libmt().mt_model_clip_grad_norm(self._h, max_norm, ctypes.byref(n)), "mt_model_clip_grad_norm")
