@@ -104,6 +104,18 @@ int mt_model_load_base(void* model, const char* weights_path);
  * merged as deq(Wq) + (alpha / r) A B in fp32 on the device (the reference's merged_weight,
  * src/quant.cpp:82-89), under the dense model's names. */
 int mt_model_save_merged(void* model, const char* weights_path);
+/* GGUF (version 3) export with the byte layout of the reference's exporter
+ * (include/microtorch/gguf.hpp:58-66, src/gguf.cpp:27-166): llama.* metadata, token_embd /
+ * blk.N.* / output_norm (/ output) tensors as F32, data aligned to 32 bytes.
+ * mt_model_export_gguf writes a llama-family model (a QLoRA model with its adapters merged).
+ * mt_gguf_export_llama converts a safetensors file without a GPU: spec keys name, arch, ctx, d,
+ * layers, dff, heads, kv_heads, vocab, eps, theta, in_out (1: projections stored [in, out] and
+ * transposed on export; 0: stored [out, in] as in HF checkpoints); tokens_path (may be null)
+ * names a text file with one token per line for the tokenizer block; *n_unmapped_h receives the
+ * number of tensors of the file that have no place in the layout. */
+int mt_model_export_gguf(void* model, const char* gguf_path, const char* name, int64_t context_length);
+int mt_gguf_export_llama(const char* weights_path, const char* gguf_path, const char* spec, const char* tokens_path,
+                         int64_t* n_unmapped_h);
 
 /* Gradient accumulation over micro-batches (the reference's trainer loop,
  * tools/mtstudio.cpp:456-474: zero_grad once, `accum` backward passes pre-scaled by 1/accum,

@@ -2,12 +2,14 @@
 #include "mt_capi.h"
 
 #include <cstring>
+#include <fstream>
 #include <map>
 #include <sstream>
 #include <stdexcept>
 #include <string>
 
 #include "microtorch/flex.hpp"
+#include "microtorch/gguf.hpp"
 #include "microtorch/llama.hpp"
 #include "microtorch/nn.hpp"
 #include "microtorch/safetensors.hpp"
@@ -390,6 +392,58 @@ int mt_model_save_merged(void* h, const char* weights_path) {
         if (!weights_path) throw std::runtime_error("null path");
         if (!m->llama) throw std::runtime_error("save_merged: only the llama family has a QLoRA mode");
         save_safetensors(weights_path, m->llama->merged_state());
+    });
+}
+
+int mt_gguf_export_llama(const char* weights_path, const char* gguf_path, const char* spec, const char* tokens_path,
+                         int64_t* n_unmapped) {
+    return guard([&] {
+        if (!weights_path || !gguf_path) throw std::runtime_error("null path");
+        SpecReader r{parse_spec(spec), {}};
+        gguf::LlamaExportConfig c;
+        c.name = r.str("name", c.name);
+        c.architecture = r.str("arch", c.architecture);
+        c.context_length = static_cast<uint32_t>(r.num("ctx", c.context_length));
+        c.embedding_length = static_cast<uint32_t>(r.num("d", 0));
+        c.block_count = static_cast<uint32_t>(r.num("layers", 0));
+        c.feed_forward_length = static_cast<uint32_t>(r.num("dff", 0));
+        c.head_count = static_cast<uint32_t>(r.num("heads", 0));
+        c.head_count_kv = static_cast<uint32_t>(r.num("kv_heads", 0));
+        c.vocab_size = static_cast<uint32_t>(r.num("vocab", 0));
+        c.rms_eps = static_cast<float>(r.real("eps", c.rms_eps));
+        c.rope_freq_base = static_cast<float>(r.real("theta", c.rope_freq_base));
+        c.weights_in_out = r.num("in_out", 0) != 0;
+        r.finish();
+        if (tokens_path) {  // one token per line
+            std::ifstream tf(tokens_path);
+            if (!tf) throw std::runtime_error(std::string("cannot open ") + tokens_path);
+            std::string line;
+            while (std::getline(tf, line)) c.tokens.push_back(line);
+        }
+        std::vector<std::string> unmapped;
+        gguf::export_gguf_llama(gguf_path, load_safetensors(weights_path), c, &unmapped);
+        if (n_unmapped) *n_unmapped = static_cast<int64_t>(unmapped.size());
+    });
+}
+int mt_model_export_gguf(void* h, const char* gguf_path, const char* name, int64_t context_length) {
+    return guard([&] {
+        Model* m = M(h);
+        if (!gguf_path) throw std::runtime_error("null path");
+        if (!m->llama) throw std::runtime_error("export_gguf: only the llama family maps onto the GGUF llama layout");
+        const nn::LlamaConfig& lc = m->llama->cfg;
+        gguf::LlamaExportConfig c;
+        if (name) c.name = name;
+        c.context_length = static_cast<uint32_t>(context_length);
+        c.embedding_length = static_cast<uint32_t>(lc.d);
+        c.block_count = static_cast<uint32_t>(lc.n_layers);
+        c.feed_forward_length = static_cast<uint32_t>(lc.d_ff);
+        c.head_count = static_cast<uint32_t>(lc.n_heads);
+        c.head_count_kv = static_cast<uint32_t>(lc.n_kv_heads);
+        c.vocab_size = static_cast<uint32_t>(lc.vocab);
+        c.rms_eps = 1e-5f;  // what ops::rmsnorm computes with
+        c.rope_freq_base = lc.rope_theta;
+        c.weights_in_out = true;  // Linear stores [in, out]
+        gguf::export_gguf_llama(gguf_path, m->llama->merged_state(), c, nullptr);
     });
 }
 

@@ -255,6 +255,11 @@ class Model:
         """QLoRA models: the equivalent dense model's weights file (base + merged LoRA)."""
         _check(libmt().mt_model_save_merged(self._h, weights_path.encode()), "mt_model_save_merged")
 
+    def export_gguf(self, path: str, name: str = "microtorch-model", context_length: int = 2048):
+        """GGUF v3 file of a llama-family model (adapters merged), the reference exporter's layout."""
+        _check(libmt().mt_model_export_gguf(self._h, path.encode(), name.encode(), context_length),
+               "mt_model_export_gguf")
+
     def clip_grad_norm(self, max_norm: float) -> float:
         n = ctypes.c_float(0.0)
         _check(libmt().mt_model_clip_grad_norm(self._h, max_norm, ctypes.byref(n)), "mt_model_clip_grad_norm")
