@@ -41,7 +41,8 @@ int mt_model_create(const char* spec, void** model_h);
 int mt_model_destroy(void* model);
 int mt_model_set_checkpoint(void* model, int on);
 /* rows > 0: the vocabulary projection and the cross entropy run fused over chunks of that many
- * rows, so the [tokens, vocab] logits never exist as a whole (default 16384). rows = 0: the two
+ * rows, so the [tokens, vocab] logits never exist as a whole (default: about 2^29 logits per chunk,
+ * i.e. 16384 rows for a 32000-word vocabulary, 3072 for 151936). rows = 0: the two
  * separate ops of the reference (src/llama.cpp:85-88 then src/ops.cpp:350-376). */
 int mt_model_set_loss_chunk(void* model, int64_t rows);
 

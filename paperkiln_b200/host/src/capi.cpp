@@ -100,6 +100,15 @@ struct SpecReader {
     }
 };
 
+// Rows per chunk of the fused head + loss: about 2^29 logits per chunk (1 GiB in bf16), so a wide
+// vocabulary gets shorter chunks; 1024 ... 16384 rows, a multiple of 1024.
+size_t default_loss_chunk(size_t vocab) {
+    size_t rows = (size_t(1) << 29) / (vocab ? vocab : 1) / 1024 * 1024;
+    if (rows < 1024) rows = 1024;
+    if (rows > 16384) rows = 16384;
+    return rows;
+}
+
 // Index of the transformer block a parameter belongs to, or -1.
 long block_of(const std::string& name) {
     for (const char* prefix : {"layers.", "h."}) {
@@ -182,6 +191,7 @@ int mt_model_create(const char* spec, void** out) {
             r.finish();
             m->llama = std::make_shared<nn::Llama>(c, seed);
             m->named = m->llama->named_parameters();
+            m->loss_chunk = default_loss_chunk(c.vocab);
         } else if (m->family == "gpt2") {
             nn::GPT2Config c;
             c.vocab = r.num("vocab", 50257);
@@ -192,6 +202,7 @@ int mt_model_create(const char* spec, void** out) {
             r.finish();
             m->gpt2 = std::make_shared<nn::GPT2>(c, seed);
             m->named = m->gpt2->named_parameters();
+            m->loss_chunk = default_loss_chunk(c.vocab);
         } else if (m->family == "flex") {
             parity::FlexConfig c;
             c.vocab = r.num("vocab", 97);
@@ -206,6 +217,7 @@ int mt_model_create(const char* spec, void** out) {
             r.finish();
             m->flex = std::make_shared<parity::FlexLM>(c, seed);
             m->named = m->flex->named_parameters();
+            m->loss_chunk = default_loss_chunk(c.vocab);
         } else if (m->family == "block") {
             nn::LlamaConfig c;
             c.d = r.num("d", 128);
