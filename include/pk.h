@@ -240,9 +240,10 @@ int pk_attn_last_path(void);
  * gave up). Synchronises the device; clear != 0 resets it. */
 int pk_attn_tc_status(int* status_h, int clear);
 int pk_attn_force_simt(int on);
-/* Which tensor-core forward kernel runs: 1 (default) = warp-specialised, two 128-query slots per
- * CTA with P and O kept in tensor memory; 0 = one 128-query tile per CTA. Same results up to
- * rounding; meant for tests and measurements. */
+/* Which tensor-core forward kernel runs: 2 (default) = warp-specialised, two 128-query slots per
+ * CTA with P and O kept in tensor memory, one thread per score row; 1 = the same with two threads
+ * per row; 0 = one 128-query tile per CTA. Same results up to rounding; meant for tests and
+ * measurements. */
 int pk_attn_fwd_variant(int variant);
 /* The same for the tensor-core backward: 1 (default) = warp-specialised (scores of the next
  * tiles computed while the current ones are processed, P / dS kept in tensor memory), 0 = one

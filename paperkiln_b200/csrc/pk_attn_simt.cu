@@ -254,7 +254,10 @@ int attn_bwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int6
                 void* dk_, int64_t lddk, void* dv, int64_t lddv, float* scratch, int64_t B, int64_t S, int Hq, int Hkv,
                 int dk, float scale, int causal);
 size_t attn_bwd_ws_scratch_bytes(int64_t B, int64_t S, int Hq);
-static int g_attn_fwd_variant = 1;  // 1: warp-specialised forward (pk_attn_fwd_ws.cu), 0: single-tile forward (pk_attn_tc.cu)
+static int g_attn_fwd_variant = 2;  // 2: one thread per row (pk_attn_fwd_row.cu), 1: two threads per row (pk_attn_fwd_ws.cu), 0: single-tile forward (pk_attn_tc.cu)
+int attn_fwd_row(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
+                 void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
+                 int causal);
 
 int attn_fwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                 void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
@@ -363,6 +366,8 @@ int pk_attn_fwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     ProfScope prof(PROF_ATTN_FWD, (causal ? 2.0 : 4.0) * B * S * S * Hq * dk, as_stream(stream));
     if (!g_attn_force_simt && attn_tc_supported(dtype, dk, q, ldq, k, ldk, v, ldv, out, ldo, B, S)) {
         g_attn_last_path = 1;
+        if (g_attn_fwd_variant == 2)
+            return attn_fwd_row(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
         if (g_attn_fwd_variant == 1)
             return attn_fwd_ws(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
         return attn_tc_fwd(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
@@ -426,7 +431,7 @@ int pk_attn_bwd_variant(int variant) {
     return PK_OK;
 }
 int pk_attn_fwd_variant(int variant) {
-    PK_REQUIRE(variant == 0 || variant == 1, "unknown forward variant");
+    PK_REQUIRE(variant >= 0 && variant <= 2, "unknown forward variant");
     g_attn_fwd_variant = variant;
     return PK_OK;
 }

@@ -36,6 +36,7 @@ extern "C" int pk_debug_read_fwd(long long* out_h) {
 #endif
 int attn_bwd_tc_status(int* status_h, int clear);  // pk_attn_bwd_tc.cu
 int attn_fwd_ws_status(int* status_h, int clear);  // pk_attn_fwd_ws.cu
+int attn_fwd_row_status(int* status_h, int clear);  // pk_attn_fwd_row.cu
 int attn_bwd_ws_status(int* status_h, int clear);  // pk_attn_bwd_ws.cu
 
 namespace tc {
@@ -422,6 +423,10 @@ int pk_attn_tc_status(int* status_h, int clear) {
     const int rc2 = pk::attn_fwd_ws_status(&ws, clear);
     if (rc2 != PK_OK) return rc2;
     *status_h |= ws;
+    int row = 0;
+    const int rc4 = pk::attn_fwd_row_status(&row, clear);
+    if (rc4 != PK_OK) return rc4;
+    *status_h |= row;
     int wsb = 0;
     const int rc3 = pk::attn_bwd_ws_status(&wsb, clear);
     if (rc3 != PK_OK) return rc3;

@@ -483,9 +483,10 @@ def test_attention(pk, dtype, cfg):
 @pytest.mark.parametrize("cfg", [(2, 200, 2, 2, 64, True), (1, 640, 4, 1, 64, True), (2, 333, 2, 2, 128, False),
                                  (1, 1100, 2, 2, 128, True)])
 def test_attention_tensor_core_variants(pk, cfg):
-    """The two tensor-core forward kernels (one 128-query tile per CTA / two slots per CTA with O
-    kept in tensor memory and rescaled only when a row maximum grows by more than 2^8) and the
-    two backward kernels agree with the fp32 restatement of ops::fused_attention
+    """The three tensor-core forward kernels (0: one 128-query tile per CTA; 1: two slots per CTA
+    with O kept in tensor memory and rescaled only when a row maximum grows by more than 2^8, two
+    threads per score row; 2: the same with one thread per row, the default) and the two backward
+    kernels agree with the fp32 restatement of ops::fused_attention
     (src/ops.cpp:863-934). Queries are scaled up so that row maxima keep growing along the keys
     and the in-place rescale of the running output is exercised."""
     B, S, Hq, Hkv, dk, causal = cfg
@@ -503,9 +504,9 @@ def test_attention_tensor_core_variants(pk, cfg):
     ref.backward(do.float())
     outs = {}
     try:
-        for variant in (0, 1):
+        for variant in (0, 1, 2):
             pkt.check(pk.pk_attn_fwd_variant(variant))
-            pkt.check(pk.pk_attn_bwd_variant(variant))
+            pkt.check(pk.pk_attn_bwd_variant(min(variant, 1)))
             out = torch.empty_like(q)
             lse = torch.empty(R, Hq, device="cuda")
             pkt.check(pk.pk_attn_fwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
@@ -525,10 +526,11 @@ def test_attention_tensor_core_variants(pk, cfg):
             close(dv, vf.grad, 6e-2, 2 ** -5)
             outs[variant] = (out, lse, dq, dkk, dv)
     finally:
-        pkt.check(pk.pk_attn_fwd_variant(1))
+        pkt.check(pk.pk_attn_fwd_variant(2))
         pkt.check(pk.pk_attn_bwd_variant(1))
     # the log-sum-exp does not depend on how often the running output was rescaled
     close(outs[0][1], outs[1][1], 1e-3)
+    close(outs[0][1], outs[2][1], 1e-3)
 
 
 def test_attention_batch_isolation(pk):
