@@ -97,7 +97,7 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                    const __grid_constant__ CUtensorMap map_v, const RowParams p) {
     using L = RowLayout<DK>;
     constexpr int NS = L::NS;
-        extern __shared__ uint8_t smem_raw[];
+    extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
     uint64_t* q_full = bars;            // [2]
@@ -149,7 +149,7 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // (threads x registers per thread of the compiled kernel), not the SM's whole file; an
     // increase that the pool cannot cover would wait forever. The control warpgroup shrinks to
     // WS_REGS_CTRL and the softmax warps grow to WS_REGS_SOFT; launch_row() refuses to launch
-    // unless 512 * WS_REGS_SOFT + 128 * WS_REGS_CTRL fits the launch allocation.
+    // unless 256 * WS_REGS_SOFT + 128 * WS_REGS_CTRL fits the launch allocation (384 threads x 168).
     // setmaxnreg is a warpgroup-wide aligned instruction: all four warps of the control
     // warpgroup execute the one instance below before they part ways.
     if (warp >= WS_SOFT_WARPS) {
