@@ -135,7 +135,14 @@ int mt_model_optimizer_steps_get(void* model, int64_t* t_h);
 int mt_model_optimizer_steps_set(void* model, int64_t t);
 int mt_model_optimizer_state_get(void* model, int64_t index, float* m_h, float* v_h);
 int mt_model_optimizer_state_set(void* model, int64_t index, const float* m_h, const float* v_h);
+/* ops::clip_grad_norm (src/ops.cpp:1046-1064): global L2 norm of all gradients, summed in
+ * double on the device; when it exceeds max_norm every gradient is scaled by max_norm / norm.
+ * *norm_h receives the norm before clipping. */
 int mt_model_clip_grad_norm(void* model, float max_norm, float* norm_h);
+/* The same op on n host arrays [rows_h[i], cols_h[i]] taken as the gradients of n variables:
+ * uploaded, clipped on the device, written back in place. */
+int mt_clip_grad_norm_arrays(int n, const int64_t* rows_h, const int64_t* cols_h, float* const* grads_h, float max_norm,
+                             float* norm_h);
 
 /* Gradient ranges for data parallelism: bucket i < n-1 is the contiguous fp32 gradient
  * range of transformer block i; the last bucket holds everything else (embeddings,

@@ -93,13 +93,21 @@ int pk_prof_summary(int kind, double* ms_h, double* work_h, int64_t* launches_h)
  * bf16 inputs take the tcgen05 tensor-core kernel when M,N,K and the leading
  * dimensions meet its alignment (multiples of 8 elements, 16-byte aligned
  * bases); other shapes take a SIMT kernel. pk_gemm_last_path() tells which
- * one the last call on this thread used (0 SIMT fp32, 1 SIMT bf16, 2 tcgen05). */
+ * one the last call on this thread used (0 SIMT fp32, 1 SIMT bf16, 2 tcgen05, 3 tcgen05 on
+ * CTA pairs, 4 the Q8_0 kernel of pk_gemm_q8_lora). */
 int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b,
             int64_t M, int64_t N, int64_t K,
             const void* A, int64_t lda, const void* B, int64_t ldb,
             void* C, int64_t ldc, int accumulate,
             const float* bias, const void* residual, int64_t ldr);
 int pk_gemm_last_path(void);
+/* Launch counts per kernel path since the last reset, for a host that wants to know which
+ * kernels a whole step ran on (the last-path calls only see one launch). counts_h[0..n):
+ * 0 GEMM SIMT fp32, 1 GEMM SIMT bf16, 2 GEMM tcgen05 (one CTA per tile), 3 GEMM tcgen05 on CTA
+ * pairs, 4 Q8_0 dequantise-GEMM, 5 attention forward SIMT, 6 attention forward tcgen05,
+ * 7 attention backward SIMT, 8 attention backward tcgen05. reset != 0 zeroes them afterwards.
+ * Host-side counters; not synchronised between threads. */
+int pk_launch_counts(int64_t* counts_h, int n, int reset);
 /* Status word of the tensor-core kernel: non-zero (PK_ERR_TIMEOUT) when one of its
  * bounded mbarrier waits gave up. Synchronises the device; clear != 0 resets it. */
 int pk_gemm_tc_status(int* status_h, int clear);
@@ -237,18 +245,27 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
  * head_dim 64 or 128 and 16-byte aligned rows takes the tcgen05 kernels. */
 int pk_attn_last_path(void);
 /* Status word of the tensor-core attention kernels (PK_ERR_TIMEOUT when a bounded wait
- * gave up). Synchronises the device; clear != 0 resets it. */
+ * gave up). Synchronises the device; clear != 0 resets it. A host that launches these kernels
+ * should read (and clear) the word wherever it synchronises anyway: a launch that timed out
+ * has left its outputs incomplete. */
 int pk_attn_tc_status(int* status_h, int clear);
 int pk_attn_force_simt(int on);
-/* Which tensor-core forward kernel runs: 2 (default) = warp-specialised, two 128-query slots per
- * CTA with P and O kept in tensor memory, one thread per score row; 1 = the same with two threads
- * per row; 0 = one 128-query tile per CTA. Same results up to rounding; meant for tests and
- * measurements. */
-int pk_attn_fwd_variant(int variant);
-/* The same for the tensor-core backward: 1 (default) = warp-specialised (scores of the next
- * tiles computed while the current ones are processed, P / dS kept in tensor memory), 0 = one
- * tile at a time per CTA. */
-int pk_attn_bwd_variant(int variant);
+/* All status words of the tensor-core kernels (GEMM and attention) ORed together, without a
+ * device synchronisation: for a host that has just synchronised the stream it launched on (a
+ * training step reading its loss back). clear != 0 resets the words that were set. */
+int pk_kernel_status(int* status_h, int clear);
+/* Limit of the bounded device-side waits of every tensor-core kernel (GEMM and attention): a
+ * wait on an mbarrier that lasts longer gives up, ORs PK_ERR_TIMEOUT into its family's status
+ * word and lets the kernel drain and return (no trap, tensor memory released). Default 2 s;
+ * the limit is given in microseconds and converted to SM clock cycles at the highest clock, so
+ * a wait never gives up earlier than asked. Applies to launches made after the call. */
+int pk_set_wait_limit_us(double microseconds);
+/* Self-test of that path: one warp waits on an mbarrier nobody arrives at, under the current
+ * limit. On return *status_h holds the status the wait recorded (PK_ERR_TIMEOUT expected; the
+ * word is cleared) and *waited_us_h how long the warp waited. Synchronises the stream and
+ * allocates 8 bytes for the duration of the call. The status words of the GEMM and attention
+ * kernels are separate and stay untouched. */
+int pk_wait_selftest(void* stream, int* status_h, double* waited_us_h);
 
 /* ---- embedding / loss --------------------------------------------------------
  * Row gather out[i,:] = table[ids[i],:] (pure copy; table has the out dtype).
@@ -296,6 +313,34 @@ int pk_adamw(void* stream, float* p, const float* g, float* m, float* v, int64_t
 int pk_q8_quantize(void* stream, const float* W, int8_t* q, uint16_t* scales, int64_t rows, int64_t cols);
 int pk_q8_dequantize(void* stream, const int8_t* q, const uint16_t* scales, int out_dtype, void* out,
                      int64_t rows, int64_t cols);
+/* The reference's own block quantisation (src/quant.cpp:11-48) for any block length, a short last
+ * block included: fp32 scale = absmax / 127 per block (1.0 for an all-zero block), scales
+ * [rows, ceil(cols / block)], q = round-half-away(clamp(x / s, -127, 127)); dequantisation is
+ * float(q) * scale. Bit-identical to the reference on the same input. */
+int pk_q8_quantize_block(void* stream, const float* W, int8_t* q, float* scales, int64_t rows, int64_t cols,
+                         int64_t block);
+int pk_q8_dequantize_block(void* stream, const int8_t* q, const float* scales, int64_t block, int out_dtype, void* out,
+                           int64_t rows, int64_t cols);
+/* Fused dequantise-GEMM over a frozen Q8_0 weight with the LoRA side path in the same accumulator:
+ *     C[M,N] (+)= A[M,K] . deq(W) + XA[M,r] . L (+ bias) (+ residual)
+ * A, XA, L are bf16; accumulation is fp32 in tensor memory; C / residual have c_dtype.
+ *   trans_w = 0   W is the quantised matrix [K, N] with scales [K, N/32]; L is [r, N].
+ *                 The forward of QLinear / QLoRALinear: y = x deq(W) + (s x A) B with XA = s x A,
+ *                 L = B (src/quant.cpp:91-119; the reference multiplies by a dequantised fp32 copy).
+ *   trans_w = 1   W is [N, K] with scales [N, K/32] and is used transposed; L is [N, r], used
+ *                 transposed. The input gradient: dx = dy deq(W)^T + (s dy B^T) A^T.
+ * XA == NULL (r = 0) leaves the LoRA term out. The int8 tiles and their fp16 scales are brought
+ * into shared memory, expanded there to bf16 -- float(q) * float(scale) in fp32, one rounding to
+ * bf16, the bits pk_q8_dequantize writes -- straight into the swizzled operand buffer that
+ * tcgen05.mma reads; the weight never exists in bf16 in global memory. The result equals
+ * pk_gemm over [A | XA] and [deq(W); L] bit for bit (same products, same k order).
+ * Needs: W's column count a multiple of 32, 16-byte aligned bases, lda / ldxa / ldl / ldc / ldr
+ * multiples of 8, r a multiple of 8 and <= 64. Other requests return PK_ERR_UNSUPPORTED; the
+ * caller can always dequantise and call pk_gemm. pk_gemm_last_path reports 4. */
+int pk_gemm_q8_lora(void* stream, int c_dtype, int trans_w, int64_t M, int64_t N, int64_t K,
+                    const void* A, int64_t lda, const int8_t* Wq, const uint16_t* scales,
+                    const void* XA, int64_t ldxa, const void* L, int64_t ldl, int r,
+                    void* C, int64_t ldc, int accumulate, const float* bias, const void* residual, int64_t ldr);
 
 #ifdef __cplusplus
 }

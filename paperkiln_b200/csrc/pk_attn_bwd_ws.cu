@@ -40,21 +40,9 @@
 
 namespace pk {
 
-__device__ int g_attn_bwd_ws_status = 0;
+PK_DEFINE_WAITCTL(attn_bwd_ws)
 
 using namespace tc;
-
-#ifdef PK_WS_TIMING
-// Development aid (not compiled into the library): clock64 stamps of one CTA's iterations 8 / 9.
-__device__ long long g_bws_dbg[128];
-#define BWS_T(kern, role, i, iter) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && ((iter) >> 1) == 4) g_bws_dbg[(kern) * 64 + (role) * 16 + (i)] = clock64(); } while (0)
-extern "C" int pk_debug_read_bws(long long* out_h) {
-    cudaDeviceSynchronize();
-    return cudaMemcpyFromSymbol(out_h, g_bws_dbg, sizeof(long long) * 128) == cudaSuccess ? 0 : 2;
-}
-#else
-#define BWS_T(kern, role, i, iter) do { } while (0)
-#endif
 
 namespace {
 
@@ -236,7 +224,7 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             tma_tile<DK>(sDO, &map_do, h * DK, seq0 + q0, smem_u32(qdo_full), CH128);
             for (int j = 0; j < nkv; ++j) {
                 const int st = j % NS, n = j / NS;
-                if (n > 0) ok = mbar_wait(smem_u32(&kv_empty[st]), (n - 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (n > 0) ok = mbar_wait(smem_u32(&kv_empty[st]), (n - 1) & 1, abort_flag, &g_attn_bwd_ws_ctl);
                 if (!ok) break;
                 const int64_t row = seq0 + static_cast<int64_t>(j) * BW_COLS;
                 mbar_expect_tx(smem_u32(&kv_full[st]), 2 * L::TILEK);
@@ -255,8 +243,8 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 const int bsel = j % NB;
                 // K_j landed long ago (S(j) used it); this thread observes its barrier too before reading it --
                 // first, so that only the wait on the critical path follows the group's arrival
-                ok = mbar_wait(smem_u32(&kv_full[j % NS]), (j / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (ok) ok = mbar_wait(smem_u32(&ds_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&kv_full[j % NS]), (j / NS) & 1, abort_flag, &g_attn_bwd_ws_ctl);
+                if (ok) ok = mbar_wait(smem_u32(&ds_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_ctl);
                 if (!ok) break;
                 fence_after();
                 const uint32_t kmn = kmn_lo0 + (j % NS) * (L::TILEK >> 4);
@@ -291,9 +279,9 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                     mma_ss(t, a_lo + kstep_kmajor(k, CH128), b_lo + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
                 commit(smem_u32(&s_full[j % NB]));
             };
-            ok = mbar_wait(smem_u32(qdo_full), 0, abort_flag, &g_attn_bwd_ws_status);
+            ok = mbar_wait(smem_u32(qdo_full), 0, abort_flag, &g_attn_bwd_ws_ctl);
             for (int j = 0; j < NB && j < nkv && ok; ++j) {
-                ok = mbar_wait(smem_u32(&kv_full[j % NS]), 0, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&kv_full[j % NS]), 0, abort_flag, &g_attn_bwd_ws_ctl);
                 if (ok) {
                     fence_after();
                     issue(j);
@@ -302,8 +290,8 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int j = 0; j + NB < nkv && ok; ++j) {
                 // buffer j % NB is free once dQ of tile j has consumed the dS packed into it (which also
                 // means that the element-wise group has read S(j) and dP(j))
-                ok = mbar_wait(smem_u32(&kv_full[(j + NB) % NS]), ((j + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (ok) ok = mbar_wait(smem_u32(&dq_done[j % NB]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&kv_full[(j + NB) % NS]), ((j + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_ctl);
+                if (ok) ok = mbar_wait(smem_u32(&dq_done[j % NB]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_ctl);
                 if (!ok) break;
                 fence_after();
                 issue(j + NB);
@@ -329,19 +317,16 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         bool ok = true;
         for (int j = grp; j < nkv; j += 2) {
             const int kv0 = j * BW_COLS;
-            if (wl == 0 && lane == 0) BWS_T(0, grp, 0, j);
             const int bsel = j % NB;
             const uint32_t t_s = t_col + bsel * 128, t_dp = t_s + 64;
-            ok = mbar_wait(smem_u32(&s_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+            ok = mbar_wait(smem_u32(&s_full[bsel]), (j / NB) & 1, abort_flag, &g_attn_bwd_ws_ctl);
             ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tensor-memory accesses are warp-wide
             if (!ok) break;
-            if (wl == 0 && lane == 0) BWS_T(0, grp, 1, j);
             fence_after();
             uint32_t rs[32], rd[32];
             tmem_ld32(t_s, rs);
             tmem_ld32(t_dp, rd);
             tmem_wait_ld();
-            if (wl == 0 && lane == 0) BWS_T(0, grp, 2, j);
             const bool need_mask = (p.causal && kv0 + BW_COLS - 1 > q0) || (kv0 + BW_COLS > p.S);
             const int key0 = kv0 + hf * 32;
             uint32_t pk[16];
@@ -363,15 +348,13 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                 f2_unpack(f2_mul(f2_pack(p0, p1), f2_fma(f2_pack_bits(rd[2 * e], rd[2 * e + 1]), sc2, nd2)), d0, d1);
                 pk[e] = pack2(d0, d1);
             }
-            if (wl == 0 && lane == 0) BWS_T(0, grp, 3, j);
             tmem_st16(t_s, pk);   // over this thread's own (already read) S columns
             tmem_wait_st();
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&ds_full[bsel]));
-            if (wl == 0 && lane == 0) BWS_T(0, grp, 4, j);
         }
-        if (ok) ok = mbar_wait(smem_u32(done), 0, abort_flag, &g_attn_bwd_ws_status);
+        if (ok) ok = mbar_wait(smem_u32(done), 0, abort_flag, &g_attn_bwd_ws_ctl);
         ok = __all_sync(0xffffffffu, ok);
         fence_after();
         if (ok) {
@@ -488,7 +471,7 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 const int st = it % NS, n = it / NS;
                 const int h = hk * group + it / per_head;
                 const int q0 = (i_begin + it % per_head) * BW_COLS;
-                if (n > 0) ok = mbar_wait(smem_u32(&q_empty[st]), (n - 1) & 1, abort_flag, &g_attn_bwd_ws_status);
+                if (n > 0) ok = mbar_wait(smem_u32(&q_empty[st]), (n - 1) & 1, abort_flag, &g_attn_bwd_ws_ctl);
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&q_full[st]);
                 mbar_expect_tx(bar, 2 * L::TILEQ + 512);
@@ -509,8 +492,8 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int it = 0; it < nit && ok; ++it) {
                 const int bsel = it % NB;
                 // Q_i / dO_i landed long ago (the scores used them); observe their barrier too, first
-                ok = mbar_wait(smem_u32(&q_full[it % NS]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (ok) ok = mbar_wait(smem_u32(&p_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&q_full[it % NS]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_ctl);
+                if (ok) ok = mbar_wait(smem_u32(&p_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_ctl);
                 if (!ok) break;
                 fence_after();
                 const uint32_t st_off = (it % NS) * (L::TILEQ >> 4);
@@ -547,9 +530,9 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     mma_ss(t, a_lo + kstep_kmajor(k, CH128), b_lo + kstep_kmajor(k, CH64), idesc_s, k > 0 ? 1u : 0u);
                 commit(smem_u32(&s_full[it % NB]));
             };
-            ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, &g_attn_bwd_ws_status);
+            ok = mbar_wait(smem_u32(kv_full), 0, abort_flag, &g_attn_bwd_ws_ctl);
             for (int it = 0; it < NB && it < nit && ok; ++it) {
-                ok = mbar_wait(smem_u32(&q_full[it % NS]), 0, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&q_full[it % NS]), 0, abort_flag, &g_attn_bwd_ws_ctl);
                 if (ok) {
                     fence_after();
                     issue(it);
@@ -557,8 +540,8 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             for (int it = 0; it + NB < nit && ok; ++it) {
                 // the packed P^T / dS^T of tile `it` live in this buffer until dV / dK of that tile are done
-                ok = mbar_wait(smem_u32(&q_full[(it + NB) % NS]), ((it + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
-                if (ok) ok = mbar_wait(smem_u32(&g_done[it % NB]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+                ok = mbar_wait(smem_u32(&q_full[(it + NB) % NS]), ((it + NB) / NS) & 1, abort_flag, &g_attn_bwd_ws_ctl);
+                if (ok) ok = mbar_wait(smem_u32(&g_done[it % NB]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_ctl);
                 if (!ok) break;
                 fence_after();
                 issue(it + NB);
@@ -583,9 +566,9 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             const int q0 = (i_begin + it % per_head) * BW_COLS;
             const int bsel = it % NB;
             const uint32_t t_s = t_col + bsel * 128, t_dp = t_s + 64;
-            ok = mbar_wait(smem_u32(&s_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_status);
+            ok = mbar_wait(smem_u32(&s_full[bsel]), (it / NB) & 1, abort_flag, &g_attn_bwd_ws_ctl);
             // the statistics arrived with Q_i / dO_i: observe that barrier too before reading them
-            if (ok) ok = mbar_wait(smem_u32(&q_full[st]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_status);
+            if (ok) ok = mbar_wait(smem_u32(&q_full[st]), (it / NS) & 1, abort_flag, &g_attn_bwd_ws_ctl);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             fence_after();
@@ -621,7 +604,7 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full[bsel]));
         }
-        if (ok) ok = mbar_wait(smem_u32(done), 0, abort_flag, &g_attn_bwd_ws_status);
+        if (ok) ok = mbar_wait(smem_u32(done), 0, abort_flag, &g_attn_bwd_ws_ctl);
         ok = __all_sync(0xffffffffu, ok);
         fence_after();
         if (ok) {
@@ -747,13 +730,5 @@ int attn_bwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int6
                     : launch_bwd_ws<128>(st, mq128, mdo128, mk64, mv64, mq64, mdo64, mk128, mv128, p, B);
 }
 
-int attn_bwd_ws_status(int* status_h, int clear) {
-    PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, g_attn_bwd_ws_status, sizeof(int)));
-    if (clear) {
-        const int zero = 0;
-        PK_CHECK_CUDA(cudaMemcpyToSymbol(g_attn_bwd_ws_status, &zero, sizeof(int)));
-    }
-    return PK_OK;
-}
 
 }  // namespace pk

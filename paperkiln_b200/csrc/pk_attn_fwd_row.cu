@@ -26,21 +26,9 @@
 
 namespace pk {
 
-__device__ int g_attn_fwd_row_status = 0;
+PK_DEFINE_WAITCTL(attn_fwd_row)
 
 using namespace tc;
-
-#ifdef PK_WS_TIMING
-// Development aid (not compiled into the library): clock64 stamps of one CTA's iteration 5.
-__device__ long long g_row_dbg[64];
-#define WS_T(slot, i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j == 5) g_row_dbg[(slot) * 16 + (i)] = clock64(); } while (0)
-extern "C" int pk_debug_read_row(long long* out_h) {
-    cudaDeviceSynchronize();
-    return cudaMemcpyFromSymbol(out_h, g_row_dbg, sizeof(long long) * 64) == cudaSuccess ? 0 : 2;
-}
-#else
-#define WS_T(slot, i) do { } while (0)
-#endif
 
 namespace {
 
@@ -165,11 +153,11 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             for (int j = 0; j < nkv_max && ok; ++j) {
                 const int st = j % NS, n = j / NS;
                 const int64_t row = seq0 + static_cast<int64_t>(j) * WS_BN;
-                if (n > 0) ok = mbar_wait(smem_u32(&k_empty[st]), (n - 1) & 1, abort_flag, &g_attn_fwd_row_status);
+                if (n > 0) ok = mbar_wait(smem_u32(&k_empty[st]), (n - 1) & 1, abort_flag, &g_attn_fwd_row_ctl);
                 if (!ok) break;
                 mbar_expect_tx(smem_u32(&k_full[st]), L::TILE);
                 load_tile<DK>(sK + st * L::TILE, &map_k, hk * DK, row, smem_u32(&k_full[st]));
-                if (n > 0) ok = mbar_wait(smem_u32(&v_empty[st]), (n - 1) & 1, abort_flag, &g_attn_fwd_row_status);
+                if (n > 0) ok = mbar_wait(smem_u32(&v_empty[st]), (n - 1) & 1, abort_flag, &g_attn_fwd_row_ctl);
                 if (!ok) break;
                 mbar_expect_tx(smem_u32(&v_full[st]), L::TILE);
                 load_tile<DK>(sV + st * L::TILE, &map_v, hk * DK, row, smem_u32(&v_full[st]));
@@ -190,9 +178,9 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int k = 0; k < DK / 16; ++k) mma_ss(d, q_lo + kstep_kmajor(k), k_lo + kstep_kmajor(k), idesc_s, k > 0 ? 1u : 0u);
                 commit(smem_u32(&s_full[s]));
             };
-            ok = mbar_wait(smem_u32(&q_full[0]), 0, abort_flag, &g_attn_fwd_row_status);
-            if (ok) ok = mbar_wait(smem_u32(&q_full[1]), 0, abort_flag, &g_attn_fwd_row_status);
-            if (ok) ok = mbar_wait(smem_u32(&k_full[0]), 0, abort_flag, &g_attn_fwd_row_status);
+            ok = mbar_wait(smem_u32(&q_full[0]), 0, abort_flag, &g_attn_fwd_row_ctl);
+            if (ok) ok = mbar_wait(smem_u32(&q_full[1]), 0, abort_flag, &g_attn_fwd_row_ctl);
+            if (ok) ok = mbar_wait(smem_u32(&k_full[0]), 0, abort_flag, &g_attn_fwd_row_ctl);
             if (ok) {
                 fence_after();
                 issue_s(0, 0);
@@ -205,11 +193,9 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll 1
                 for (int s = 0; s < 2; ++s) {
                     if (j >= nkv[s] || !ok) continue;
-                    WS_T(2, s * 4 + 0);
-                    ok = mbar_wait(smem_u32(&p_full[s]), j & 1, abort_flag, &g_attn_fwd_row_status);
-                    WS_T(2, s * 4 + 1);
+                    ok = mbar_wait(smem_u32(&p_full[s]), j & 1, abort_flag, &g_attn_fwd_row_ctl);
                     if (ok && !v_ready) {
-                        ok = mbar_wait(smem_u32(&v_full[st]), (j / NS) & 1, abort_flag, &g_attn_fwd_row_status);
+                        ok = mbar_wait(smem_u32(&v_full[st]), (j / NS) & 1, abort_flag, &g_attn_fwd_row_ctl);
                         v_ready = true;
                     }
                     if (!ok) break;
@@ -219,10 +205,9 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
                     for (int k = 0; k < WS_BN / 16; ++k)
                         mma_ts(d, a + k * 8, v_lo + kstep_mnmajor(k), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
-                    WS_T(2, s * 4 + 2);
                     if (j + 1 < nkv[s]) {
                         if (!k_ready) {
-                            ok = mbar_wait(smem_u32(&k_full[(j + 1) % NS]), ((j + 1) / NS) & 1, abort_flag, &g_attn_fwd_row_status);
+                            ok = mbar_wait(smem_u32(&k_full[(j + 1) % NS]), ((j + 1) / NS) & 1, abort_flag, &g_attn_fwd_row_ctl);
                             k_ready = true;
                             if (!ok) break;
                             fence_after();
@@ -231,7 +216,6 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     } else {
                         commit(smem_u32(&o_done[s]));
                     }
-                    WS_T(2, s * 4 + 3);
                 }
                 if (!ok) break;
                 commit(smem_u32(&v_empty[st]));                              // V_j free once P.V of both slots is done
@@ -258,9 +242,7 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         bool ok = true;
         for (int j = 0; j < my_nkv; ++j) {
             const int kv0 = j * WS_BN;
-            if (quad == 0 && lane == 0) WS_T(s, 0);
-            ok = mbar_wait(smem_u32(&s_full[s]), j & 1, abort_flag, &g_attn_fwd_row_status);
-            if (quad == 0 && lane == 0) WS_T(s, 1);
+            ok = mbar_wait(smem_u32(&s_full[s]), j & 1, abort_flag, &g_attn_fwd_row_ctl);
             ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the tensor-memory accesses below are warp-wide
             if (!ok) break;                    // nobody waits for this warp at a meeting point
             fence_after();
@@ -268,7 +250,6 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r[c]);
             tmem_wait_ld();
-            if (quad == 0 && lane == 0) WS_T(s, 2);
             const bool need_mask = (p.causal && kv0 + WS_BN - 1 > q0) || (kv0 + WS_BN > p.S);
             if (need_mask) {
 #pragma unroll
@@ -288,7 +269,6 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 mx3 = fmax3(mx3, __uint_as_float(r[3][e]), __uint_as_float(r[3][e + 1]));
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            if (quad == 0 && lane == 0) WS_T(s, 3);
             // Row maximum in log2 units. Every row sees at least one key in its first tile
             // (key 0), so cand is finite from j = 0 on.
             const float cand = fmaxf(m, mx * p.scale_log2);
@@ -312,7 +292,6 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     }
                 }
             }
-            if (quad == 0 && lane == 0) WS_T(s, 4);
             const float neg_m = -m;
             const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(neg_m, neg_m);
             uint64_t sum_a = f2_pack(0.0f, 0.0f), sum_b = sum_a;
@@ -340,16 +319,13 @@ attn_fwd_row_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 f2_unpack(sum_b, s2, s3);
                 l += (s0 + s1) + (s2 + s3);
             }
-            if (quad == 0 && lane == 0) WS_T(s, 5);
             tmem_wait_st();
-            if (quad == 0 && lane == 0) WS_T(s, 6);
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&p_full[s]));
-            if (quad == 0 && lane == 0) WS_T(s, 7);
         }
 
-        if (ok) ok = mbar_wait(smem_u32(&o_done[s]), 0, abort_flag, &g_attn_fwd_row_status);
+        if (ok) ok = mbar_wait(smem_u32(&o_done[s]), 0, abort_flag, &g_attn_fwd_row_ctl);
         ok = __all_sync(0xffffffffu, ok);
         fence_after();
         if (ok) {
@@ -429,13 +405,5 @@ int attn_fwd_row(cudaStream_t st, const void* q, int64_t ldq, const void* k, int
     return dk == 64 ? launch_row<64>(st, mq, mk, mv, p, B) : launch_row<128>(st, mq, mk, mv, p, B);
 }
 
-int attn_fwd_row_status(int* status_h, int clear) {
-    PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, g_attn_fwd_row_status, sizeof(int)));
-    if (clear) {
-        const int zero = 0;
-        PK_CHECK_CUDA(cudaMemcpyToSymbol(g_attn_fwd_row_status, &zero, sizeof(int)));
-    }
-    return PK_OK;
-}
 
 }  // namespace pk

@@ -248,31 +248,17 @@ attn_bwd_dkv_kernel(const T* __restrict__ q, int64_t ldq, const T* __restrict__ 
 
 static thread_local int g_attn_last_path = -1;
 static int g_attn_force_simt = 0;
-static int g_attn_bwd_variant = 1;  // 1: warp-specialised backward (pk_attn_bwd_ws.cu), 0: pk_attn_bwd_tc.cu
+// tcgen05 kernels: forward in pk_attn_fwd_row.cu, backward in pk_attn_bwd_ws.cu
 int attn_bwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                 const void* out, int64_t ldo, const float* lse, const void* dout, int64_t lddo, void* dq, int64_t lddq,
                 void* dk_, int64_t lddk, void* dv, int64_t lddv, float* scratch, int64_t B, int64_t S, int Hq, int Hkv,
                 int dk, float scale, int causal);
 size_t attn_bwd_ws_scratch_bytes(int64_t B, int64_t S, int Hq);
-static int g_attn_fwd_variant = 2;  // 2: one thread per row (pk_attn_fwd_row.cu), 1: two threads per row (pk_attn_fwd_ws.cu), 0: single-tile forward (pk_attn_tc.cu)
 int attn_fwd_row(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                  void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
                  int causal);
-
-int attn_fwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
-                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
-                int causal);
-
-// tensor-core kernels (pk_attn_tc.cu)
 int attn_tc_supported(int dtype, int dk, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v,
-                      int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S);
-int attn_tc_fwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
-                void* out, int64_t ldo, float* lse, int64_t B, int64_t S, int Hq, int Hkv, int dk, float scale,
-                int causal);
-int attn_tc_bwd(cudaStream_t st, const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
-                const float* lse, const float* delta, const void* dout, int64_t lddo, void* dq, int64_t lddq,
-                void* dk_, int64_t lddk, void* dv, int64_t lddv, int64_t B, int64_t S, int Hq, int Hkv, int dk,
-                float scale, int causal);
+                      int64_t ldv, const void* out, int64_t ldo, int64_t B, int64_t S);  // pk_tc_host.cu
 
 struct AttnArgs {
     const void *q, *k, *v, *out, *dout;
@@ -366,20 +352,17 @@ int pk_attn_fwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     ProfScope prof(PROF_ATTN_FWD, (causal ? 2.0 : 4.0) * B * S * S * Hq * dk, as_stream(stream));
     if (!g_attn_force_simt && attn_tc_supported(dtype, dk, q, ldq, k, ldk, v, ldv, out, ldo, B, S)) {
         g_attn_last_path = 1;
-        if (g_attn_fwd_variant == 2)
-            return attn_fwd_row(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
-        if (g_attn_fwd_variant == 1)
-            return attn_fwd_ws(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
-        return attn_tc_fwd(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
+        note_launch(PATH_ATTN_FWD_TC);
+        return attn_fwd_row(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, B, S, Hq, Hkv, dk, scale, causal);
     }
     g_attn_last_path = 0;
+    note_launch(PATH_ATTN_FWD_SIMT);
     if (dtype == PK_F32) return attn_dispatch<float>(as_stream(stream), a, dk, false);
     return attn_dispatch<bf16>(as_stream(stream), a, dk, false);
 }
 
 size_t pk_attn_bwd_scratch_bytes(int64_t B, int64_t S, int Hq) {
-    // delta [B*S, Hq] for the SIMT and single-tile kernels; two head-major padded arrays for the
-    // warp-specialised ones
+    // delta [B*S, Hq] for the SIMT kernel; two head-major padded arrays for the tcgen05 ones
     const size_t plain = static_cast<size_t>(B) * static_cast<size_t>(S) * static_cast<size_t>(Hq) * sizeof(float);
     const size_t ws = attn_bwd_ws_scratch_bytes(B, S, Hq);
     return plain > ws ? plain : ws;
@@ -405,17 +388,12 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
     if (!g_attn_force_simt && attn_tc_supported(dtype, dk, q, ldq, k, ldk, v, ldv, out, ldo, B, S) &&
         attn_tc_supported(dtype, dk, dout, lddo, dk_, lddk, dv, lddv, dq, lddq, B, S)) {
         g_attn_last_path = 1;
-        if (g_attn_bwd_variant == 1)
-            return attn_bwd_ws(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, dout, lddo, dq, lddq, dk_, lddk,
-                               dv, lddv, a.delta, B, S, Hq, Hkv, dk, scale, causal);
-        const int64_t R = B * S;
-        attn_delta_kernel<bf16><<<static_cast<unsigned>((R * Hq + 7) / 8), 256, 0, as_stream(stream)>>>(
-            static_cast<const bf16*>(out), ldo, static_cast<const bf16*>(dout), lddo, a.delta, R, Hq, dk);
-        PK_LAUNCH_CHECK();
-        return attn_tc_bwd(as_stream(stream), q, ldq, k, ldk, v, ldv, lse, a.delta, dout, lddo, dq, lddq, dk_, lddk,
-                           dv, lddv, B, S, Hq, Hkv, dk, scale, causal);
+        note_launch(PATH_ATTN_BWD_TC);
+        return attn_bwd_ws(as_stream(stream), q, ldq, k, ldk, v, ldv, out, ldo, lse, dout, lddo, dq, lddq, dk_, lddk,
+                           dv, lddv, a.delta, B, S, Hq, Hkv, dk, scale, causal);
     }
     g_attn_last_path = 0;
+    note_launch(PATH_ATTN_BWD_SIMT);
     if (dtype == PK_F32) return attn_dispatch<float>(as_stream(stream), a, dk, true);
     return attn_dispatch<bf16>(as_stream(stream), a, dk, true);
 }
@@ -423,16 +401,6 @@ int pk_attn_bwd(void* stream, int dtype, const void* q, int64_t ldq, const void*
 int pk_attn_last_path(void) { return g_attn_last_path; }
 int pk_attn_force_simt(int on) {
     g_attn_force_simt = on ? 1 : 0;
-    return PK_OK;
-}
-int pk_attn_bwd_variant(int variant) {
-    PK_REQUIRE(variant == 0 || variant == 1, "unknown backward variant");
-    g_attn_bwd_variant = variant;
-    return PK_OK;
-}
-int pk_attn_fwd_variant(int variant) {
-    PK_REQUIRE(variant >= 0 && variant <= 2, "unknown forward variant");
-    g_attn_fwd_variant = variant;
     return PK_OK;
 }
 

@@ -55,6 +55,14 @@ struct ProfScope {
     cudaStream_t st;
 };
 
+// Launches per kernel path since the last reset (pk_launch_counts): which kernel a call took is
+// otherwise visible only for the last call of a thread.
+enum PathSlot {
+    PATH_GEMM_SIMT_F32 = 0, PATH_GEMM_SIMT_BF16 = 1, PATH_GEMM_TC = 2, PATH_GEMM_TC_PAIR = 3, PATH_GEMM_Q8 = 4,
+    PATH_ATTN_FWD_SIMT = 5, PATH_ATTN_FWD_TC = 6, PATH_ATTN_BWD_SIMT = 7, PATH_ATTN_BWD_TC = 8, PATH_SLOTS = 9
+};
+void note_launch(int slot);
+
 // Number of SMs of the current device (cached); grids of the bandwidth-bound
 // kernels are sized in multiples of it.
 int sm_count();

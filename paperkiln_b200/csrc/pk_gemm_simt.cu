@@ -137,6 +137,8 @@ int launch_simt(cudaStream_t st, int ta, int tb, int64_t M, int64_t N, int64_t K
     return PK_OK;
 }
 
+void gemm_note_path(int path) { g_last_path = path; }  // for the kernels with an entry point of their own
+
 }  // namespace pk
 
 using namespace pk;
@@ -165,21 +167,25 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
             const double fill = static_cast<double>(t2) / static_cast<double>((t2 + pairs - 1) / pairs * pairs);
             if (N >= 256 && M >= 256 && fill >= 0.8) {
                 g_last_path = 3;
+                note_launch(PATH_GEMM_TC_PAIR);
                 return gemm_tc2_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate, bias,
                                        residual, ldr);
             }
         }
         g_last_path = 2;
+        note_launch(PATH_GEMM_TC);
         return gemm_tc_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate,
                               bias, residual, ldr);
     }
     ProfScope prof(PROF_GEMM_SIMT, 2.0 * M * N * K, st);
     if (ab_dtype == PK_F32) {
         g_last_path = 0;
+        note_launch(PATH_GEMM_SIMT_F32);
         return launch_simt<float, float>(st, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate,
                                          bias, residual, ldr);
     }
     g_last_path = 1;
+    note_launch(PATH_GEMM_SIMT_BF16);
     if (c_dtype == PK_F32)
         return launch_simt<bf16, float>(st, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate,
                                         bias, residual, ldr);

@@ -19,18 +19,16 @@
 // loop, tensor memory is released and the kernel returns.
 #include <cuda.h>
 
-#include <mutex>
-
 #include "pk_common.cuh"
+#include "pk_tc.cuh"
 
 namespace pk {
 
-__device__ int g_gemm_tc_status = 0;
+PK_DEFINE_WAITCTL(gemm_tc)
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;            // 64 bf16 = 128 bytes = one swizzle row
 constexpr int TC_THREADS = 192;
-constexpr uint64_t TC_WAIT_LIMIT_NS = 2000000000ull;
 
 struct TcParams {
     int64_t M, N, K;
@@ -82,19 +80,7 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity) {
 // Bounded wait. Returns false when the wait was abandoned (time limit, or another
 // role already raised the abort flag).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try(bar, parity)) return true;
-        if ((it & 255u) == 0u) {
-            if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > TC_WAIT_LIMIT_NS) {
-                *abort_flag = 1;
-                atomicOr(&g_gemm_tc_status, PK_ERR_TIMEOUT);
-                return false;
-            }
-        }
-    }
+    return tc::mbar_wait(bar, parity, abort_flag, &g_gemm_tc_ctl);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y,
                                             uint32_t bar) {
@@ -159,6 +145,7 @@ __host__ __device__ inline uint32_t make_idesc(int n, int a_mn_major, int b_mn_m
 }
 
 int gemm_tc2_status(int* status_h, int clear);  // pk_gemm_tc2.cu
+int gemm_q8_status(int* status_h, int clear);   // pk_gemm_q8.cu
 
 template <int BN>
 struct TcCfg {
@@ -452,47 +439,6 @@ int gemm_splitk_reduce(cudaStream_t st, int c_dtype, const float* partial, int s
 }
 
 // ---- host side --------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, []() {
-        void* sym = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(sym);
-    });
-    return fn;
-}
-
-// 2-D bf16 tensor map over a row-major [outer, inner] matrix with row stride ld elements.
-static int make_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld,
-                    int box_inner, int box_outer) {
-    EncodeTiledFn fn = get_encode_fn();
-    if (!fn) {
-        set_error("cuTensorMapEncodeTiled is not available from the driver");
-        return PK_ERR_CUDA;
-    }
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        set_error("cuTensorMapEncodeTiled failed with code %d (inner %lld outer %lld ld %lld)", static_cast<int>(r),
-                  static_cast<long long>(inner), static_cast<long long>(outer), static_cast<long long>(ld));
-        return PK_ERR_CUDA;
-    }
-    return PK_OK;
-}
-
 int gemm_tc_supported(int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A,
                       int64_t lda, const void* B, int64_t ldb, const void* C, int64_t ldc,
                       const void* residual, int64_t ldr, const float* bias) {
@@ -566,11 +512,11 @@ int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int6
     }
     CUtensorMap ma, mb;
     int rc;
-    if (!a_mn) rc = make_map(&ma, A, K, M, lda, TC_BK, TC_BM);
-    else rc = make_map(&ma, A, M, K, lda, 64, TC_BK);
+    if (!a_mn) rc = tc::make_tensor_map(&ma, A, K, M, lda, TC_BK, TC_BM);
+    else rc = tc::make_tensor_map(&ma, A, M, K, lda, 64, TC_BK);
     if (rc != PK_OK) return rc;
-    if (!b_mn) rc = make_map(&mb, B, K, N, ldb, TC_BK, bn);
-    else rc = make_map(&mb, B, N, K, ldb, 64, TC_BK);
+    if (!b_mn) rc = tc::make_tensor_map(&mb, B, K, N, ldb, TC_BK, bn);
+    else rc = tc::make_tensor_map(&mb, B, N, K, ldb, 64, TC_BK);
     if (rc != PK_OK) return rc;
     TcParams p;
     p.M = M; p.N = N; p.K = K;
@@ -608,20 +554,17 @@ int pk_gemm_set_workspace(void* ptr, size_t bytes) {
 }
 int pk_gemm_last_splits(void) { return pk::g_last_splits; }
 
-// Reads (and clears when `clear` != 0) the status word the tensor-core GEMM writes when
-// a bounded wait gives up. Synchronises the device.
+// Reads (and clears when `clear` != 0) the status words the tensor-core GEMM kernels write
+// when a bounded wait gives up. Synchronises the device.
 int pk_gemm_tc_status(int* status_h, int clear) {
     PK_REQUIRE(status_h != nullptr, "null output");
     PK_CHECK_CUDA(cudaDeviceSynchronize());
-    PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, pk::g_gemm_tc_status, sizeof(int)));
-    if (clear) {
-        const int zero = 0;
-        PK_CHECK_CUDA(cudaMemcpyToSymbol(pk::g_gemm_tc_status, &zero, sizeof(int)));
-    }
-    int pair = 0;  // the CTA-pair kernel (pk_gemm_tc2.cu) keeps its own word
-    const int rc = pk::gemm_tc2_status(&pair, clear);
+    int one = 0, pair = 0, q8 = 0;
+    int rc = pk::gemm_tc_status(&one, clear);
+    if (rc == PK_OK) rc = pk::gemm_tc2_status(&pair, clear);   // CTA-pair kernel (pk_gemm_tc2.cu)
+    if (rc == PK_OK) rc = pk::gemm_q8_status(&q8, clear);      // Q8_0 kernel (pk_gemm_q8.cu)
     if (rc != PK_OK) return rc;
-    *status_h |= pair;
+    *status_h = one | pair | q8;
     return PK_OK;
 }
 

@@ -28,7 +28,7 @@
 
 namespace pk {
 
-__device__ int g_gemm_tc2_status = 0;
+PK_DEFINE_WAITCTL(gemm_tc2)
 
 namespace {
 
@@ -113,7 +113,7 @@ __host__ __device__ inline uint32_t idesc_pair(int n, int a_mn_major, int b_mn_m
     return d;
 }
 __device__ __forceinline__ bool wait2(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    return mbar_wait(bar, parity, abort_flag, &g_gemm_tc2_status);
+    return mbar_wait(bar, parity, abort_flag, &g_gemm_tc2_ctl);
 }
 
 template <typename TC>
@@ -437,13 +437,5 @@ int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int
     return launch2<bf16>(st, ma, mb, p, c_dtype);
 }
 
-int gemm_tc2_status(int* status_h, int clear) {
-    PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, g_gemm_tc2_status, sizeof(int)));
-    if (clear) {
-        const int zero = 0;
-        PK_CHECK_CUDA(cudaMemcpyToSymbol(g_gemm_tc2_status, &zero, sizeof(int)));
-    }
-    return PK_OK;
-}
 
 }  // namespace pk

@@ -95,6 +95,40 @@ q8_dequantize_kernel(const int8_t* __restrict__ q, const __half* __restrict__ sc
     }
 }
 
+// Block quantisation with any block length and fp32 scales (the reference's quantize_int8,
+// src/quant.cpp:11-37): one warp per (row, block); the last block of a row may be short.
+__global__ void __launch_bounds__(256)
+q8_quantize_block_kernel(const float* __restrict__ W, int8_t* __restrict__ q, float* __restrict__ scales,
+                         int64_t rows, int64_t cols, int64_t block, int64_t bpr) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * 8, n = rows * bpr;
+    for (int64_t b = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); b < n; b += warps) {
+        const int64_t row = b / bpr, j0 = (b % bpr) * block;
+        const int64_t j1 = j0 + block < cols ? j0 + block : cols;
+        const float* src = W + row * cols;
+        float amax = 0.0f;
+        for (int64_t j = j0 + lane; j < j1; j += 32) amax = fmaxf(amax, fabsf(src[j]));
+        amax = warp_max(amax);
+        const float s = amax > 0.0f ? amax / 127.0f : 1.0f;
+        for (int64_t j = j0 + lane; j < j1; j += 32) {
+            const float v = fmaxf(-127.0f, fminf(127.0f, src[j] / s));
+            q[row * cols + j] = static_cast<int8_t>(static_cast<int>(roundf(v)));
+        }
+        if (lane == 0) scales[b] = s;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+q8_dequantize_block_kernel(const int8_t* __restrict__ q, const float* __restrict__ scales, T* __restrict__ out,
+                           int64_t rows, int64_t cols, int64_t block, int64_t bpr) {
+    const int64_t n = rows * cols, stride = static_cast<int64_t>(gridDim.x) * 256;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < n; i += stride) {
+        const int64_t row = i / cols, col = i % cols;
+        out[i] = from_f32<T>(static_cast<float>(q[i]) * scales[row * bpr + col / block]);
+    }
+}
+
 }  // namespace pk
 
 using namespace pk;
@@ -149,6 +183,40 @@ int pk_q8_dequantize(void* stream, const int8_t* q, const uint16_t* scales, int 
     else
         q8_dequantize_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
             q, reinterpret_cast<const __half*>(scales), static_cast<bf16*>(out), n);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+int pk_q8_quantize_block(void* stream, const float* W, int8_t* q, float* scales, int64_t rows, int64_t cols,
+                         int64_t block) {
+    PK_REQUIRE(rows >= 0 && cols >= 0 && block > 0, "bad shape");
+    const int64_t bpr = (cols + block - 1) / block, n = rows * bpr;
+    if (n == 0) return PK_OK;
+    PK_REQUIRE(W && q && scales, "null pointer");
+    int64_t blocks = (n + 7) / 8;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    q8_quantize_block_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(W, q, scales, rows, cols, block, bpr);
+    PK_LAUNCH_CHECK();
+    return PK_OK;
+}
+
+int pk_q8_dequantize_block(void* stream, const int8_t* q, const float* scales, int64_t block, int out_dtype, void* out,
+                           int64_t rows, int64_t cols) {
+    PK_REQUIRE(valid_dtype(out_dtype), "bad dtype");
+    PK_REQUIRE(rows >= 0 && cols >= 0 && block > 0, "bad shape");
+    const int64_t n = rows * cols, bpr = (cols + block - 1) / block;
+    if (n == 0) return PK_OK;
+    PK_REQUIRE(q && scales && out, "null pointer");
+    int64_t blocks = (n + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+    if (blocks > cap) blocks = cap;
+    if (out_dtype == PK_F32)
+        q8_dequantize_block_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
+            q, scales, static_cast<float*>(out), rows, cols, block, bpr);
+    else
+        q8_dequantize_block_kernel<bf16><<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(
+            q, scales, static_cast<bf16*>(out), rows, cols, block, bpr);
     PK_LAUNCH_CHECK();
     return PK_OK;
 }

@@ -32,6 +32,12 @@ int sm_count() {
     return cached;
 }
 
+// ---- launch counters per kernel path ---------------------------------------------------
+static int64_t g_path_counts[PATH_SLOTS] = {0};
+void note_launch(int slot) {
+    if (slot >= 0 && slot < PATH_SLOTS) ++g_path_counts[slot];
+}
+
 // ---- event-based profiling --------------------------------------------------------
 namespace {
 struct ProfRec {
@@ -88,6 +94,14 @@ int pk_prof_summary(int kind, double* ms_h, double* work_h, int64_t* launches_h)
     *ms_h = ms;
     *work_h = work;
     *launches_h = n;
+    return PK_OK;
+}
+
+int pk_launch_counts(int64_t* counts_h, int n, int reset) {
+    PK_REQUIRE(counts_h != nullptr && n >= 0, "bad argument");
+    for (int i = 0; i < n; ++i) counts_h[i] = i < pk::PATH_SLOTS ? pk::g_path_counts[i] : 0;
+    if (reset)
+        for (int i = 0; i < pk::PATH_SLOTS; ++i) pk::g_path_counts[i] = 0;
     return PK_OK;
 }
 

@@ -1,15 +1,46 @@
 // Inline-PTX building blocks for the tensor-core (tcgen05) kernels: mbarriers with
 // bounded waits, TMA tile loads, tensor-memory allocation / loads, UMMA descriptors.
-// Used by the attention kernels; namespace pk::tc.
+// Used by the GEMM and attention kernels; namespace pk::tc.
 #pragma once
 #include <cuda.h>
+
+#include <cstddef>
 
 #include "pk_common.cuh"
 
 namespace pk {
 namespace tc {
 
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // ~2 s of SM clock: a longer wait is abandoned
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // default: ~2 s of SM clock, then a wait is abandoned
+// A wait that has already lasted this long also gives up when the family's status word is
+// non-zero (some CTA of the grid ran into its limit): the rest of the grid drains quickly. Far
+// longer than any wait of a healthy launch, so a status word that an earlier launch left
+// behind cannot cut a later launch short.
+constexpr long long DRAIN_AFTER_CYCLES = 40000000ll;
+
+// Control block of one kernel family's bounded waits (one __device__ instance per family).
+struct WaitCtl {
+    int status;              // PK_ERR_* codes ORed in by the kernels; read and cleared by the host
+    int reserved;
+    long long limit_cycles;  // SM clock cycles after which a wait is abandoned (pk_set_wait_limit_us)
+};
+
+// Defines the control block `g_<name>_ctl` of a kernel family and its two host accessors.
+#define PK_DEFINE_WAITCTL(name)                                                                              \
+    __device__ pk::tc::WaitCtl g_##name##_ctl = {0, 0, pk::tc::WAIT_LIMIT_CYCLES};                           \
+    int name##_status(int* status_h, int clear) {                                                            \
+        PK_CHECK_CUDA(cudaMemcpyFromSymbol(status_h, g_##name##_ctl, sizeof(int), offsetof(pk::tc::WaitCtl, status))); \
+        if (clear && *status_h != 0) {                                                                       \
+            const int zero = 0;                                                                              \
+            PK_CHECK_CUDA(cudaMemcpyToSymbol(g_##name##_ctl, &zero, sizeof(int), offsetof(pk::tc::WaitCtl, status))); \
+        }                                                                                                    \
+        return PK_OK;                                                                                        \
+    }                                                                                                        \
+    int name##_set_wait_limit(long long cycles) {                                                            \
+        PK_CHECK_CUDA(cudaMemcpyToSymbol(g_##name##_ctl, &cycles, sizeof(long long),                         \
+                                         offsetof(pk::tc::WaitCtl, limit_cycles)));                          \
+        return PK_OK;                                                                                        \
+    }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -74,21 +105,23 @@ __device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
-// Bounded wait: false when abandoned (time limit reached here or elsewhere in the CTA).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+// Bounded wait: false when abandoned (time limit reached here or elsewhere in the CTA, or
+// elsewhere in the grid once this wait has itself lasted DRAIN_AFTER_CYCLES).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, WaitCtl* ctl) {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
+    const long long limit = *reinterpret_cast<volatile long long*>(&ctl->limit_cycles);
     for (uint32_t it = 1;; ++it) {
         if (mbar_try(bar, parity)) return true;
         if ((it & 255u) == 0u) {
-            // once any CTA of any launch has given up, the others drain instead of each
-            // waiting out its own limit
-            if (*abort_flag || *reinterpret_cast<volatile int*>(status) != 0) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            if (*abort_flag) return false;
+            const long long waited = clock64() - t0;
+            if (waited > limit) {
                 *abort_flag = 1;
-                atomicOr(status, PK_ERR_TIMEOUT);
+                atomicOr(&ctl->status, PK_ERR_TIMEOUT);
                 return false;
             }
+            if (waited > DRAIN_AFTER_CYCLES && *reinterpret_cast<volatile int*>(&ctl->status) != 0) return false;
         }
     }
 }
@@ -263,9 +296,17 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-// bf16 row-major [outer, inner] matrix with row stride ld (elements); box = box_inner x box_outer.
+// bf16 row-major [outer, inner] matrix with row stride ld (elements); box = box_inner x box_outer,
+// 128-byte swizzle, out-of-range elements read as zero.
 int make_tensor_map(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner,
                     int box_outer);
+// The same matrix seen as [batch, rows, inner]: `rows` consecutive rows per batch entry, so that a
+// box which runs past the last row of a batch entry is zero-filled instead of reading the next one.
+int make_tensor_map_3d(CUtensorMap* map, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t ld,
+                       int box_inner, int box_rows);
+// Byte matrix [outer, inner] with row stride ld bytes, no swizzle (rows of the box are packed).
+int make_tensor_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner,
+                       int box_outer);
 
 }  // namespace tc
 }  // namespace pk

@@ -8,6 +8,8 @@
 #include <stdexcept>
 #include <string>
 
+#include "pk.h"
+
 #include "microtorch/flex.hpp"
 #include "microtorch/gguf.hpp"
 #include "microtorch/llama.hpp"
@@ -482,6 +484,13 @@ int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64
         }
         device::step_end();
         if (loss_h) *loss_h = loss_value;
+        // The loss readback has synchronised the stream: a kernel whose bounded wait gave up has
+        // left the step's results incomplete, which must not pass for a finished step.
+        int status = 0;
+        device::check(pk_kernel_status(&status, 1), "pk_kernel_status");
+        if (status != 0)
+            throw std::runtime_error("mt_model_step: a tensor-core kernel abandoned a bounded wait (status " +
+                                     std::to_string(status) + ", PK_ERR_TIMEOUT = 4); the results of this step are incomplete");
     });
 }
 
@@ -605,6 +614,28 @@ int mt_model_clip_grad_norm(void* h, float max_norm, float* norm) {
     return guard([&] {
         const float n = ops::clip_grad_norm(M(h)->params, max_norm);
         if (norm) *norm = n;
+    });
+}
+
+int mt_clip_grad_norm_arrays(int n, const int64_t* rows_h, const int64_t* cols_h, float* const* grads_h, float max_norm,
+                             float* norm_h) {
+    return guard([&] {
+        if (n < 0 || (n > 0 && (!rows_h || !cols_h || !grads_h))) throw std::runtime_error("bad argument");
+        std::vector<Var> vars;
+        for (int i = 0; i < n; ++i) {
+            const size_t r = static_cast<size_t>(rows_h[i]), c = static_cast<size_t>(cols_h[i]);
+            Var v = make_var(Matrix(r, c), true);
+            Matrix g(r, c);
+            std::memcpy(g.data(), grads_h[i], r * c * sizeof(float));
+            v->accumulate(g);
+            vars.push_back(v);
+        }
+        const float total = ops::clip_grad_norm(vars, max_norm);
+        for (int i = 0; i < n; ++i) {
+            const Matrix& g = vars[i]->grad.host();
+            std::memcpy(grads_h[i], g.data(), g.rows() * g.cols() * sizeof(float));
+        }
+        if (norm_h) *norm_h = total;
     });
 }
 

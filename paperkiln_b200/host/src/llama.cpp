@@ -29,10 +29,8 @@ Var Projection::forward(const Var& x) const { return forward_residual(x, nullptr
 
 Var Projection::forward_residual(const Var& x, const Var& residual) const {
     if (W) return ops::linear(x, W, nullptr, residual);
-    Var base = ops::q8_linear(x, Wq, nullptr, residual);
-    if (!A) return base;
-    Var xa = ops::scale(ops::matmul(x, A), scaling);
-    return ops::linear(xa, B, nullptr, base);
+    if (!A) return ops::q8_linear(x, Wq, nullptr, residual);
+    return ops::q8_lora_linear(x, Wq, A, B, scaling, nullptr, residual);
 }
 
 LlamaBlock::LlamaBlock(const LlamaConfig& cfg, unsigned seed)

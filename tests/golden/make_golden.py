@@ -44,6 +44,34 @@ STEP_CASES = {
                        seed=2, **{"data-seed": 13}, ckpt=1, rank=8, alpha=16),
 }
 
+# Reduced shapes of the bf16 configurations: the model width, head layout (head_dim 64), MLP width
+# and rotary base of GPT-2 small, the Qwen2.5-0.5B-shape QLoRA model and the Llama-1B shape, with
+# 2 layers, 2 short sequences and a 1024-word vocabulary so that the reference's CPU path finishes
+# in minutes. At these widths the GPU build runs its tcgen05 GEMM and attention kernels, which the
+# tiny cases above never reach. Stored as statistics and strided samples (the parameters are
+# regenerated from the seeds by the GPU build, bit for bit).
+REDUCED_CASES = {
+    "c2_reduced": dict(family="gpt2", vocab=1024, d=768, layers=2, heads=12, nctx=256, batch=2, seq=192, seed=21,
+                       **{"data-seed": 31}, ckpt=1),
+    "c3_reduced": dict(family="qlora", vocab=1024, d=896, layers=2, heads=14, **{"kv-heads": 2}, dff=4864, batch=2,
+                       seq=128, seed=22, **{"data-seed": 32}, ckpt=1, rank=16, alpha=32, theta=1000000),
+    "c4_reduced": dict(family="llamagqa", vocab=1024, d=2048, layers=2, heads=32, **{"kv-heads": 8}, dff=8192, batch=2,
+                       seq=128, seed=23, **{"data-seed": 33}, ckpt=1, theta=500000),
+}
+SAMPLE = 2048
+
+
+def strided_sample(v, n=SAMPLE):
+    return v.reshape(-1)[::max(1, v.size // n)][:n].copy()
+
+
+def tensor_stats(stats, prefix, v):
+    flat = v.reshape(-1).astype(np.float64)
+    stats[f"{prefix}.l2"] = np.float64(np.sqrt((flat * flat).sum()))
+    stats[f"{prefix}.sum"] = np.float64(flat.sum())
+    stats[f"{prefix}.sample"] = strided_sample(v)
+
+
 CONFIG1 = dict(family="llama", vocab=4096, d=128, layers=4, heads=4, dff=512, nctx=256, batch=8, seq=256, seed=0,
                **{"data-seed": 0})
 
@@ -102,7 +130,29 @@ def main():
     stats["meta_json"] = np.frombuffer(json.dumps({"args": CONFIG1}).encode(), dtype=np.uint8)
     np.savez_compressed(HERE / "config1_llama_stats.npz", **stats)
     print("config1", f"{(HERE / 'config1_llama_stats.npz').stat().st_size / 1024:.0f} KiB")
+    make_reduced()
+
+
+def make_reduced(only=None):
+    for name, args in REDUCED_CASES.items():
+        if only and name not in only:
+            continue
+        with tempfile.TemporaryDirectory() as tmp:
+            info = run_harness("step", args, tmp)
+            arrays = load_dir(Path(tmp))
+            stats = {"loss": np.float32(info["loss"]), "ids": arrays["ids"], "targets": arrays["targets"]}
+            for k, v in arrays.items():
+                if k.startswith(("grad.", "param.", "after.")):
+                    tensor_stats(stats, k, v)
+            stats["meta_json"] = np.frombuffer(json.dumps({"args": args, "result": info}).encode(), dtype=np.uint8)
+            np.savez_compressed(HERE / f"{name}.npz", **stats)
+            print(name, info, f"{(HERE / (name + '.npz')).stat().st_size / 1024:.0f} KiB")
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "reduced":   # only the reduced bf16-configuration cases
+        if not HARNESS.exists():
+            sys.exit(f"{HARNESS} not found: run `make -C oracle` first")
+        make_reduced(sys.argv[2:])
+    else:
+        main()

@@ -482,18 +482,16 @@ def test_attention(pk, dtype, cfg):
 
 @pytest.mark.parametrize("cfg", [(2, 200, 2, 2, 64, True), (1, 640, 4, 1, 64, True), (2, 333, 2, 2, 128, False),
                                  (1, 1100, 2, 2, 128, True)])
-def test_attention_tensor_core_variants(pk, cfg):
-    """The three tensor-core forward kernels (0: one 128-query tile per CTA; 1: two slots per CTA
-    with O kept in tensor memory and rescaled only when a row maximum grows by more than 2^8, two
-    threads per score row; 2: the same with one thread per row, the default) and the two backward
-    kernels agree with the fp32 restatement of ops::fused_attention
-    (src/ops.cpp:863-934). Queries are scaled up so that row maxima keep growing along the keys
-    and the in-place rescale of the running output is exercised."""
+def test_attention_tensor_core_growing_maxima(pk, cfg):
+    """The tcgen05 forward keeps the running output in tensor memory and rescales it only when a
+    row maximum grows by more than 2^8; queries are scaled up and keys grow along the sequence so
+    that row maxima keep growing and that rescale is exercised again and again. Forward and
+    backward agree with the fp32 restatement of ops::fused_attention (src/ops.cpp:863-934), and
+    the log-sum-exp agrees with the SIMT kernel's, which rescales on every tile."""
     B, S, Hq, Hkv, dk, causal = cfg
     R = B * S
     q = rnd(R, Hq * dk, seed=11, lo=-1, hi=1, dtype=torch.bfloat16) * 6
     k = rnd(R, Hkv * dk, seed=12, lo=-1, hi=1, dtype=torch.bfloat16)
-    # keys grow along the sequence: later tiles raise the running row maximum again and again
     ramp = torch.linspace(0.2, 3.0, S, device="cuda").repeat(B).unsqueeze(1)
     k = (k.float() * ramp).to(torch.bfloat16)
     v = rnd(R, Hkv * dk, seed=13, lo=-1, hi=1, dtype=torch.bfloat16)
@@ -502,16 +500,18 @@ def test_attention_tensor_core_variants(pk, cfg):
     qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
     ref = attn_ref(qf, kf, vf, B, S, Hq, Hkv, dk, scale, causal)
     ref.backward(do.float())
-    outs = {}
+    lses = {}
     try:
-        for variant in (0, 1, 2):
-            pkt.check(pk.pk_attn_fwd_variant(variant))
-            pkt.check(pk.pk_attn_bwd_variant(min(variant, 1)))
+        for simt in (0, 1):
+            pkt.check(pk.pk_attn_force_simt(simt))
             out = torch.empty_like(q)
             lse = torch.empty(R, Hq, device="cuda")
             pkt.check(pk.pk_attn_fwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
                                      Hq * dk, ptr(lse), B, S, Hq, Hkv, dk, scale, int(causal)))
-            assert pk.pk_attn_last_path() == 1
+            assert pk.pk_attn_last_path() == 1 - simt
+            lses[simt] = lse
+            if simt:
+                continue
             dq, dkk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
             sc = scratch(pk.pk_attn_bwd_scratch_bytes(B, S, Hq))
             pkt.check(pk.pk_attn_bwd(stream(), dt(q), ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out),
@@ -519,18 +519,14 @@ def test_attention_tensor_core_variants(pk, cfg):
                                      ptr(dv), Hkv * dk, ptr(sc), B, S, Hq, Hkv, dk, scale, int(causal)))
             st = ctypes.c_int(0)
             pkt.check(pk.pk_attn_tc_status(ctypes.byref(st), 1))
-            assert st.value == 0, f"variant {variant}: a bounded wait gave up"
+            assert st.value == 0, "a bounded wait gave up"
             close(out, ref, 2e-2, 2 ** -6)
             close(dq, qf.grad, 6e-2, 2 ** -5)
             close(dkk, kf.grad, 6e-2, 2 ** -5)
             close(dv, vf.grad, 6e-2, 2 ** -5)
-            outs[variant] = (out, lse, dq, dkk, dv)
     finally:
-        pkt.check(pk.pk_attn_fwd_variant(2))
-        pkt.check(pk.pk_attn_bwd_variant(1))
-    # the log-sum-exp does not depend on how often the running output was rescaled
-    close(outs[0][1], outs[1][1], 1e-3)
-    close(outs[0][1], outs[2][1], 1e-3)
+        pkt.check(pk.pk_attn_force_simt(0))
+    close(lses[0], lses[1], 1e-3)
 
 
 def test_attention_batch_isolation(pk):
@@ -662,3 +658,165 @@ def test_q8_roundtrip(pk):
     deqb = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
     pkt.check(pk.pk_q8_dequantize(stream(), ptr(q), ptr(sc), BF16, ptr(deqb), rows, cols))
     assert torch.equal(deqb, deq.to(torch.bfloat16))
+
+
+def test_q8_block_quantisation_any_block(pk):
+    """The reference's quantize_int8 / dequantize (src/quant.cpp:11-48) at its default block of 64
+    and at a block length that leaves a short last block: fp32 scales, bit-exact."""
+    rows, cols = 24, 100
+    W = rnd(rows, cols, seed=2, lo=-1, hi=1)
+    W[5, :64] = 0.0
+    for block in (64, 48, 7):
+        bpr = (cols + block - 1) // block
+        q = torch.empty(rows, cols, dtype=torch.int8, device="cuda")
+        sc = torch.empty(rows, bpr, device="cuda")
+        pkt.check(pk.pk_q8_quantize_block(stream(), ptr(W), ptr(q), ptr(sc), rows, cols, block))
+        pad = bpr * block - cols
+        Wp = torch.nn.functional.pad(W, (0, pad)).view(rows, bpr, block)
+        amax = Wp.abs().amax(dim=2)
+        s = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
+        assert torch.equal(sc, s)
+        qr = torch.clamp(Wp / s[:, :, None], -127, 127)
+        qr = torch.where(qr >= 0, torch.floor(qr + 0.5), torch.ceil(qr - 0.5)).to(torch.int8).view(rows, bpr * block)
+        assert torch.equal(q, qr[:, :cols].contiguous())
+        ref = (qr.float().view(rows, bpr, block) * s[:, :, None]).view(rows, bpr * block)[:, :cols].contiguous()
+        for odt, tdt in ((F32, torch.float32), (BF16, torch.bfloat16)):
+            deq = torch.empty(rows, cols, dtype=tdt, device="cuda")
+            pkt.check(pk.pk_q8_dequantize_block(stream(), ptr(q), ptr(sc), block, odt, ptr(deq), rows, cols))
+            assert torch.equal(deq, ref.to(tdt))
+        err = (ref - W).abs().view(rows, cols)
+        lim = torch.repeat_interleave(0.5 * s, block, dim=1)[:, :cols]
+        assert bool((err <= lim + 1e-7).all())
+
+
+def q8_weight(pk, rows, cols, seed):
+    W = rnd(rows, cols, seed=seed, lo=-0.06, hi=0.06)
+    q = torch.empty(rows, cols, dtype=torch.int8, device="cuda")
+    sc = torch.empty(rows, cols // 32, dtype=torch.float16, device="cuda")
+    pkt.check(pk.pk_q8_quantize(stream(), ptr(W), ptr(q), ptr(sc), rows, cols))
+    deq = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+    pkt.check(pk.pk_q8_dequantize(stream(), ptr(q), ptr(sc), BF16, ptr(deq), rows, cols))
+    return q, sc, deq
+
+
+def q8_call(pk, trans_w, A, q, sc, M, N, K, XA=None, L=None, C=None, out_dtype=torch.bfloat16, accumulate=False,
+            bias=None, residual=None):
+    if C is None:
+        C = torch.empty(M, N, dtype=out_dtype, device="cuda")
+    r = 0 if XA is None else XA.shape[1]
+    pkt.check(pk.pk_gemm_q8_lora(stream(), dt(C), int(trans_w), M, N, K, ptr(A), A.stride(0), ptr(q), ptr(sc),
+                                 ptr(XA), XA.stride(0) if XA is not None else 0, ptr(L),
+                                 L.stride(0) if L is not None else 0, r, ptr(C), C.stride(0), int(accumulate),
+                                 ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0),
+              "pk_gemm_q8_lora")
+    assert pk.pk_gemm_last_path() == 4
+    return C
+
+
+# (M, N, K); sized so that the dense comparison GEMM never takes split-K, whose summation order differs
+@pytest.mark.parametrize("shape", [(300, 896, 896), (1024, 128, 896), (1500, 4864, 896), (1501, 896, 4864), (64, 32, 64),
+                                   (4096, 896, 896)])
+@pytest.mark.parametrize("rank", [0, 16, 8, 64])
+def test_gemm_q8_lora_equals_dequantise_then_gemm(pk, shape, rank):
+    """The fused kernel forms the products of a bf16 GEMM over the expanded weight in the same k
+    order: y = x deq(W) + XA B equals pk_gemm([x | XA], [deq(W); B]) BIT FOR BIT, and so does the
+    input-gradient form dx = dy deq(W)^T + DXA A^T. (src/quant.cpp:91-119 is the layer this
+    replaces; the reference multiplies by a dequantised copy.) Also against fp32 torch."""
+    M, N, K = shape
+    # forward: W is [K, N]
+    q, sc, deq = q8_weight(pk, K, N, seed=3)
+    x = rnd(M, K, seed=4, dtype=torch.bfloat16)
+    xa = rnd(M, rank, seed=5, lo=-0.5, hi=0.5, dtype=torch.bfloat16) if rank else None
+    Bl = rnd(rank, N, seed=6, lo=-0.05, hi=0.05, dtype=torch.bfloat16) if rank else None
+    res = rnd(M, N, seed=7, dtype=torch.bfloat16)
+    y = q8_call(pk, 0, x, q, sc, M, N, K, xa, Bl, residual=res)
+    if rank:
+        unfused = pkt.gemm(torch.cat([x, xa], dim=1).contiguous(), torch.cat([deq, Bl], dim=0).contiguous(), residual=res)
+    else:
+        unfused = pkt.gemm(x, deq, residual=res)
+    assert pk.pk_gemm_last_path() in (2, 3)
+    assert torch.equal(y, unfused), f"forward differs: max {(y.float() - unfused.float()).abs().max().item():.3e}"
+    ref = x.float() @ deq.float() + res.float()
+    if rank:
+        ref = ref + xa.float() @ Bl.float()
+    close(y, ref, 2e-2, 2 ** -6)
+    # input gradient: dy [M, N] . deq(W)^T -> [M, K]; the LoRA operand is A [K, r]
+    dy = rnd(M, N, seed=8, dtype=torch.bfloat16)
+    dxa = rnd(M, rank, seed=9, lo=-0.5, hi=0.5, dtype=torch.bfloat16) if rank else None
+    Al = rnd(K, rank, seed=10, lo=-0.05, hi=0.05, dtype=torch.bfloat16) if rank else None
+    dx = q8_call(pk, 1, dy, q, sc, M, K, N, dxa, Al)
+    if rank:
+        unfused = pkt.gemm(torch.cat([dy, dxa], dim=1).contiguous(), torch.cat([deq, Al], dim=1).contiguous(), tb=True)
+    else:
+        unfused = pkt.gemm(dy, deq, tb=True)
+    assert torch.equal(dx, unfused), f"input gradient differs: max {(dx.float() - unfused.float()).abs().max().item():.3e}"
+    # accumulate into an existing gradient, fp32 output, and a bias
+    bias = rnd(K, seed=11)
+    acc0 = rnd(M, K, seed=12)
+    acc = acc0.clone()
+    q8_call(pk, 1, dy, q, sc, M, K, N, dxa, Al, C=acc, accumulate=True, bias=bias)
+    ref = acc0 + dy.float() @ deq.float().T + bias[None, :]
+    if rank:
+        ref = ref + dxa.float() @ Al.float().T
+    close(acc, ref, 2e-2, 1e-3)
+    st = ctypes.c_int(0)
+    pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
+    assert st.value == 0, "a bounded wait gave up"
+    # repeatable bit for bit
+    assert torch.equal(y, q8_call(pk, 0, x, q, sc, M, N, K, xa, Bl, residual=res))
+
+
+def test_gemm_q8_rejects_what_it_does_not_take(pk):
+    q, sc, _ = q8_weight(pk, 64, 64, seed=1)
+    x = rnd(16, 64, seed=2, dtype=torch.bfloat16)
+    y = torch.empty(16, 64, dtype=torch.bfloat16, device="cuda")
+    xa = rnd(16, 12, seed=3, dtype=torch.bfloat16)   # rank not a multiple of 8
+    L = rnd(12, 64, seed=4, dtype=torch.bfloat16)
+    rc = pk.pk_gemm_q8_lora(stream(), BF16, 0, 16, 64, 64, ptr(x), 64, ptr(q), ptr(sc), ptr(xa), 12, ptr(L), 64, 12,
+                            ptr(y), 64, 0, None, None, 0)
+    assert rc == 3  # PK_ERR_UNSUPPORTED
+    rc = pk.pk_gemm_q8_lora(stream(), BF16, 0, 16, 64, 64, ptr(x), 32, ptr(q), ptr(sc), None, 0, None, 0, 0, ptr(y), 64,
+                            0, None, None, 0)
+    assert rc == 1  # PK_ERR_INVALID: lda < K
+
+
+def test_bounded_wait_runs_out_and_the_library_carries_on(pk):
+    """A wait on an mbarrier nobody arrives at gives up at the limit, records PK_ERR_TIMEOUT and
+    the kernel returns; nothing traps, the context stays usable and the kernels' own status words
+    stay clean. The limit is settable (default 2 s)."""
+    import time
+    try:
+        pkt.check(pk.pk_set_wait_limit_us(2000.0))
+        st = ctypes.c_int(0)
+        waited = ctypes.c_double(0.0)
+        t0 = time.perf_counter()
+        pkt.check(pk.pk_wait_selftest(stream(), ctypes.byref(st), ctypes.byref(waited)))
+        wall = time.perf_counter() - t0
+        assert st.value == 4, f"status {st.value}, expected PK_ERR_TIMEOUT"
+        assert 2000.0 <= waited.value < 200000.0, waited.value
+        assert wall < 1.0
+        # the word was cleared by the read
+        pkt.check(pk.pk_set_wait_limit_us(500.0))
+        pkt.check(pk.pk_wait_selftest(stream(), ctypes.byref(st), ctypes.byref(waited)))
+        assert st.value == 4 and 500.0 <= waited.value < 100000.0
+    finally:
+        pkt.check(pk.pk_set_wait_limit_us(2e6))
+    # normal work afterwards: tensor-core GEMM and attention, correct and with clean status
+    a = rnd(512, 256, seed=1, dtype=torch.bfloat16)
+    b = rnd(256, 512, seed=2, dtype=torch.bfloat16)
+    c = pkt.gemm(a, b)
+    assert pk.pk_gemm_last_path() in (2, 3)
+    close(c, a.float() @ b.float(), 0.5, 2 ** -6)
+    B, S, H, dk = 1, 256, 2, 64
+    qq = rnd(S, H * dk, seed=3, lo=-1, hi=1, dtype=torch.bfloat16)
+    out = torch.empty_like(qq)
+    lse = torch.empty(S, H, device="cuda")
+    pkt.check(pk.pk_attn_fwd(stream(), BF16, ptr(qq), H * dk, ptr(qq), H * dk, ptr(qq), H * dk, ptr(out), H * dk, ptr(lse),
+                             B, S, H, H, dk, 0.125, 1))
+    assert pk.pk_attn_last_path() == 1
+    ref = attn_ref(qq.float(), qq.float(), qq.float(), B, S, H, H, dk, 0.125, True)
+    close(out, ref, 2e-2, 2 ** -6)
+    all_st = ctypes.c_int(-1)
+    pkt.check(pk.pk_device_sync())
+    pkt.check(pk.pk_kernel_status(ctypes.byref(all_st), 1))
+    assert all_st.value == 0
