@@ -155,6 +155,29 @@ int mt_model_bucket(void* model, int64_t index, void** ptr_h, int64_t* count_h);
 typedef void (*mt_segment_cb)(int, void*);
 int mt_set_segment_hook(mt_segment_cb cb, void* user);
 
+/* Data parallelism inside the library (no Python, no torch.distributed on the data path): the
+ * gradient exchange of microtorch/dp.hpp over the collective group of libpk (NCCL). Rank 0 draws
+ * the 128-byte id with mt_dp_unique_id and the launcher hands it to every rank; mt_dp_init builds
+ * the communicator on the model's GPU (max_ctas > 0 caps NCCL's CTAs, 0 = its default) and
+ * installs the exchange as the segment hook (it replaces a hook set with mt_set_segment_hook):
+ * from then on every mt_model_step starts the all-reduce of a block's gradients as that block's
+ * backward is enqueued. The caller scales the loss by 1 / world (loss_scale of mt_model_step),
+ * calls mt_dp_finish after the (last) backward and before mt_model_optimizer_step -- it sends
+ * the remaining ranges and orders the compute stream behind all transfers, without blocking
+ * the host -- and, under gradient accumulation, mt_dp_enable(model, 0) for all but the last
+ * micro-batch. A model with less than 32 MiB of gradients (LoRA adapters) is sent as one flat
+ * buffer in one collective. mt_dp_wait_host blocks until the transfers are done and fails after
+ * the time limit (mt_dp_set_timeout, default 30 s), aborting the communicator: a rank that
+ * died is noticed there, not by hanging. Needs pack=1. */
+int mt_dp_unique_id(void* id_h, size_t cap);
+int mt_dp_init(void* model, const void* id_h, int rank, int world, int max_ctas);
+int mt_dp_enable(void* model, int on);
+int mt_dp_finish(void* model);
+int mt_dp_wait_host(void* model);
+int mt_dp_set_timeout(void* model, double seconds);
+int mt_dp_stats(void* model, int64_t* launches_last_step_h, int* single_collective_h);
+int mt_dp_destroy(void* model);
+
 /* out_h[0..5] = activation bytes in use, activation peak, persistent in use, persistent
  * peak, bytes reserved from the driver, number of driver allocations. */
 int mt_mem_stats(uint64_t* out_h);

@@ -40,7 +40,8 @@ enum pk_status {
     PK_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed; see pk_last_error */
     PK_ERR_UNSUPPORTED = 3, /* valid request this build has no kernel for */
     PK_ERR_TIMEOUT = 4,     /* a bounded device-side wait gave up */
-    PK_ERR_INDEX = 5        /* an id / target was out of range (device status word) */
+    PK_ERR_INDEX = 5,       /* an id / target was out of range (device status word) */
+    PK_ERR_COMM = 6         /* a collective failed or its communicator was aborted */
 };
 
 /* ---- library / runtime ----------------------------------------------------
@@ -200,6 +201,11 @@ int pk_gelu_fwd(void* stream, int dtype, const void* x, void* y, int64_t n);
 int pk_gelu_bwd(void* stream, int dtype, const void* dy, const void* x, void* dx, int64_t n);
 int pk_relu_fwd(void* stream, int dtype, const void* x, void* y, int64_t n);
 int pk_relu_bwd(void* stream, int dtype, const void* dy, const void* x, void* dx, int64_t n);
+/* Row softmax y[i,:] = softmax(x[i,:]) (maximum subtracted) and its backward
+ * dx = s .* (dy - rowsum(dy .* s)) with s the forward's output: ops::softmax_row
+ * (src/ops.cpp:140-167), devops::softmax_fwd / softmax_bwd. */
+int pk_softmax_fwd(void* stream, int dtype, const void* x, void* y, int64_t R, int64_t C);
+int pk_softmax_bwd(void* stream, int dtype, const void* s, const void* dy, void* dx, int64_t R, int64_t C);
 /* y = a (op) b, op: 0 add, 1 sub, 2 mul. ops::add/sub/mul (src/ops.cpp:60-83),
  * devops::add/sub/mul (device_cache.hpp:99-101). */
 int pk_binary(void* stream, int dtype, int op, const void* a, const void* b, void* y, int64_t n);
@@ -334,13 +340,49 @@ int pk_q8_dequantize_block(void* stream, const int8_t* q, const float* scales, i
  * bf16, the bits pk_q8_dequantize writes -- straight into the swizzled operand buffer that
  * tcgen05.mma reads; the weight never exists in bf16 in global memory. The result equals
  * pk_gemm over [A | XA] and [deq(W); L] bit for bit (same products, same k order).
- * Needs: W's column count a multiple of 32, 16-byte aligned bases, lda / ldxa / ldl / ldc / ldr
- * multiples of 8, r a multiple of 8 and <= 64. Other requests return PK_ERR_UNSUPPORTED; the
+ * Needs: W's column count a multiple of 128 (trans_w = 0) or of 64 (trans_w = 1), N a multiple
+ * of 8, 16-byte aligned bases, lda / ldxa / ldl / ldc / ldr multiples of 8, r a multiple of 8
+ * and <= 64. Other requests return PK_ERR_UNSUPPORTED; the
  * caller can always dequantise and call pk_gemm. pk_gemm_last_path reports 4. */
 int pk_gemm_q8_lora(void* stream, int c_dtype, int trans_w, int64_t M, int64_t N, int64_t K,
                     const void* A, int64_t lda, const int8_t* Wq, const uint16_t* scales,
                     const void* XA, int64_t ldxa, const void* L, int64_t ldl, int r,
                     void* C, int64_t ldc, int accumulate, const float* bias, const void* residual, int64_t ldr);
+
+/* ---- collectives -------------------------------------------------------------
+ * Sum all-reduce of fp32 gradient ranges between the ranks of a data-parallel job (one process
+ * per GPU), asynchronous behind the compute stream so that the exchange of one block's gradients
+ * overlaps the recompute + backward of the next. The reference has no multi-GPU path; the
+ * identity used -- every rank pre-scales its loss and the gradients are summed -- is the one of
+ * its gradient accumulation loop (tools/mtstudio.cpp:456-474).
+ *   pk_comm_unique_id   rank 0 draws the 128-byte NCCL id; the host distributes it (any channel)
+ *   pk_comm_init        every rank, with its GPU current: builds the NCCL communicator and a
+ *                       private communication stream. max_ctas > 0 caps the CTAs NCCL's kernels
+ *                       use (SMs they take from the kernels they overlap); 0 = NCCL's default.
+ *                       NCCL is opened at run time (libnccl.so.2); absent -> PK_ERR_COMM.
+ *   pk_comm_init_file   CPU ranks exchanging HOST buffers through an existing directory: for
+ *                       exercising the host-side protocol without GPUs. The files stay there.
+ *   pk_allreduce_async  buf[0..count) = sum over ranks, in place. NCCL backend: starts once the
+ *                       work enqueued so far on compute_stream has finished; returns at once.
+ *   pk_comm_wait        orders compute_stream behind every collective started so far (no host
+ *                       block) and reports an asynchronous communicator error if there is one.
+ *                       File backend: completes the collectives on the host.
+ *   pk_comm_wait_host   blocks the host until they have finished, polling the communicator's
+ *                       error state; after the time limit (pk_comm_set_timeout, default 30 s) it
+ *                       aborts the communicator and returns PK_ERR_TIMEOUT.
+ *   pk_comm_abort       ncclCommAbort: ends the communicator's kernels; every later call on the
+ *                       handle returns PK_ERR_COMM. pk_comm_destroy frees the handle.
+ * All ranks must start the same collectives in the same order. One host thread per handle. */
+int pk_comm_unique_id(void* id_h, size_t cap);
+int pk_comm_init(const void* id_h, int rank, int world, int max_ctas, void** comm_h);
+int pk_comm_init_file(const char* dir, int rank, int world, void** comm_h);
+int pk_comm_set_timeout(void* comm, double seconds);
+int pk_comm_info(void* comm, int* rank_h, int* world_h, int* backend_h, int* alive_h);
+int pk_allreduce_async(void* comm, float* buf, int64_t count, void* compute_stream);
+int pk_comm_wait(void* comm, void* compute_stream);
+int pk_comm_wait_host(void* comm);
+int pk_comm_abort(void* comm);
+int pk_comm_destroy(void* comm);
 
 #ifdef __cplusplus
 }

@@ -12,13 +12,17 @@
 //
 // Tile schedule, pairing and epilogue are those of pk_gemm_tc2.cu: a cluster of two CTAs owns a
 // 256 x 256 output tile, CTA r holds rows r*128.. of A and of the accumulator and columns r*128..
-// of B; the leader issues tcgen05.mma.cta_group::2. Roles in each CTA (320 threads):
-//   warp 0      TMA producer: A slice (completes on the leader's "full" barrier) and the raw
-//               int8 half slice of W (completes on this CTA's "raw" barrier)
-//   warp 1      tensor-memory allocation; in the leader one thread issues the MMAs once "full"
-//               and "converted" (eight converter warps of the pair) have both completed
-//   warps 2..5  epilogue (tcgen05.ld, bias / residual / accumulate, stores)
-//   warps 6..9  converters: int8 + scale -> swizzled bf16, fence.proxy.async, arrive
+// of B; the leader issues tcgen05.mma.cta_group::2. Roles in each CTA (448 threads):
+//   warp 0       producer: lane 0 issues the TMA loads -- the A slice (completes on the leader's
+//                "full" barrier) and the raw int8 half slice of W (this CTA's "raw" barrier); all 32
+//                lanes copy the slice's fp16 scales into shared memory with cp.async, whose
+//                completion is counted on the same "raw" barrier
+//   warp 1       tensor-memory allocation; in the leader one thread issues the MMAs
+//   warps 2..5   epilogue (tcgen05.ld, bias / residual / accumulate, stores)
+//   warps 6..13  converters: int8 + scale -> swizzled bf16, fence.proxy.async, then one arrival per
+//                warp on the LEADER's "full" barrier, which therefore completes when the A bytes of
+//                both CTAs have landed and all 16 converter warps of the pair are done: the issuer
+//                waits once per k slice
 // Both layouts of W are served: trans_w = 0 (W is [K, N], the operand is MN-major; forward) and
 // trans_w = 1 (W is [N, K], K-major; input gradient). The k order is fixed and the products are
 // the ones a bf16 GEMM over the expanded weight would form, so the result equals
@@ -42,15 +46,17 @@ using namespace tc;
 constexpr int Q8_BM = 128;          // rows per CTA; the pair covers 256
 constexpr int Q8_BN = 256;
 constexpr int Q8_BK = 64;
-constexpr int Q8_THREADS = 320;
+constexpr int Q8_THREADS = 448;
 constexpr int Q8_CONV_WARP0 = 6;    // first converter warp
-constexpr int Q8_CONV_WARPS = 4;
+constexpr int Q8_CONV_WARPS = 8;
+constexpr int Q8_CONV_ITERS = 1024 / (Q8_CONV_WARPS * 32);   // 16-byte operand units per thread and k slice (4)
 constexpr int Q8_STAGES = 5;
 constexpr int Q8_A_BYTES = Q8_BM * Q8_BK * 2;          // 16 KiB
 constexpr int Q8_B_BYTES = (Q8_BN / 2) * Q8_BK * 2;    // 16 KiB: this CTA's half of B in bf16
 constexpr int Q8_RAW_BYTES = (Q8_BN / 2) * Q8_BK;      // 8 KiB: the same half as int8
 constexpr int Q8_STAGE_BYTES = Q8_A_BYTES + Q8_B_BYTES + Q8_RAW_BYTES;
-constexpr int Q8_SMEM_BYTES = Q8_STAGES * Q8_STAGE_BYTES + 1024 + 512;
+constexpr int Q8_SCALE_BYTES = 512;                    // fp16 scales of one half slice: 64 x 4 or 128 x 2
+constexpr int Q8_SMEM_BYTES = Q8_STAGES * (Q8_STAGE_BYTES + Q8_SCALE_BYTES) + 1024 + 512;
 
 struct Q8Params {
     int64_t M, N, K;
@@ -80,6 +86,13 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t ra
 }
 __device__ __forceinline__ void remote_arrive(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The converters' arrival on the leader's barrier. Their shared-memory writes are read by the
+// tensor core (async proxy) of their own SM and have been ordered for it by fence.proxy.async;
+// the arrival itself needs no cluster-wide release of generic writes, which costs about a
+// thousand cycles per arrival and would sit on the critical path of every k slice.
+__device__ __forceinline__ void remote_arrive_cta_release(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t leader_bar) {
     asm volatile(
@@ -116,36 +129,15 @@ __host__ __device__ inline uint32_t idesc_pair(int n, int b_mn_major) {
 __device__ __forceinline__ bool waitq(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     return mbar_wait(bar, parity, abort_flag, &g_gemm_q8_ctl);
 }
-// The issuer's wait for the converters of BOTH CTAs: their shared-memory writes must be visible
-// across the cluster, hence the cluster-scope acquire.
-__device__ __forceinline__ uint32_t mbar_try_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
+// 4- or 8-byte asynchronous copy global -> shared; src_bytes == 0 writes zeros instead.
+template <int BYTES>
+__device__ __forceinline__ void cp_async_small(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(dst), "l"(src), "n"(BYTES), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ bool waitq_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_cluster(bar, parity)) return true;
-    const long long t0 = clock64();
-    const long long limit = *reinterpret_cast<volatile long long*>(&g_gemm_q8_ctl.limit_cycles);
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try_cluster(bar, parity)) return true;
-        if ((it & 255u) == 0u) {
-            if (*abort_flag) return false;
-            const long long waited = clock64() - t0;
-            if (waited > limit) {
-                *abort_flag = 1;
-                atomicOr(&g_gemm_q8_ctl.status, PK_ERR_TIMEOUT);
-                return false;
-            }
-            if (waited > DRAIN_AFTER_CYCLES && *reinterpret_cast<volatile int*>(&g_gemm_q8_ctl.status) != 0) return false;
-        }
-    }
+// One arrival on the barrier once all earlier cp.async of this thread have landed (the arrival is
+// part of the barrier's expected count).
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 template <typename TC>
@@ -202,14 +194,15 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                const __grid_constant__ CUtensorMap map_xa, const __grid_constant__ CUtensorMap map_l, const Q8Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Q8_STAGES * Q8_STAGE_BYTES);
-    uint64_t* full_bar = bars;                        // [STAGES]  leader: TMA bytes of A (and of the LoRA slice) of both CTAs
+    uint8_t* scale_smem = smem + Q8_STAGES * Q8_STAGE_BYTES;   // [STAGES][Q8_SCALE_BYTES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(scale_smem + Q8_STAGES * Q8_SCALE_BYTES);
+    uint64_t* full_bar = bars;                        // [STAGES]  leader: TMA bytes of A (and of the LoRA slice) of both
+                                                      //           CTAs + the 16 converter warps of the pair
     uint64_t* empty_bar = bars + Q8_STAGES;           // [STAGES]  per CTA, both signalled by the leader's commits
-    uint64_t* raw_full = bars + 2 * Q8_STAGES;        // [STAGES]  per CTA: its int8 half slice has landed
-    uint64_t* conv_done = bars + 3 * Q8_STAGES;       // [STAGES]  leader: 8 converter warps of the pair
-    uint64_t* acc_full = bars + 4 * Q8_STAGES;        // [2]       per CTA, both signalled by the leader
-    uint64_t* acc_empty = bars + 4 * Q8_STAGES + 2;   // [2]       leader: 8 epilogue warps of the pair
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4 * Q8_STAGES + 4);
+    uint64_t* raw_full = bars + 2 * Q8_STAGES;        // [STAGES]  per CTA: its int8 half slice and its scales have landed
+    uint64_t* acc_full = bars + 3 * Q8_STAGES;        // [2]       per CTA, both signalled by the leader
+    uint64_t* acc_empty = bars + 3 * Q8_STAGES + 2;   // [2]       leader: 8 epilogue warps of the pair
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * Q8_STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -223,10 +216,9 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Q8_STAGES; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&full_bar[s]), 1 + 2 * Q8_CONV_WARPS);   // producer's expect_tx + converter warps
             mbar_init(smem_u32(&empty_bar[s]), 1);
-            mbar_init(smem_u32(&raw_full[s]), 1);
-            mbar_init(smem_u32(&conv_done[s]), 2 * Q8_CONV_WARPS);
+            mbar_init(smem_u32(&raw_full[s]), 1 + 32);                   // lane 0's expect_tx + one per producer lane
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&acc_full[a]), 1);
@@ -246,20 +238,23 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer (both CTAs)
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int64_t w = pair; w < n_tiles && ok; w += n_pairs) {
-                const int32_t m0 = static_cast<int32_t>((w / tiles_n) * (2 * Q8_BM) + rank * Q8_BM);
-                const int32_t n0 = static_cast<int32_t>((w % tiles_n) * Q8_BN + rank * (Q8_BN / 2));
-                const int nb = k_blocks + (lora ? 1 : 0);
-                for (int kb = 0; kb < nb; ++kb) {
-                    if (!waitq(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
+        // ------------------------------------------------ producer (both CTAs): TMA by lane 0, scales by all lanes
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.scales);
+        for (int64_t w = pair; w < n_tiles && ok; w += n_pairs) {
+            const int32_t m0 = static_cast<int32_t>((w / tiles_n) * (2 * Q8_BM) + rank * Q8_BM);
+            const int32_t n0 = static_cast<int32_t>((w % tiles_n) * Q8_BN + rank * (Q8_BN / 2));
+            const int nb = k_blocks + (lora ? 1 : 0);
+            for (int kb = 0; kb < nb; ++kb) {
+                if (lane == 0) ok = waitq(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                const uint32_t rb = smem_u32(&raw_full[stage]);
+                if (lane == 0) {
                     const uint32_t fb_local = smem_u32(&full_bar[stage]);
                     const uint32_t fb = map_to_rank(fb_local, 0);   // the leader's barrier counts both CTAs' bytes
-                    const uint32_t rb = smem_u32(&raw_full[stage]);
                     const uint32_t sa = smem_u32(smem + stage * Q8_STAGE_BYTES);
                     const uint32_t sb = sa + Q8_A_BYTES;
                     const uint32_t sr = sb + Q8_B_BYTES;
@@ -281,10 +276,35 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         } else {
                             tma_load_2d_pair(sb, &map_l, 0, n0, fb);              // box 64(r) x 128(n)
                         }
-                        mbar_arrive(rb);   // nothing to convert: keeps the converters' phase in step
+                        mbar_arrive(rb);   // stands for the expect_tx arrival: nothing to convert in this slice
                     }
-                    if (++stage == Q8_STAGES) { stage = 0; phase ^= 1u; }
                 }
+                if (kb < k_blocks) {
+                    // fp16 scales of this half slice, laid out [row of the slice][scale column]
+                    const uint32_t ss = smem_u32(scale_smem + stage * Q8_SCALE_BYTES);
+                    const int64_t k0 = static_cast<int64_t>(kb) * Q8_BK;
+                    if (B_MN) {   // 64 k rows x 4 scales (8 bytes) each
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            const int row = lane + 32 * i;
+                            const bool in = k0 + row < p.K && n0 < p.N;
+                            const unsigned short* src = in ? sp + (k0 + row) * p.scale_ld + (n0 >> 5) : sp;
+                            cp_async_small<8>(ss + row * 8, src, in ? 8u : 0u);
+                        }
+                    } else {      // 128 n rows x 2 scales (4 bytes) each
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int row = lane + 32 * i;
+                            const bool in = n0 + row < p.N && k0 < p.K;
+                            const unsigned short* src = in ? sp + static_cast<int64_t>(n0 + row) * p.scale_ld + (k0 >> 5) : sp;
+                            cp_async_small<4>(ss + row * 4, src, in ? 4u : 0u);
+                        }
+                    }
+                    cp_async_arrive(rb);
+                } else {
+                    mbar_arrive(rb);
+                }
+                if (++stage == Q8_STAGES) { stage = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -307,7 +327,6 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int nb = k_blocks + (lora ? 1 : 0);
                 for (int kb = 0; kb < nb; ++kb) {
                     if (!waitq(smem_u32(&full_bar[stage]), phase, abort_flag)) { ok = false; break; }
-                    if (!waitq_cluster(smem_u32(&conv_done[stage]), phase, abort_flag)) { ok = false; break; }
                     fence_after();
                     const uint32_t a_lo = a_lo0 + stage * (Q8_STAGE_BYTES >> 4), b_lo = b_lo0 + stage * (Q8_STAGE_BYTES >> 4);
                     if (kb < k_blocks) {
@@ -329,73 +348,44 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp >= Q8_CONV_WARP0) {
         // ------------------------------------------------ converters (both CTAs)
-        const int c = threadIdx.x - Q8_CONV_WARP0 * 32;   // 0..127
-        // MN-major (W is [K, N]): thread = (k row kr + 8 i, 8 columns starting at 8 j)
-        // K-major  (W is [N, K]): thread = (row nr + 16 i, 8 k values starting at 8 u)
+        const int c = threadIdx.x - Q8_CONV_WARP0 * 32;   // 0..255
+        // MN-major (W is [K, N]): thread = (k row r0 + 16 i, 8 columns starting at 8 j), j < 16
+        // K-major  (W is [N, K]): thread = (row r0 + 32 i, 8 k values starting at 8 j), j < 8
         const int j = B_MN ? (c & 15) : (c & 7);
         const int r0 = B_MN ? (c >> 4) : (c >> 3);
-        const int raw_pitch = B_MN ? 128 : 64;
+        constexpr int raw_pitch = B_MN ? 128 : 64;
+        constexpr int row_step = B_MN ? 16 : 32;
+        constexpr int scale_pitch = B_MN ? 8 : 4;   // bytes of scales per row of the slice
         const int raw_off = r0 * raw_pitch + 8 * j;
-        const int row_step = B_MN ? 8 : 16;
         // destination of iteration 0; iteration i adds row_step rows (the swizzle term (row & 7) does not change)
         const int dst_off = B_MN ? ((j >> 3) * 8192 + r0 * 128 + (((j & 7) ^ (r0 & 7)) << 4))
                                  : (r0 * 128 + ((j ^ (r0 & 7)) << 4));
-        const uint32_t leader_conv0 = map_to_rank(smem_u32(&conv_done[0]), 0);
+        const int scale_off = r0 * scale_pitch + (j >> 2) * 2;
+        const uint32_t leader_full0 = map_to_rank(smem_u32(&full_bar[0]), 0);
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        // scales of the slice being converted and of the one after it (loaded one slice ahead)
-        uint16_t sc[8], sc_next[8];
-        auto load_scales = [&](int64_t w, int kb, uint16_t (&dst)[8]) {
-            const int64_t n0 = (w % tiles_n) * Q8_BN + rank * (Q8_BN / 2);
-            const int64_t k0 = static_cast<int64_t>(kb) * Q8_BK;
-            const unsigned short* sp = reinterpret_cast<const unsigned short*>(p.scales);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                int64_t wrow, wcol;   // element of W this thread converts first in iteration i
-                if (B_MN) { wrow = k0 + r0 + 8 * i; wcol = n0 + 8 * j; }
-                else { wrow = n0 + r0 + 16 * i; wcol = k0 + 8 * j; }
-                const bool in = B_MN ? (wrow < p.K && wcol < p.N) : (wrow < p.N && wcol < p.K);
-                dst[i] = in ? __ldg(sp + wrow * p.scale_ld + (wcol >> 5)) : static_cast<unsigned short>(0);
-            }
-        };
-        int64_t w = pair;
-        int kb = 0;
-        bool have = w < n_tiles && k_blocks > 0;
-        if (have) load_scales(w, kb, sc_next);
-        while (have && ok) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sc[i] = sc_next[i];
-            int64_t nw = w;
-            int nkb = kb + 1;
-            if (nkb == k_blocks) { nkb = 0; nw = w + n_pairs; }
-            const bool have_next = nw < n_tiles;
-            if (have_next) load_scales(nw, nkb, sc_next);
-            if (!waitq(smem_u32(&raw_full[stage]), phase, abort_flag)) { ok = false; break; }
-            {
-                const uint8_t* raw = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + Q8_B_BYTES + raw_off;
-                uint8_t* dst = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + dst_off;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint2 q = *reinterpret_cast<const uint2*>(raw + i * row_step * raw_pitch);
-                    const float s = __half2float(__ushort_as_half(sc[i]));
-                    *reinterpret_cast<uint4*>(dst + i * row_step * 128) = dequant8(q.x, q.y, s);
-                }
-            }
-            fence_async_smem();   // generic-proxy writes -> visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) remote_arrive(leader_conv0 + stage * 8);
-            if (++stage == Q8_STAGES) { stage = 0; phase ^= 1u; }
-            if (lora && kb == k_blocks - 1) {
-                // the LoRA slice of this tile: nothing to convert, only keep the barriers in step
+        for (int64_t w = pair; w < n_tiles && ok; w += n_pairs) {
+            const int nb = k_blocks + (lora ? 1 : 0);
+            for (int kb = 0; kb < nb; ++kb) {
                 if (!waitq(smem_u32(&raw_full[stage]), phase, abort_flag)) { ok = false; break; }
+                if (kb < k_blocks) {
+                    const uint8_t* raw = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + Q8_B_BYTES + raw_off;
+                    uint8_t* dst = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + dst_off;
+                    const uint8_t* scl = scale_smem + stage * Q8_SCALE_BYTES + scale_off;
+#pragma unroll
+                    for (int i = 0; i < Q8_CONV_ITERS; ++i) {
+                        const uint2 q = *reinterpret_cast<const uint2*>(raw + i * row_step * raw_pitch);
+                        const float sc = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(scl + i * row_step * scale_pitch)));
+                        *reinterpret_cast<uint4*>(dst + i * row_step * 128) = dequant8(q.x, q.y, sc);
+                    }
+                    fence_async_smem();   // generic-proxy writes -> visible to the tensor core's reads
+                }
+                // (the LoRA slice has nothing to convert: the arrival only keeps the barrier's count)
                 __syncwarp();
-                if (lane == 0) remote_arrive(leader_conv0 + stage * 8);
+                if (lane == 0) remote_arrive_cta_release(leader_full0 + stage * 8);
                 if (++stage == Q8_STAGES) { stage = 0; phase ^= 1u; }
             }
-            w = nw;
-            kb = nkb;
-            have = have_next;
         }
     } else {
         // ------------------------------------------------ epilogue (warps 2..5, both CTAs)
@@ -466,9 +456,12 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
-// how many CTA pairs of this kernel the current device holds at once (cached per device)
-template <typename K>
-int max_pairs_of(K kern, int* out) {
+// Prepares one instantiation of the kernel on the current device (shared-memory opt-in) and tells
+// how many CTA pairs of it the device holds at once; cached per device and per instantiation
+// (the template parameters keep the caches of the four kernels apart).
+template <typename TC, bool B_MN>
+int max_pairs_of(int* out) {
+    auto kern = gemm_q8_kernel<TC, B_MN>;
     static int cache[64] = {0};
     static bool attr_done[64] = {false};
     int dev = 0;
@@ -504,7 +497,7 @@ int launch_q8(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mw, con
               const Q8Params& p) {
     auto kern = gemm_q8_kernel<TC, B_MN>;
     int max_pairs = 0;
-    const int rc = max_pairs_of(kern, &max_pairs);
+    const int rc = max_pairs_of<TC, B_MN>(&max_pairs);
     if (rc != PK_OK) return rc;
     const int64_t tiles = ((p.M + 2 * Q8_BM - 1) / (2 * Q8_BM)) * ((p.N + Q8_BN - 1) / Q8_BN);
     int64_t pairs = max_pairs;
@@ -536,8 +529,9 @@ extern "C" int pk_gemm_q8_lora(void* stream, int c_dtype, int trans_w, int64_t M
     const bool lora = XA != nullptr && r > 0;
     PK_REQUIRE(!lora || (L != nullptr && ldxa >= r && ldl >= (trans_w ? r : N)), "bad LoRA operands");
     const int64_t w_cols = trans_w ? K : N;
-    bool ok = w_cols % 32 == 0 && lda % 8 == 0 && ldc % 8 == 0 && N % 8 == 0 && aligned16(A) && aligned16(Wq) && aligned16(C) &&
-              (reinterpret_cast<uintptr_t>(scales) & 1u) == 0 && (residual == nullptr || (aligned16(residual) && ldr % 8 == 0)) &&
+    // the scales of a half slice are copied as 8-byte (W is [K, N]) or 4-byte (W is [N, K]) pieces
+    bool ok = (trans_w ? w_cols % 64 == 0 : w_cols % 128 == 0) && aligned16(scales) && lda % 8 == 0 && ldc % 8 == 0 && N % 8 == 0 && aligned16(A) && aligned16(Wq) && aligned16(C) &&
+              (residual == nullptr || (aligned16(residual) && ldr % 8 == 0)) &&
               (bias == nullptr || aligned16(bias)) && M < (int64_t(1) << 31) && N < (int64_t(1) << 31) && K < (int64_t(1) << 31);
     if (lora) ok = ok && r % 8 == 0 && r <= 64 && ldxa % 8 == 0 && ldl % 8 == 0 && aligned16(XA) && aligned16(L);
     if (!ok) {
@@ -581,3 +575,4 @@ extern "C" int pk_gemm_q8_lora(void* stream, int c_dtype, int trans_w, int64_t M
     if (c_dtype == PK_F32) return launch_q8<float, false>(st, ma, mw, mxa, ml, p);
     return launch_q8<bf16, false>(st, ma, mw, mxa, ml, p);
 }
+

@@ -47,6 +47,10 @@ public:
     const Matrix& host() const;
     operator const Matrix&() const { return host(); }  // NOLINT
     float operator()(size_t i, size_t j) const { return host()(i, j); }
+    // Element of the host view that can be assigned to (v->data(i, j) = x, as code written for
+    // the reference does): like mutable_host(), so the device copy is refreshed on its next use.
+    // Code that only reads should go through host().
+    float& operator()(size_t i, size_t j) { return mutable_host()(i, j); }
     // Mutable host access: the device copy becomes stale and is re-uploaded on next use.
     Matrix& mutable_host();
     Value& operator=(const Matrix& m);

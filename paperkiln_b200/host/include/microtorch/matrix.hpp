@@ -4,12 +4,12 @@
 // by tests or bindings); the arithmetic of the training step never runs on it.
 // Same surface as the matrix type the reference's tape is written against
 // (rows(), cols(), operator()(i,j), data(), fill) so code written for the
-// reference's Variable::data / ::grad reads unchanged.
+// reference's Variable::data / ::grad reads unchanged. Like the reference's matrix type it
+// lives in the global namespace (code written for the reference names it unqualified) and is
+// also visible as microtorch::Matrix.
 #include <cstddef>
 #include <stdexcept>
 #include <vector>
-
-namespace microtorch {
 
 class Matrix {
 public:
@@ -23,7 +23,7 @@ public:
     bool empty() const { return buf_.empty(); }
 
     float& operator()(size_t i, size_t j) { return buf_[index(i, j)]; }
-    float operator()(size_t i, size_t j) const { return buf_[index(i, j)]; }
+    const float& operator()(size_t i, size_t j) const { return buf_[index(i, j)]; }
 
     float* data() { return buf_.data(); }
     const float* data() const { return buf_.data(); }
@@ -48,4 +48,6 @@ private:
     std::vector<float> buf_;
 };
 
+namespace microtorch {
+using ::Matrix;
 }  // namespace microtorch

@@ -9,6 +9,7 @@
 // blocks call the fused forms (one attention node for all heads, bias / residual in
 // the GEMM epilogue).
 #include <cmath>
+#include <functional>
 #include <map>
 #include <memory>
 #include <string>
@@ -192,6 +193,101 @@ private:
     bool runs_built_ = false;
     float b1_, b2_, eps_, wd_;
     long t_ = 0;
+};
+
+// Inverted dropout layer (reference: include/microtorch/nn.hpp:281-289, src/nn.cpp:479-482):
+// identity in eval mode or when p == 0; in training mode each call draws a fresh mask from the
+// next seed. Must not be used inside a checkpointed segment (the recomputation would draw a
+// different mask), as the reference's checkpoint contract says.
+class Dropout : public Module {
+public:
+    explicit Dropout(float p, unsigned long long seed = 0) : p_(p), next_seed_(seed) {}
+    Var forward(const Var& x) const;
+
+private:
+    float p_;
+    mutable unsigned long long next_seed_;
+};
+
+// ---- learning-rate schedules over an optimizer's public `lr` field ----------------------
+// (reference: include/microtorch/nn.hpp:291-340; templated because SGD and AdamW share the
+// field, not a base class)
+// Linear warm-up over `warmup` steps, then half a cosine from the base rate down to min_lr at
+// step `total`; constant min_lr afterwards.
+template <typename Opt>
+class CosineWarmupLR {
+public:
+    CosineWarmupLR(Opt& opt, size_t warmup, size_t total, float min_lr = 0.0f)
+        : opt_(opt), base_(opt.lr), warmup_(warmup), total_(total), floor_(min_lr) {}
+    void step() {
+        ++count_;
+        if (warmup_ > 0 && count_ <= warmup_) {
+            opt_.lr = base_ * static_cast<float>(count_) / warmup_;
+            return;
+        }
+        float frac = 1.0f;
+        if (total_ > warmup_) frac = static_cast<float>(count_ - warmup_) / (total_ - warmup_);
+        if (frac > 1.0f) frac = 1.0f;
+        opt_.lr = floor_ + 0.5f * (base_ - floor_) * (1.0f + std::cos(3.14159265358979f * frac));
+    }
+    size_t current_step() const { return count_; }
+
+private:
+    Opt& opt_;
+    float base_;
+    size_t warmup_, total_, count_ = 0;
+    float floor_;
+};
+
+// lr = base * gamma^(steps / step_size), the product formed by repeated multiplication.
+template <typename Opt>
+class StepLR {
+public:
+    StepLR(Opt& opt, size_t step_size, float gamma = 0.1f) : opt_(opt), base_(opt.lr), every_(step_size), gamma_(gamma) {}
+    void step() {
+        ++count_;
+        float lr = base_;
+        for (size_t k = 0; k < count_ / every_; ++k) lr *= gamma_;
+        opt_.lr = lr;
+    }
+
+private:
+    Opt& opt_;
+    float base_;
+    size_t every_, count_ = 0;
+    float gamma_;
+};
+
+// ---- declared for source compatibility, not provided -------------------------------------
+// Attention variants and the depth-attention stack of the reference's research models. They
+// are outside the checkpointed transformer-block training path; the classes exist so that code
+// written against the reference's headers (its Python bindings, tools/parity_model.hpp)
+// compiles unchanged. Constructors that own ordinary Linear layers build them; every forward
+// throws std::runtime_error.
+class SlidingWindowAttention : public Module {
+public:
+    SlidingWindowAttention(size_t d, size_t n_heads, size_t window, size_t sinks = 1, unsigned seed = 0);
+    Var forward(const Var& x, size_t seq_len = 0) const;
+    std::shared_ptr<Linear> c_attn, c_proj;
+    size_t H, dk, window, sinks;
+};
+
+class KimiLinearAttention : public Module {
+public:
+    KimiLinearAttention(size_t d, size_t n_heads, unsigned seed = 0, bool causal = true);
+    Var forward(const Var& x, size_t seq_len = 0) const;
+    std::shared_ptr<Linear> c_attn, c_proj;
+    size_t H, dk;
+    bool causal;
+};
+
+class AttnResStack : public Module {
+public:
+    AttnResStack(std::vector<std::shared_ptr<Module>> owned, std::vector<std::function<Var(const Var&)>> fns, size_t d,
+                 size_t block_size = 0);
+    Var forward(const Var& h1) const;
+    std::vector<Var> w;
+    size_t block_size;
 };
 
 }  // namespace nn

@@ -42,6 +42,19 @@ Var apply_rope(const Var& qk, const std::vector<int>& pos, float theta_base, siz
 Var fused_attention(const Var& q, const Var& k, const Var& v, float scale, size_t seq_len, bool causal);
 float clip_grad_norm(const std::vector<Var>& params, float max_norm);
 Matrix attention_mask(size_t rows, size_t seq_len, bool causal);
+Var softmax_row(const Var& x);               // dX = S .* (dY - rowsum(dY .* S))
+// Inverted dropout (src/ops.cpp:760-786): keep with probability 1 - p, kept values scaled by
+// 1 / (1 - p); the mask is a pure function of (seed, element index), drawn on the host with the
+// reference's generator (std::mt19937_64 + uniform_real_distribution<float>, row-major) and
+// applied on the device; backward replays it. p == 0 returns x. Not allowed inside checkpoint().
+Var dropout(const Var& x, float p, unsigned long long seed);
+
+// ---- declared for source compatibility, not provided -------------------------------
+// Research mechanisms of the reference outside the checkpointed transformer-block training
+// path. The declarations let code written against the reference's headers (its Python
+// bindings, its model zoo header) compile unchanged; calling one throws std::runtime_error.
+// (four parameters: the arity the reference's python/bindings.cpp binds)
+Var kimi_attention(const Var& q, const Var& k, const Var& v, bool causal);
 
 // ---- fused forms ------------------------------------------------------------------
 // y = x W (+ bias) (+ residual): matmul + add_bias + add in one GEMM epilogue.

@@ -10,6 +10,7 @@
 
 #include "pk.h"
 
+#include "microtorch/dp.hpp"
 #include "microtorch/flex.hpp"
 #include "microtorch/gguf.hpp"
 #include "microtorch/llama.hpp"
@@ -39,6 +40,7 @@ struct Model {
     nn::ParamPack pack;
     bool packed = false;
     std::unique_ptr<nn::AdamW> opt;
+    std::unique_ptr<dp::GradientExchange> exchange;   // data-parallel gradient exchange (mt_dp_*)
     float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f, wd = 0.01f;
     int64_t live_after_fwd = 0;
     size_t loss_chunk = 16384;
@@ -476,11 +478,11 @@ int mt_model_step(void* h, const int32_t* ids_h, const int32_t* targets_h, int64
             m->live_after_fwd = static_cast<int64_t>(live_variables() - live0);
             Var root = loss_scale == 1.0f ? loss : ops::scale(loss, loss_scale);
             backward(root);
-            loss_value = loss->data(0, 0);
+            loss_value = loss->data.host()(0, 0);
         } else {
             NoGrad ng;
             Var loss = m->loss(ids, targets, static_cast<size_t>(seq_len));
-            loss_value = loss->data(0, 0);
+            loss_value = loss->data.host()(0, 0);
         }
         device::step_end();
         if (loss_h) *loss_h = loss_value;
@@ -653,6 +655,64 @@ int mt_model_bucket(void* h, int64_t i, void** ptr, int64_t* count) {
         *ptr = m->pack.grad.f32() + begin;
         *count = static_cast<int64_t>(end - begin);
     });
+}
+
+// ---- data parallelism over the collective group of libpk -----------------------------------
+namespace {
+void dp_attach(Model* m, void* comm) {
+    if (!m->packed) {
+        pk_comm_destroy(comm);
+        throw std::runtime_error("data parallelism needs a packed model (pack=1)");
+    }
+    std::vector<std::pair<float*, int64_t>> buckets;
+    for (const auto& b : m->buckets) {
+        const size_t begin = m->pack.offset[b.first];
+        const size_t end = b.second + 1 < m->pack.offset.size() ? m->pack.offset[b.second + 1] : m->pack.total;
+        buckets.emplace_back(m->pack.grad.f32() + begin, static_cast<int64_t>(end - begin));
+    }
+    m->exchange.reset();
+    m->exchange = std::make_unique<dp::GradientExchange>(
+        comm, std::move(buckets), std::make_pair(m->pack.grad.f32(), static_cast<int64_t>(m->pack.total)));
+    m->exchange->attach();
+}
+dp::GradientExchange& DPX(void* h) {
+    Model* m = M(h);
+    if (!m->exchange) throw std::runtime_error("the model has no gradient exchange (call mt_dp_init first)");
+    return *m->exchange;
+}
+}  // namespace
+
+int mt_dp_unique_id(void* id_h, size_t cap) {
+    return guard([&] { device::check(pk_comm_unique_id(id_h, cap), "pk_comm_unique_id"); });
+}
+int mt_dp_init(void* h, const void* id_h, int rank, int world, int max_ctas) {
+    return guard([&] {
+        Model* m = M(h);
+        void* comm = nullptr;
+        device::check(pk_comm_init(id_h, rank, world, max_ctas, &comm), "pk_comm_init");
+        dp_attach(m, comm);
+    });
+}
+int mt_dp_enable(void* h, int on) {
+    return guard([&] { DPX(h).set_enabled(on != 0); });
+}
+int mt_dp_finish(void* h) {
+    return guard([&] { DPX(h).finish(); });
+}
+int mt_dp_wait_host(void* h) {
+    return guard([&] { DPX(h).wait_host(); });
+}
+int mt_dp_set_timeout(void* h, double seconds) {
+    return guard([&] { DPX(h).set_timeout(seconds); });
+}
+int mt_dp_stats(void* h, int64_t* launches_last_step_h, int* single_collective_h) {
+    return guard([&] {
+        if (launches_last_step_h) *launches_last_step_h = DPX(h).launches_last_step();
+        if (single_collective_h) *single_collective_h = DPX(h).single_collective() ? 1 : 0;
+    });
+}
+int mt_dp_destroy(void* h) {
+    return guard([&] { M(h)->exchange.reset(); });
 }
 
 int mt_set_segment_hook(mt_segment_cb cb, void* user) {

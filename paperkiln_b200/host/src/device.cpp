@@ -28,6 +28,7 @@ struct Runtime {
     DType cdt = DType::F32;
     bool step_residency = true;
     bool device_ops = true;
+    bool env_seen = false;  // the environment was consulted (explicitly or at first use)
 };
 Runtime& rt() {
     static Runtime r;
@@ -137,6 +138,7 @@ void set(Device d) {
 }
 
 void set_from_env() {
+    rt().env_seen = true;
     if (const char* g = std::getenv("MICROTORCH_GPU")) rt().ordinal = std::atoi(g);
     if (const char* t = std::getenv("MICROTORCH_DTYPE")) {
         const std::string s(t);
@@ -155,6 +157,13 @@ void set_from_env() {
 void set_stream(void* s) { rt().ext_stream = s; }
 void* stream() {
     Runtime& r = rt();
+    if (r.dev != Device::CUDA && !r.inited && !r.env_seen) {
+        // A program written for the reference may never touch the device switch (its CPU path
+        // needs none). The first op then honours MICROTORCH_DEVICE / _DTYPE / _GPU once, so
+        // such a program runs on the GPU by setting the environment alone.
+        r.env_seen = true;
+        set_from_env();
+    }
     if (r.dev != Device::CUDA)
         throw std::runtime_error("microtorch: the CUDA device is not selected and there is no CPU fallback "
                                  "(call device::init() or set MICROTORCH_DEVICE=cuda)");

@@ -140,6 +140,12 @@ Embedding::Embedding(size_t vocab, size_t d, unsigned seed) {
 }
 Var Embedding::forward(const std::vector<int>& ids) const { return ops::embedding(weight, ids); }
 
+// reference: src/nn.cpp:479-482
+Var Dropout::forward(const Var& x) const {
+    if (!training() || p_ == 0.0f) return x;
+    return ops::dropout(x, p_, next_seed_++);
+}
+
 CausalSelfAttention::CausalSelfAttention(size_t d, size_t n_heads, unsigned seed, bool causal_)
     : H(n_heads), dk(d / n_heads), causal(causal_) {
     if (d % n_heads != 0) throw std::runtime_error("attention: d must divide by n_heads");

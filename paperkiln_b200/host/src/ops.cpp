@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstring>
 #include <list>
+#include <random>
 #include <stdexcept>
 
 #include "pk.h"
@@ -447,7 +448,7 @@ Var mean(const Var& x) {
     return record(std::move(out), {x}, [n](Variable* self) {
         const Var& x = self->parents[0];
         if (!x->requires_grad) return;
-        const float g = self->grad(0, 0) / static_cast<float>(n);
+        const float g = self->grad.host()(0, 0) / static_cast<float>(n);
         Tensor dx = Tensor::empty(x->data.rows(), x->data.cols(), x->grad_dtype());
         check(pk_fill(S(), dx.dt(), dx.ptr(), g, i64(dx.numel())), "pk_fill");
         x->accumulate(dx);
@@ -664,7 +665,7 @@ Var cross_entropy(const Var& logits, const std::vector<int>& targets) {
     return record(std::move(out), {logits}, [work](Variable* self) {
         const Var& l = self->parents[0];
         if (!l->requires_grad) return;
-        const float g = self->grad(0, 0);  // the seed is host-known: no readback in the common case
+        const float g = self->grad.host()(0, 0);  // the seed is host-known: no readback in the common case
         Tensor dl = work;
         if (g != 1.0f)  // padding columns of a strided buffer hold zeros and stay zero
             check(pk_scale(S(), dl.dt(), dl.ptr(), g, dl.ptr(), i64(dl.rows() * dl.ld())), "pk_scale");
@@ -721,7 +722,7 @@ Var linear_cross_entropy(const Var& h, const Var& W, bool transposed_w, const st
     return record(std::move(out), {h, W}, [dh, dw](Variable* self) {
         const Var& h = self->parents[0];
         const Var& W = self->parents[1];
-        const float g = self->grad(0, 0);
+        const float g = self->grad.host()(0, 0);
         if (h->requires_grad && dh.defined()) {
             Tensor t = dh;
             if (g != 1.0f) check(pk_scale(S(), t.dt(), t.ptr(), g, t.ptr(), i64(t.numel())), "pk_scale");
@@ -814,6 +815,55 @@ float clip_grad_norm(const std::vector<Var>& params, float max_norm) {
         }
     }
     return total;
+}
+
+// reference: src/ops.cpp:140-167
+Var softmax_row(const Var& x) {
+    const Tensor& xt = x->compute();
+    Tensor y = new_act(xt.rows(), xt.cols());
+    check(pk_softmax_fwd(S(), xt.dt(), xt.ptr(), y.ptr(), i64(xt.rows()), i64(xt.cols())), "pk_softmax_fwd");
+    Tensor saved = y;
+    return record(std::move(y), {x}, [saved](Variable* self) {
+        const Var& x = self->parents[0];
+        if (!x->requires_grad) return;
+        Tensor g = grad_of(self);
+        Tensor dx = new_act(g.rows(), g.cols());
+        check(pk_softmax_bwd(S(), g.dt(), saved.ptr(), g.ptr(), dx.ptr(), i64(g.rows()), i64(g.cols())), "pk_softmax_bwd");
+        x->accumulate(dx);
+    });
+}
+
+namespace {
+// The reference's mask: one uniform draw per element in row-major order from mt19937_64(seed);
+// an element is kept (and scaled by 1 / keep) when the draw is below keep (src/ops.cpp:766-773).
+Tensor dropout_mask(size_t rows, size_t cols, float p, unsigned long long seed) {
+    const float keep = 1.0f - p, inv_keep = 1.0f / keep;
+    std::mt19937_64 rng(seed);
+    std::uniform_real_distribution<float> u(0.0f, 1.0f);
+    Matrix m(rows, cols);
+    float* d = m.data();
+    for (size_t i = 0; i < rows * cols; ++i) d[i] = (u(rng) < keep) ? inv_keep : 0.0f;
+    return Tensor::from_host(m, cdt());
+}
+}  // namespace
+
+// reference: src/ops.cpp:760-786
+Var dropout(const Var& x, float p, unsigned long long seed) {
+    if (p < 0.0f || p >= 1.0f) throw std::runtime_error("dropout: p must be in [0, 1)");
+    if (p == 0.0f) return x;
+    const Tensor& xt = x->compute();
+    Tensor mask = dropout_mask(xt.rows(), xt.cols(), p, seed);
+    Tensor y = new_act(xt.rows(), xt.cols());
+    check(pk_binary(S(), xt.dt(), 2, xt.ptr(), mask.ptr(), y.ptr(), i64(xt.numel())), "pk_binary");
+    return record(std::move(y), {x}, [p, seed](Variable* self) {
+        const Var& x = self->parents[0];
+        if (!x->requires_grad) return;
+        Tensor g = grad_of(self);
+        Tensor mask = dropout_mask(g.rows(), g.cols(), p, seed);  // replayed, not stored
+        Tensor dx = new_act(g.rows(), g.cols());
+        check(pk_binary(S(), g.dt(), 2, g.ptr(), mask.ptr(), dx.ptr(), i64(g.numel())), "pk_binary");
+        x->accumulate(dx);
+    });
 }
 
 Matrix attention_mask(size_t rows, size_t seq_len, bool causal) {
