@@ -211,6 +211,11 @@ def main():
     ap.add_argument("--accum", type=int, default=0,
                     help="micro-batches per step (gradient accumulation; exchange on the last one only); "
                          "0 = micro-batches of at most 65536 tokens per GPU")
+    ap.add_argument("--comm", default="pk", choices=["pk", "torch"],
+                    help="gradient exchange at N > 1: inside the library over libpk's collective group (pk, default) "
+                         "or torch.distributed all-reduces from the Python segment hook (torch)")
+    ap.add_argument("--nccl-max-ctas", type=int, default=int(os.environ.get("PK_NCCL_MAX_CTAS", "0")),
+                    help="--comm pk: cap on the CTAs NCCL's kernels take from the kernels they overlap (0: NCCL's default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=0)
     ap.add_argument("--skip-nockpt", action="store_true", help="do not measure the un-checkpointed step")
@@ -341,7 +346,17 @@ def main():
 
     def make_step(m):
         reducer = None
-        if world > 1:
+        in_library = world > 1 and args.comm == "pk"
+        if in_library:
+            # The exchange runs inside the library: each block's gradient range is all-reduced over
+            # libpk's collective group (NCCL) as that block's backward is enqueued. Rank 0 draws the
+            # communicator id; it travels over the launcher's process group.
+            idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+            if rank == 0:
+                idt.copy_(torch.frombuffer(bytearray(mt.Model.dp_unique_id()), dtype=torch.uint8))
+            dist.broadcast(idt, 0)
+            m.dp_init(idt.cpu().numpy().tobytes(), rank, world, args.nccl_max_ctas)
+        elif world > 1:
             from paperkiln_b200.dp import BucketAllReducer
             # block i's gradients are one contiguous fp32 range of the flat gradient buffer
             reducer = BucketAllReducer([torch.as_tensor(_Buf(p, n), device="cuda") for (p, n) in m.buckets()])
@@ -362,11 +377,15 @@ def main():
                 m.zero_grad()
                 loss = 0.0
                 for k in range(accum):
+                    if in_library:
+                        m.dp_enable(k == accum - 1)
                     if reducer is not None:
                         reducer.enabled = k == accum - 1
                     off = k * n_micro * 4
                     loss += m.step_ptr(host_ids[i].data_ptr() + off, host_tg[i].data_ptr() + off, n_micro, S,
                                        loss_scale=1.0 / (world * accum)) / accum
+            if in_library:
+                m.dp_finish()     # remaining ranges, then the compute stream waits for all transfers
             if reducer is not None:
                 reducer.finish()  # remaining buckets, then wait for all of them
             m.optimizer_step()

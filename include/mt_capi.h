@@ -175,6 +175,9 @@ int mt_dp_enable(void* model, int on);
 int mt_dp_finish(void* model);
 int mt_dp_wait_host(void* model);
 int mt_dp_set_timeout(void* model, double seconds);
+/* Gradient bytes up to which the whole buffer is sent as one collective (default 32 MiB; 0: always
+ * one collective per block, started during the backward pass). */
+int mt_dp_set_flat_threshold(void* model, int64_t bytes);
 int mt_dp_stats(void* model, int64_t* launches_last_step_h, int* single_collective_h);
 int mt_dp_destroy(void* model);
 

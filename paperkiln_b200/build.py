@@ -106,6 +106,12 @@ def build_host(verbose: bool = False, force: bool = False) -> Path:
     lib = PKG / "libmicrotorch.so"
     if force or not _newer(lib, objs + [PKG / "libpk.so"]):
         _run([cxx, "-shared", "-o", lib, *objs, "-L", PKG, "-lpk", "-Wl,-rpath,$ORIGIN"], verbose)
+    # example programs over the C driver ABI (one executable per file of host/examples)
+    for src in sorted((HOST / "examples").glob("*.cpp")):
+        exe = PKG / src.stem
+        if force or not _newer(exe, [src, lib, *headers]):
+            _run([cxx, "-O2", "-std=c++17", "-I", INCLUDE, src, "-o", exe, "-L", PKG, "-lmicrotorch", "-lpk", "-pthread",
+                  "-Wl,-rpath,$ORIGIN"], verbose)
     return lib
 
 

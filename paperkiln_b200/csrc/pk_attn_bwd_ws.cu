@@ -60,11 +60,14 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
+// Rows pos.. of sequence `seq` (three-dimensional tensor maps: feature, position, sequence). Rows
+// past the end of the sequence read as zero, never as the next sequence's rows: P = 0 or dS = 0
+// times an Inf of a neighbour would otherwise leak NaN into this sequence's gradients.
 template <int DK>
-__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, int col0, int64_t row, uint32_t bar,
+__device__ __forceinline__ void tma_tile(uint32_t dst, const CUtensorMap* map, int col0, int pos, int seq, uint32_t bar,
                                          uint32_t chunk_pitch) {
 #pragma unroll
-    for (int c = 0; c < DK / 64; ++c) tma_load_2d(dst + c * chunk_pitch, map, col0 + c * 64, static_cast<int32_t>(row), bar);
+    for (int c = 0; c < DK / 64; ++c) tma_load_3d(dst + c * chunk_pitch, map, col0 + c * 64, pos, seq, bar);
 }
 __device__ __forceinline__ void st16_global(bf16* dst, const uint32_t (&r)[16]) {
 #pragma unroll
@@ -220,16 +223,16 @@ attn_bwd_ws_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (lane == 0) {
             bool ok = true;
             mbar_expect_tx(smem_u32(qdo_full), 2 * L::TILEQ);
-            tma_tile<DK>(sQ, &map_q, h * DK, seq0 + q0, smem_u32(qdo_full), CH128);
-            tma_tile<DK>(sDO, &map_do, h * DK, seq0 + q0, smem_u32(qdo_full), CH128);
+            tma_tile<DK>(sQ, &map_q, h * DK, q0, b, smem_u32(qdo_full), CH128);
+            tma_tile<DK>(sDO, &map_do, h * DK, q0, b, smem_u32(qdo_full), CH128);
             for (int j = 0; j < nkv; ++j) {
                 const int st = j % NS, n = j / NS;
                 if (n > 0) ok = mbar_wait(smem_u32(&kv_empty[st]), (n - 1) & 1, abort_flag, &g_attn_bwd_ws_ctl);
                 if (!ok) break;
-                const int64_t row = seq0 + static_cast<int64_t>(j) * BW_COLS;
+                const int pos = j * BW_COLS;
                 mbar_expect_tx(smem_u32(&kv_full[st]), 2 * L::TILEK);
-                tma_tile<DK>(sK + st * L::TILEK, &map_k, hk * DK, row, smem_u32(&kv_full[st]), CH64);
-                tma_tile<DK>(sV + st * L::TILEK, &map_v, hk * DK, row, smem_u32(&kv_full[st]), CH64);
+                tma_tile<DK>(sK + st * L::TILEK, &map_k, hk * DK, pos, b, smem_u32(&kv_full[st]), CH64);
+                tma_tile<DK>(sV + st * L::TILEK, &map_v, hk * DK, pos, b, smem_u32(&kv_full[st]), CH64);
             }
         }
         __syncwarp();
@@ -465,8 +468,8 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (lane == 0) {
             bool ok = true;
             mbar_expect_tx(smem_u32(kv_full), 2 * L::TILEK);
-            tma_tile<DK>(sK, &map_k, hk * DK, seq0 + k0, smem_u32(kv_full), CH128);
-            tma_tile<DK>(sV, &map_v, hk * DK, seq0 + k0, smem_u32(kv_full), CH128);
+            tma_tile<DK>(sK, &map_k, hk * DK, k0, b, smem_u32(kv_full), CH128);
+            tma_tile<DK>(sV, &map_v, hk * DK, k0, b, smem_u32(kv_full), CH128);
             for (int it = 0; it < nit; ++it) {
                 const int st = it % NS, n = it / NS;
                 const int h = hk * group + it / per_head;
@@ -475,8 +478,8 @@ attn_bwd_ws_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&q_full[st]);
                 mbar_expect_tx(bar, 2 * L::TILEQ + 512);
-                tma_tile<DK>(sQ + st * L::TILEQ, &map_q, h * DK, seq0 + q0, bar, CH64);
-                tma_tile<DK>(sDO + st * L::TILEQ, &map_do, h * DK, seq0 + q0, bar, CH64);
+                tma_tile<DK>(sQ + st * L::TILEQ, &map_q, h * DK, q0, b, bar, CH64);
+                tma_tile<DK>(sDO + st * L::TILEQ, &map_do, h * DK, q0, b, bar, CH64);
                 const int64_t so = (static_cast<int64_t>(b) * p.Hq + h) * p.S_pad + q0;
                 bulk_load(sX + st * 512, p.lneg + so, 256, bar);
                 bulk_load(sX + st * 512 + 256, p.dneg + so, 256, bar);
@@ -702,14 +705,14 @@ int attn_bwd_ws(cudaStream_t st, const void* q, int64_t ldq, const void* k, int6
     const int64_t R = B * S;
     const int64_t wq = static_cast<int64_t>(Hq) * dk, wk = static_cast<int64_t>(Hkv) * dk;
     int rc;
-    if ((rc = make_tensor_map(&mq128, q, wq, R, ldq, 64, 128)) != PK_OK) return rc;
-    if ((rc = make_tensor_map(&mdo128, dout, wq, R, lddo, 64, 128)) != PK_OK) return rc;
-    if ((rc = make_tensor_map(&mk64, k, wk, R, ldk, 64, 64)) != PK_OK) return rc;
-    if ((rc = make_tensor_map(&mv64, v, wk, R, ldv, 64, 64)) != PK_OK) return rc;
-    if ((rc = make_tensor_map(&mq64, q, wq, R, ldq, 64, 64)) != PK_OK) return rc;
-    if ((rc = make_tensor_map(&mdo64, dout, wq, R, lddo, 64, 64)) != PK_OK) return rc;
-    if ((rc = make_tensor_map(&mk128, k, wk, R, ldk, 64, 128)) != PK_OK) return rc;
-    if ((rc = make_tensor_map(&mv128, v, wk, R, ldv, 64, 128)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mq128, q, wq, S, B, ldq, 64, 128)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mdo128, dout, wq, S, B, lddo, 64, 128)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mk64, k, wk, S, B, ldk, 64, 64)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mv64, v, wk, S, B, ldv, 64, 64)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mq64, q, wq, S, B, ldq, 64, 64)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mdo64, dout, wq, S, B, lddo, 64, 64)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mk128, k, wk, S, B, ldk, 64, 128)) != PK_OK) return rc;
+    if ((rc = make_tensor_map_3d(&mv128, v, wk, S, B, ldv, 64, 128)) != PK_OK) return rc;
     WsBwdParams p;
     p.dq = static_cast<bf16*>(dq);
     p.lddq = lddq;

@@ -131,6 +131,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
         : "memory");
 }
+// Tile of a [batch, rows, features] tensor map: x = feature, y = row inside the batch entry,
+// z = batch entry. Rows past the entry's end read as zero (they never come from the next entry).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // Makes generic-proxy shared-memory writes visible to the async proxy (UMMA operand reads).
@@ -173,6 +181,28 @@ __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 2^x for two values at once on the FMA pipe, leaving the special-function unit (16 results per
+// clock and SM) to other elements: x is clamped to >= -125 and split, with the 1.5 * 2^23
+// rounding trick, into its nearest integer n and a fraction f in [-0.5, 0.5]; 2^f is a cubic
+// (maximum relative error 7.5e-5, well inside the 2^-9 of the bf16 the result is rounded to) and
+// n goes straight into the exponent field. Inputs are <= 0 up to rounding; -inf gives 2^-125.
+__device__ __forceinline__ void ex2_fma_pair(uint64_t x2, float& y0, float& y1) {
+    float x0, x1;
+    f2_unpack(x2, x0, x1);
+    const uint64_t x = f2_pack(fmaxf(x0, -125.0f), fmaxf(x1, -125.0f));
+    const uint64_t t = f2_add(x, f2_pack(12582912.0f, 12582912.0f));        // low mantissa bits = n
+    const uint64_t n = f2_add(t, f2_pack(-12582912.0f, -12582912.0f));      // n as a float
+    const uint64_t f = f2_fma(n, f2_pack(-1.0f, -1.0f), x);                 // x - n, exact
+    uint64_t p = f2_fma(f2_pack(0.055171459913253784f, 0.055171459913253784f), f, f2_pack(0.2426108568906784f, 0.2426108568906784f));
+    p = f2_fma(p, f, f2_pack(0.6932609677314758f, 0.6932609677314758f));
+    p = f2_fma(p, f, f2_pack(0.9999281167984009f, 0.9999281167984009f));
+    float t0, t1, p0, p1;
+    f2_unpack(t, t0, t1);
+    f2_unpack(p, p0, p1);
+    y0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+    y1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
 }
 
 // 128-byte-swizzled shared-memory operand descriptor (version 1, layout type 2).

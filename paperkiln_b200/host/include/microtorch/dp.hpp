@@ -46,8 +46,9 @@ public:
     void wait_host();
     void set_timeout(double seconds);
     bool single_collective() const { return single_; }
+    // Gradient bytes up to which the whole buffer goes out as one collective (default 32 MiB).
+    void set_flat_threshold(int64_t bytes);
     int64_t launches_last_step() const { return launches_last_; }
-    // Gradient bytes below which the whole buffer goes out as one collective.
     static constexpr int64_t kSingleCollectiveBytes = int64_t(32) << 20;
 
 private:

@@ -705,6 +705,9 @@ int mt_dp_wait_host(void* h) {
 int mt_dp_set_timeout(void* h, double seconds) {
     return guard([&] { DPX(h).set_timeout(seconds); });
 }
+int mt_dp_set_flat_threshold(void* h, int64_t bytes) {
+    return guard([&] { DPX(h).set_flat_threshold(bytes); });
+}
 int mt_dp_stats(void* h, int64_t* launches_last_step_h, int* single_collective_h) {
     return guard([&] {
         if (launches_last_step_h) *launches_last_step_h = DPX(h).launches_last_step();

@@ -63,6 +63,10 @@ void GradientExchange::finish() {
     launches_ = 0;
 }
 
+void GradientExchange::set_flat_threshold(int64_t bytes) {
+    single_ = flat_.first != nullptr && flat_.second * int64_t(sizeof(float)) <= bytes;
+}
+
 void GradientExchange::wait_host() { check(pk_comm_wait_host(comm_), "pk_comm_wait_host"); }
 void GradientExchange::set_timeout(double seconds) { check(pk_comm_set_timeout(comm_, seconds), "pk_comm_set_timeout"); }
 

@@ -265,6 +265,41 @@ class Model:
         _check(libmt().mt_model_clip_grad_norm(self._h, max_norm, ctypes.byref(n)), "mt_model_clip_grad_norm")
         return float(n.value)
 
+    # ---- data parallelism inside the library (mt_dp_*: NCCL through libpk's collective group) ----
+    @staticmethod
+    def dp_unique_id() -> bytes:
+        """The 128-byte communicator id; rank 0 draws it and the launcher hands it to every rank."""
+        buf = ctypes.create_string_buffer(128)
+        _check(libmt().mt_dp_unique_id(buf, 128), "mt_dp_unique_id")
+        return buf.raw
+
+    def dp_init(self, unique_id: bytes, rank: int, world: int, max_ctas: int = 0):
+        _check(libmt().mt_dp_init(self._h, unique_id, rank, world, max_ctas), "mt_dp_init")
+
+    def dp_enable(self, on: bool):
+        _check(libmt().mt_dp_enable(self._h, int(on)), "mt_dp_enable")
+
+    def dp_finish(self):
+        _check(libmt().mt_dp_finish(self._h), "mt_dp_finish")
+
+    def dp_wait_host(self):
+        _check(libmt().mt_dp_wait_host(self._h), "mt_dp_wait_host")
+
+    def dp_set_timeout(self, seconds: float):
+        _check(libmt().mt_dp_set_timeout(self._h, seconds), "mt_dp_set_timeout")
+
+    def dp_set_flat_threshold(self, nbytes: int):
+        _check(libmt().mt_dp_set_flat_threshold(self._h, nbytes), "mt_dp_set_flat_threshold")
+
+    def dp_stats(self) -> Tuple[int, bool]:
+        """(collectives started in the last finished step, whole gradient sent as one buffer)."""
+        n, single = ctypes.c_int64(0), ctypes.c_int(0)
+        _check(libmt().mt_dp_stats(self._h, ctypes.byref(n), ctypes.byref(single)), "mt_dp_stats")
+        return int(n.value), bool(single.value)
+
+    def dp_destroy(self):
+        _check(libmt().mt_dp_destroy(self._h), "mt_dp_destroy")
+
     # ---- data-parallel gradient buckets ----
     def buckets(self) -> List[Tuple[int, int]]:
         """[(device pointer, fp32 element count)]: one per transformer block, then the rest."""

@@ -480,6 +480,47 @@ def test_attention(pk, dtype, cfg):
     close(dv, vf.grad, gtol)
 
 
+@pytest.mark.parametrize("cfg", [(2, 200, 2, 1, 64, True), (3, 333, 2, 2, 128, False), (2, 70, 4, 2, 64, True)])
+def test_attention_sequences_are_isolated_even_from_infinities(pk, cfg):
+    """Exact isolation between stacked sequences (tests/test_batching.cpp:108-120 of the reference)
+    when the sequence length is not a multiple of the kernels' tile: the last tile of a sequence
+    must not read the next sequence's rows at all. Infinities planted in the LAST sequence's q, k, v
+    and upstream gradient must leave every other sequence's outputs and gradients bit-identical
+    (a masked score times an infinite value would otherwise give NaN)."""
+    B, S, Hq, Hkv, dk, causal = cfg
+    R = B * S
+    scale = 1.0 / math.sqrt(dk)
+
+    def run(poison):
+        q = rnd(R, Hq * dk, seed=21, lo=-1, hi=1, dtype=torch.bfloat16)
+        k = rnd(R, Hkv * dk, seed=22, lo=-1, hi=1, dtype=torch.bfloat16)
+        v = rnd(R, Hkv * dk, seed=23, lo=-1, hi=1, dtype=torch.bfloat16)
+        do = rnd(R, Hq * dk, seed=24, lo=-1, hi=1, dtype=torch.bfloat16)
+        if poison:
+            for t in (q, k, v, do):
+                t[(B - 1) * S:] = float("inf")
+        out = torch.empty_like(q)
+        lse = torch.empty(R, Hq, device="cuda")
+        pkt.check(pk.pk_attn_fwd(stream(), BF16, ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out), Hq * dk,
+                                 ptr(lse), B, S, Hq, Hkv, dk, scale, int(causal)))
+        assert pk.pk_attn_last_path() == 1
+        dq, dkk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        sc = scratch(pk.pk_attn_bwd_scratch_bytes(B, S, Hq))
+        pkt.check(pk.pk_attn_bwd(stream(), BF16, ptr(q), Hq * dk, ptr(k), Hkv * dk, ptr(v), Hkv * dk, ptr(out), Hq * dk,
+                                 ptr(lse), ptr(do), Hq * dk, ptr(dq), Hq * dk, ptr(dkk), Hkv * dk, ptr(dv), Hkv * dk, ptr(sc),
+                                 B, S, Hq, Hkv, dk, scale, int(causal)))
+        torch.cuda.synchronize()
+        return [t[:(B - 1) * S].clone() for t in (out, lse, dq, dkk, dv)]
+
+    clean, poisoned = run(False), run(True)
+    for name, a, b in zip(("out", "lse", "dq", "dk", "dv"), clean, poisoned):
+        assert bool(torch.isfinite(b.float()).all()), f"{name}: the neighbouring sequence leaked in"
+        assert torch.equal(a, b), f"{name} of the untouched sequences changed"
+    st = ctypes.c_int(0)
+    pkt.check(pk.pk_attn_tc_status(ctypes.byref(st), 1))
+    assert st.value == 0
+
+
 @pytest.mark.parametrize("cfg", [(2, 200, 2, 2, 64, True), (1, 640, 4, 1, 64, True), (2, 333, 2, 2, 128, False),
                                  (1, 1100, 2, 2, 128, True)])
 def test_attention_tensor_core_growing_maxima(pk, cfg):
