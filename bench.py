@@ -5,8 +5,7 @@
 
 One "step" = zero_grad + forward + cross entropy + backward with per-block recompute +
 (N > 1: fp32 gradient all-reduce overlapped with the backward) + AdamW, on one batch of
-synthetic token ids. Prints ONE JSON line (rank 0). Workloads are the configurations of
-the task's baseline file:
+synthetic token ids. Prints ONE JSON line (rank 0). Workloads:
   c1  tiny Llama fp32 (4 layers, d 128, batch 8 x 256)            -- the CPU-parity case
   c2  GPT-2-small shape, bf16, batch 16 x 1024
   c3  Qwen2.5-0.5B-shape QLoRA (Q8_0 frozen base, LoRA r=16), bf16, batch 8 x 2048
@@ -424,6 +423,7 @@ def main():
     pk.pk_prof_enable(0)
     clocks = sampler.stop()
     peak_ckpt = mt.mem_stats()["activation_peak"]
+    peak_live = {f"{sz / 2 ** 20:.1f} MiB": n for sz, n in mt.peak_blocks().items() if sz * n >= (8 << 20)}
     import ctypes
     prof = {}
     for kind, name in ((0, "gemm_tc"), (1, "gemm_simt"), (2, "attn_fwd"), (3, "attn_bwd")):
@@ -470,13 +470,20 @@ def main():
     achieved = g["flops"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else 0.0
     f_blk, f_attn, f_head = flops_per_token(w)
     L = w["layers"]
-    step_flops = (L * 4 * (f_blk + f_attn) + 3 * f_head) * tokens_global
-    model_flops = 3 * (L * (f_blk + f_attn) + f_head) * tokens_global
+    if w.get("qlora"):
+        # frozen base: the weight-gradient GEMMs of the projections and of the (tied, frozen) head are
+        # not executed -- forward + recompute + input gradient for a block, forward + input gradient
+        # for the head; attention is as for a dense model. (The rank-16 LoRA products are left out.)
+        step_flops = (L * (3 * f_blk + 4 * f_attn) + 2 * f_head) * tokens_global
+        model_flops = (L * (2 * f_blk + 3 * f_attn) + 2 * f_head) * tokens_global
+    else:
+        step_flops = (L * 4 * (f_blk + f_attn) + 3 * f_head) * tokens_global
+        model_flops = 3 * (L * (f_blk + f_attn) + f_head) * tokens_global
     launches = sum(p["launches"] for p in prof.values())
     # DRAM bytes of one launch of the dominant GEMM shape (the gate / up projection, M x dff x d):
     # dram__bytes_read + dram__bytes_write of an ncu capture at M = 16384 (113.1 + 231.1 MB for
-    # d 2048, dff 8192; see profiles/), scaled to this run's rows per GPU -- traffic grows in
-    # proportion to M. Only quoted for the shape that was captured.
+    # d 2048, dff 8192), scaled to this run's rows per GPU -- traffic grows in proportion to M.
+    # Only quoted for the shape that was captured.
     traffic, traffic_note = None, None
     if args.workload == "c4":
         traffic = 344.2e6 * (n_local / max(1, args.accum) / 16384.0)
@@ -493,7 +500,8 @@ def main():
     line["loss"] = loss
     line["clocks"] = clocks
     line["gpu_launches"] = int(launches)
-    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM; CTA pairs where the tiles suffice)", "achieved": achieved,
+    line["roofline"] = {"bound": "tensor", "kernel": ("gemm_q8_kernel (tcgen05 Q8_0 dequantise-GEMM + LoRA) / gemm_tc2_kernel" if w.get("qlora") else
+                                   "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM; CTA pairs where the tiles suffice)"), "achieved": achieved,
                         "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf if peak_tf else None,
                         "peak_source": peak_src, "traffic": traffic, "traffic_note": traffic_note,
                         "share_of_step": g["ms"] / e2e_ms if e2e_ms else None, "launches_timed": g["launches"]}
@@ -504,6 +512,7 @@ def main():
     line["mfu_model_flops"] = model_flops / (res_ms / args.steps * 1e-3) / 1e12 / args.gpus / (peaks.get("bf16_tflops", 1676.5))
     line["config"].update({
         "peak_activation_gib_checkpointed": peak_ckpt / 2 ** 30,
+        "peak_activation_live_blocks": peak_live,
         "peak_activation_gib_plain": (peak_plain / 2 ** 30) if isinstance(peak_plain, int) else peak_plain,
         "ms_per_step_plain": plain_ms,
         "persistent_gib": stats["persistent_peak"] / 2 ** 30,
@@ -601,7 +610,8 @@ def run_block(args, w, mt, pk, stream, base, world, rank, torch, np):
     line["clocks"] = clocks
     line["gpu_launches"] = int(sum(t[2] for t in prof_total.values()))
     achieved = g[1] / (g[0] * 1e-3) / 1e12 if g[0] > 0 else 0.0
-    line["roofline"] = {"bound": "tensor", "kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM; CTA pairs where the tiles suffice)", "achieved": achieved, "peak": peak_tf,
+    line["roofline"] = {"bound": "tensor", "kernel": ("gemm_q8_kernel (tcgen05 Q8_0 dequantise-GEMM + LoRA) / gemm_tc2_kernel" if w.get("qlora") else
+                                   "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM; CTA pairs where the tiles suffice)"), "achieved": achieved, "peak": peak_tf,
                         "unit": "TFLOP/s", "frac": achieved / peak_tf, "peak_source": "measured (MEASURED_PEAKS.json, burst cuBLAS bf16: "
                         "the block is timed alone)" if peaks else "fallback", "traffic": None,
                         "share_of_step": g[0] / bwd_ms if bwd_ms else None}

@@ -184,6 +184,10 @@ int mt_dp_destroy(void* model);
 /* out_h[0..5] = activation bytes in use, activation peak, persistent in use, persistent
  * peak, bytes reserved from the driver, number of driver allocations. */
 int mt_mem_stats(uint64_t* out_h);
+/* What was live at the activation high-water mark (since mt_reset_peak): up to `cap` pairs
+ * (block size in bytes, number of blocks) in ascending size order; *n_h = number of distinct
+ * sizes. Sizes identify the tensors of a step ([tokens, d], [tokens, d_ff], ...). */
+int mt_mem_peak_blocks(uint64_t* sizes_h, uint64_t* counts_h, int cap, int* n_h);
 int mt_reset_peak(void);
 int mt_empty_cache(void);
 int mt_live_variables(int64_t* n_h);

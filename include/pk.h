@@ -191,7 +191,9 @@ int pk_rope(void* stream, int dtype, void* x, int64_t ld, int64_t col0, int n_he
  * SwiGLU y = silu(g) * u and its backward: ops::silu + ops::mul
  * (src/ops.cpp:404-424, 76-83). GELU (tanh form, correct derivative):
  * ops::gelu (src/ops.cpp:106-138), k_gelu_fwd/bwd (src/cuda_ops.cu:125-150).
- * ReLU: ops::relu (src/ops.cpp:788-801). n = element count. */
+ * ReLU: ops::relu (src/ops.cpp:788-801). n = element count. Every backward of this group may
+ * write its result over one of its inputs (dg == g and du == u for SwiGLU): an element is read
+ * before it is written and belongs to one thread. */
 int pk_swiglu_fwd(void* stream, int dtype, const void* g, const void* u, void* y, int64_t n);
 int pk_swiglu_bwd(void* stream, int dtype, const void* dy, const void* g, const void* u,
                   void* dg, void* du, int64_t n);

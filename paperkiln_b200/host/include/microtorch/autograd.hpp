@@ -93,6 +93,14 @@ public:
     std::vector<Var> parents;
     std::function<void()> backward_fn;
 
+    // While the private sub-tape of a checkpointed segment runs its backward pass: how many of this
+    // node's consumers have not run their closure yet (-1 outside such a pass). When it reaches
+    // zero the node's output is dead -- no closure reads its own node's output -- and is returned
+    // to the allocator at once; a closure that finds 1 here (itself) on an interior input whose
+    // buffer nobody else references may overwrite that input with the gradient it produces
+    // (disposable_input()).
+    int pending_consumers = -1;
+
     // Optional preallocated home of the gradient (a window of a flat buffer shared by
     // all parameters of a model); used on the first accumulate() instead of a fresh
     // allocation. Must be zero when adopted.
@@ -156,6 +164,10 @@ private:
 };
 
 namespace autograd {
+// True when `v` is an interior node of a private sub-tape, this closure is its last pending
+// consumer and nobody else references its buffer: the closure may then write a result of the same
+// shape and dtype over v's data (after it has read it) instead of allocating.
+bool disposable_input(const Var& v);
 // After a node's closure has run during the top-level backward(), drop its closure and
 // its gradient (interior nodes only; leaves keep theirs). On by default: interior
 // gradients of a [tokens, d_model] network are most of the backward's memory. Switch

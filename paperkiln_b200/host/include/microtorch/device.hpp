@@ -21,6 +21,8 @@
 #include <cstdint>
 #include <memory>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "microtorch/matrix.hpp"
 
@@ -42,7 +44,8 @@ bool cuda_compiled();
 // MICROTORCH_GPU (ordinal). Reference: src/device.cpp:48-67.
 void set_from_env();
 
-// Selects the GPU, creates the compute stream. Idempotent.
+// Selects the GPU, creates the compute stream. Idempotent for the same ordinal; a process uses
+// one GPU, so another ordinal after the first throws (data parallelism is one process per GPU).
 void init(int ordinal = 0);
 bool initialized();
 // Use an externally owned stream (e.g. the current stream of a framework the
@@ -74,6 +77,9 @@ struct MemStats {
 MemStats mem_stats();
 void reset_peak();
 void empty_cache();
+// The activation blocks that were in use when the activation high-water mark was last raised
+// (since reset_peak): (block size in bytes, number of blocks), ascending by size.
+std::vector<std::pair<size_t, size_t>> peak_activation_blocks();
 
 // Throws std::runtime_error carrying pk_last_error() when rc != 0.
 void check(int rc, const char* what);

@@ -222,9 +222,24 @@ void topo(const Var& root, std::vector<Var>& order) {
 // level 0: keep everything; 1: drop closure + gradient of interior nodes once used;
 // 2: also drop their output data and parent links (private sub-tapes only).
 void run_reverse(std::vector<Var>& order, int level, const Variable* keep_grad_of) {
+    if (level >= 2) {
+        // consumers per node (a node that appears twice among a consumer's parents counts twice)
+        for (const Var& v : order) v->pending_consumers = 0;
+        for (const Var& v : order)
+            for (const Var& p : v->parents) ++p->pending_consumers;
+    }
     for (auto it = order.rbegin(); it != order.rend(); ++it) {
         Variable* n = it->get();
         if (n->backward_fn && !n->grad.empty()) n->backward_fn();
+        if (level >= 2) {
+            // an input whose last consumer has now run is dead: free it here, not when its own
+            // closure comes up (several closures later, with new gradients allocated in between)
+            for (const Var& p : n->parents)
+                if (p->pending_consumers > 0 && --p->pending_consumers == 0 && !p->is_leaf()) {
+                    p->data.reset();
+                    p->shadow = Tensor();
+                }
+        }
         if (level >= 1 && !n->is_leaf()) {
             n->backward_fn = nullptr;
             if (n != keep_grad_of) n->grad.reset();
@@ -233,7 +248,10 @@ void run_reverse(std::vector<Var>& order, int level, const Variable* keep_grad_o
                 n->parents.clear();
             }
         }
-        if (level >= 2) it->reset();
+        if (level >= 2) {
+            n->pending_consumers = -1;
+            it->reset();
+        }
     }
 }
 
@@ -329,6 +347,10 @@ NoGrad::NoGrad() : prev_(g_grad_enabled) { g_grad_enabled = false; }
 NoGrad::~NoGrad() { g_grad_enabled = prev_; }
 
 namespace autograd {
+bool disposable_input(const Var& v) {
+    return v && v->pending_consumers == 1 && !v->is_leaf() && v->data.on_device() && v->data.device().use_count() == 1 &&
+           v->data.device().is_dense() && !v->shadow.defined();
+}
 void set_release_interior(bool on) { g_release_interior = on; }
 bool release_interior() { return g_release_interior; }
 void set_segment_hook(std::function<void(int)> hook) { g_segment_hook = std::move(hook); }

@@ -734,6 +734,16 @@ int mt_mem_stats(uint64_t* out) {
         out[4] = s.reserved; out[5] = s.driver_allocs;
     });
 }
+int mt_mem_peak_blocks(uint64_t* sizes_h, uint64_t* counts_h, int cap, int* n_h) {
+    return guard([&] {
+        const auto blocks = device::peak_activation_blocks();
+        if (n_h) *n_h = static_cast<int>(blocks.size());
+        for (size_t i = 0; i < blocks.size() && static_cast<int>(i) < cap; ++i) {
+            if (sizes_h) sizes_h[i] = blocks[i].first;
+            if (counts_h) counts_h[i] = blocks[i].second;
+        }
+    });
+}
 int mt_reset_peak(void) {
     return guard([&] { device::reset_peak(); });
 }

@@ -43,6 +43,9 @@ struct Allocator {
     std::mutex mu;
     std::unordered_map<size_t, std::vector<void*>> free_blocks;
     MemStats stats;
+    // activation blocks in use by rounded size, and a copy taken whenever the activation
+    // high-water mark rises: what was live at the peak, by size
+    std::map<size_t, size_t> live_by_size, peak_by_size;
 
     static size_t round(size_t n) {
         if (n == 0) n = 1;
@@ -70,12 +73,20 @@ struct Allocator {
         }
         const int k = static_cast<int>(pool);
         stats.in_use[k] += rounded;
+        if (pool == Pool::Activation) {
+            ++live_by_size[rounded];
+            if (stats.in_use[k] > stats.peak[k]) peak_by_size = live_by_size;
+        }
         stats.peak[k] = std::max(stats.peak[k], stats.in_use[k]);
         return p;
     }
     void put(void* p, size_t rounded, Pool pool) {
         std::lock_guard<std::mutex> lk(mu);
         stats.in_use[static_cast<int>(pool)] -= rounded;
+        if (pool == Pool::Activation) {
+            auto it = live_by_size.find(rounded);
+            if (it != live_by_size.end() && --it->second == 0) live_by_size.erase(it);
+        }
         free_blocks[rounded].push_back(p);
     }
     void release_cached_locked() {
@@ -108,6 +119,11 @@ bool initialized() { return rt().inited; }
 void init(int ordinal) {
     Runtime& r = rt();
     if (r.inited && r.ordinal == ordinal) return;
+    // One GPU per process (the data-parallel layout is one process per GPU): the kernels cache
+    // per-device set-up -- shared-memory opt-ins, occupancy figures, the split-K workspace -- once.
+    if (r.inited)
+        throw std::runtime_error("microtorch: GPU " + std::to_string(r.ordinal) + " is already selected; a process uses one "
+                                 "GPU (start one process per GPU)");
     int n = 0;
     check(pk_device_count(&n), "pk_device_count");
     if (n <= 0) throw std::runtime_error("no CUDA device is visible; this library has no CPU execution path");
@@ -188,6 +204,11 @@ MemStats mem_stats() {
 void reset_peak() {
     std::lock_guard<std::mutex> lk(alloc().mu);
     for (int k = 0; k < 2; ++k) alloc().stats.peak[k] = alloc().stats.in_use[k];
+    alloc().peak_by_size = alloc().live_by_size;
+}
+std::vector<std::pair<size_t, size_t>> peak_activation_blocks() {
+    std::lock_guard<std::mutex> lk(alloc().mu);
+    return std::vector<std::pair<size_t, size_t>>(alloc().peak_by_size.begin(), alloc().peak_by_size.end());
 }
 void empty_cache() {
     std::lock_guard<std::mutex> lk(alloc().mu);

@@ -71,8 +71,10 @@ void gemm(const Tensor& A, bool ta, const Tensor& B, bool tb, Tensor& C, bool ac
           "pk_gemm");
 }
 
-// target.grad += op(A) . op(B)
-void gemm_to_grad(const Var& target, const Tensor& A, bool ta, const Tensor& B, bool tb) {
+// target.grad += op(A) . op(B). reuse_data: when this is the first contribution and target's own
+// output is dead after the calling closure (autograd::disposable_input), the product is written
+// over that output instead of into a fresh buffer; the caller must be done reading it.
+void gemm_to_grad(const Var& target, const Tensor& A, bool ta, const Tensor& B, bool tb, bool reuse_data = false) {
     const bool first = target->grad.empty() && !target->grad_home.defined();
     if (!first && (target->grad_home.defined() || target->grad.device().use_count() == 1) &&
         (target->grad_dtype() == DType::F32 || cdt() == DType::BF16)) {
@@ -81,7 +83,11 @@ void gemm_to_grad(const Var& target, const Tensor& A, bool ta, const Tensor& B, 
         gemm(A, ta, B, tb, g, true);
         return;
     }
-    Tensor c = Tensor::empty(target->data.rows(), target->data.cols(), target->grad_dtype());
+    Tensor c;
+    if (reuse_data && first && autograd::disposable_input(target) && target->data.device().dtype() == target->grad_dtype())
+        c = target->data.device();
+    else
+        c = Tensor::empty(target->data.rows(), target->data.cols(), target->grad_dtype());
     gemm(A, ta, B, tb, c, false);
     target->accumulate(c);
 }
@@ -363,11 +369,12 @@ Var linear(const Var& x, const Var& W, const Var& bias, const Var& residual, boo
         const Var& x = self->parents[0];
         const Var& W = self->parents[1];
         Tensor g = grad_of(self);
-        if (x->requires_grad) gemm_to_grad(x, g, false, W->compute(), !transposed_w);
         if (W->requires_grad) {
             if (!transposed_w) gemm_to_grad(W, x->compute(), true, g, false);  // [in,out] = X^T G
             else gemm_to_grad(W, g, true, x->compute(), false);               // [out,in] = G^T X
         }
+        // last use of x by this node is behind us: dX may take x's place when x is dead otherwise
+        if (x->requires_grad) gemm_to_grad(x, g, false, W->compute(), !transposed_w, /*reuse_data=*/true);
         size_t idx = 2;
         if (has_bias) {
             const Var& b = self->parents[idx++];
@@ -430,7 +437,11 @@ Var swiglu(const Var& gate, const Var& up) {
         const Tensor& gt = gate->compute();
         const Tensor& ut = up->compute();
         Tensor g = grad_of(self);
-        Tensor dg = new_act(gt.rows(), gt.cols()), du = new_act(gt.rows(), gt.cols());
+        // gate and up have no other use once this closure has read them: inside a checkpointed
+        // segment their gradients take their place (the kernel reads an element before it writes it)
+        const bool in_place = gate.get() != up.get() && autograd::disposable_input(gate) && autograd::disposable_input(up) &&
+                              gt.dtype() == gate->grad_dtype();
+        Tensor dg = in_place ? gt : new_act(gt.rows(), gt.cols()), du = in_place ? ut : new_act(gt.rows(), gt.cols());
         check(pk_swiglu_bwd(S(), gt.dt(), g.ptr(), gt.ptr(), ut.ptr(), dg.ptr(), du.ptr(), i64(gt.numel())), "pk_swiglu_bwd");
         if (gate->requires_grad) gate->accumulate(dg);
         if (up->requires_grad) up->accumulate(du);

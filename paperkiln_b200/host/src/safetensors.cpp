@@ -235,6 +235,9 @@ std::map<std::string, Matrix> load_safetensors(const std::string& path,
     if (!f) throw std::runtime_error("safetensors: short header");
     const auto entries = HeaderReader(htext).parse();
     const std::streamoff base = 8 + static_cast<std::streamoff>(hlen);
+    f.seekg(0, std::ios::end);
+    const std::uint64_t file_size = static_cast<std::uint64_t>(f.tellg());
+    const std::uint64_t data_size = file_size - static_cast<std::uint64_t>(base);
 
     std::map<std::string, Matrix> out;
     std::vector<std::uint16_t> half;
@@ -250,10 +253,19 @@ std::map<std::string, Matrix> load_safetensors(const std::string& path,
             throw std::runtime_error("safetensors: " + name + " is " + meta.dtype + "; this loader reads F32 and BF16");
         const size_t rows = meta.shape.size() == 2 ? meta.shape[0] : 1;
         const size_t cols = meta.shape.size() == 2 ? meta.shape[1] : (meta.shape.empty() ? 1 : meta.shape[0]);
-        Matrix m(rows, cols);
+        // Nothing is allocated before the header's claims have been checked against each other and
+        // against the file: the byte range lies inside the data section, the element count does
+        // not overflow, and shape x element size is exactly the range.
+        if (meta.offsets[1] < meta.offsets[0] || meta.offsets[1] > data_size)
+            throw std::runtime_error("safetensors: data range of " + name + " lies outside the file");
         const std::uint64_t nbytes = meta.offsets[1] - meta.offsets[0];
-        if (meta.offsets[1] < meta.offsets[0] || nbytes != static_cast<std::uint64_t>(rows) * cols * (f32 ? 4 : 2))
+        const std::uint64_t esize = f32 ? 4 : 2;
+        const std::uint64_t r64 = rows, c64 = cols;
+        if (r64 != 0 && c64 > (std::uint64_t(1) << 62) / r64)
+            throw std::runtime_error("safetensors: shape of " + name + " overflows");
+        if (r64 * c64 > nbytes / esize || r64 * c64 * esize != nbytes)
             throw std::runtime_error("safetensors: size mismatch at " + name);
+        Matrix m(rows, cols);
         f.seekg(base + static_cast<std::streamoff>(meta.offsets[0]));
         if (f32) {
             f.read(reinterpret_cast<char*>(m.data()), static_cast<std::streamsize>(nbytes));

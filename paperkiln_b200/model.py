@@ -45,6 +45,13 @@ def mem_stats() -> Dict[str, int]:
     return dict(zip(keys, (int(v) for v in out)))
 
 
+def peak_blocks() -> Dict[int, int]:
+    """{block bytes: number of blocks} of the activations that were live at the high-water mark."""
+    sizes, counts, n = (ctypes.c_uint64 * 256)(), (ctypes.c_uint64 * 256)(), ctypes.c_int(0)
+    _check(libmt().mt_mem_peak_blocks(sizes, counts, 256, ctypes.byref(n)), "mt_mem_peak_blocks")
+    return {int(sizes[i]): int(counts[i]) for i in range(min(n.value, 256))}
+
+
 def reset_peak():
     _check(libmt().mt_reset_peak(), "mt_reset_peak")
 

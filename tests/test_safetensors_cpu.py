@@ -84,7 +84,7 @@ def test_loader_rules_and_writer_layout(tmp_path):
     assert open(dst2, "rb").read() == raw
 
 
-@pytest.mark.parametrize("case", ["dtype", "size", "truncated", "garbage", "missing"])
+@pytest.mark.parametrize("case", ["dtype", "size", "truncated", "garbage", "missing", "huge_shape", "wrapping_shape"])
 def test_loader_rejects_bad_files(tmp_path, case):
     src, dst = tmp_path / "bad.safetensors", tmp_path / "out.safetensors"
     x = np.arange(6, dtype="<f4").reshape(2, 3)
@@ -99,6 +99,16 @@ def test_loader_rejects_bad_files(tmp_path, case):
         write_file(src, [("x", "F32", x)])
         raw = open(src, "rb").read()
         open(src, "wb").write(raw[:-8])
+    elif case in ("huge_shape", "wrapping_shape"):
+        # a hostile header: the claimed shape would need an enormous allocation, or its byte count
+        # wraps around 2^64 to the 24 bytes that are really there -- rejected before any allocation
+        write_file(src, [("x", "F32", x)])
+        raw = bytearray(open(src, "rb").read())
+        claim = b"[4611686018427387904, 3]" if case == "huge_shape" else b"[4611686018427387905, 4]"
+        hlen = struct.unpack("<Q", raw[:8])[0]
+        head = bytes(raw[8:8 + hlen]).replace(b"[2, 3]", claim)
+        head += b" " * ((-len(head)) % 8)
+        open(src, "wb").write(struct.pack("<Q", len(head)) + head + bytes(raw[8 + hlen:]))
     elif case == "garbage":
         open(src, "wb").write(struct.pack("<Q", 16) + b"{\"x\": [1, 2, }  ")
     else:
