@@ -101,6 +101,18 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b,
             const void* A, int64_t lda, const void* B, int64_t ldb,
             void* C, int64_t ldc, int accumulate,
             const float* bias, const void* residual, int64_t ldr);
+/* y = silu(A Wg) .* (A Wu): the gate and up projections of a SwiGLU feed-forward layer and the
+ * activation in ONE pass over A (bf16; A [M, K], Wg and Wu [K, N] row-major, y [M, N]). A CTA pair
+ * computes 128 columns of G = A Wg and the same 128 columns of U = A Wu side by side in tensor
+ * memory and the epilogue forms y; G and U (both or neither; row stride ldgu) are also stored
+ * when the caller needs them for the backward pass. G, U and y have exactly the bits of
+ * pk_gemm + pk_gemm + pk_swiglu_fwd: a forward pass that keeps nothing (a checkpointed segment
+ * under NoGrad) and a recomputation that keeps G and U produce the same y. Replaces
+ * ops::mul(ops::silu(gate), up) over two ops::matmul (src/llama.cpp:55-58; src/ops.cpp:404-424,
+ * 76-83). Needs M >= 256, N a multiple of 8 and >= 128, 16-byte aligned bases, leading dimensions
+ * multiples of 8; otherwise PK_ERR_UNSUPPORTED (use the three separate calls). */
+int pk_gemm_swiglu(void* stream, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* Wg, int64_t ldg,
+                   const void* Wu, int64_t ldu, void* G, void* U, int64_t ldgu, void* Y, int64_t ldy);
 int pk_gemm_last_path(void);
 /* Launch counts per kernel path since the last reset, for a host that wants to know which
  * kernels a whole step ran on (the last-path calls only see one launch). counts_h[0..n):

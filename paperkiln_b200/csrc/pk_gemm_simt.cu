@@ -24,6 +24,8 @@ int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int
 
 static thread_local int g_last_path = -1;
 static int g_force_simt = 0;
+int gemm_tc2_swiglu_launch(cudaStream_t st, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* Wg,
+                           int64_t ldg, const void* Wu, int64_t ldu, void* G, void* U, int64_t ldgu, void* Y, int64_t ldy);
 static int g_pair_mode = 1;  // 1: 256 x 256 tiles on CTA pairs where the shape has enough of them
 
 constexpr int BM = 64, BN = 64, BK = 16;
@@ -191,6 +193,29 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
                                         bias, residual, ldr);
     return launch_simt<bf16, bf16>(st, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate, bias,
                                    residual, ldr);
+}
+
+int pk_gemm_swiglu(void* stream, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* Wg, int64_t ldg,
+                   const void* Wu, int64_t ldu, void* G, void* U, int64_t ldgu, void* Y, int64_t ldy) {
+    PK_REQUIRE(M >= 0 && N >= 0 && K > 0, "bad shape");
+    if (M == 0 || N == 0) return PK_OK;
+    PK_REQUIRE(A && Wg && Wu && Y, "null pointer");
+    PK_REQUIRE((G == nullptr) == (U == nullptr), "G and U are stored together or not at all");
+    PK_REQUIRE(lda >= K && ldg >= N && ldu >= N && ldy >= N && (G == nullptr || ldgu >= N), "leading dimension too small");
+    const bool ok = !g_force_simt && N % 8 == 0 && M >= 256 && N >= 128 && lda % 8 == 0 && ldg % 8 == 0 && ldu % 8 == 0 &&
+                    ldy % 8 == 0 && (G == nullptr || ldgu % 8 == 0) && aligned16(A) && aligned16(Wg) && aligned16(Wu) &&
+                    aligned16(Y) && (G == nullptr || (aligned16(G) && aligned16(U))) && M < (int64_t(1) << 31) &&
+                    N < (int64_t(1) << 31) && K < (int64_t(1) << 31);
+    if (!ok) {
+        set_error("pk_gemm_swiglu: shape or alignment outside what the kernel takes (M %lld N %lld K %lld)",
+                  static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K));
+        return PK_ERR_UNSUPPORTED;
+    }
+    cudaStream_t st = as_stream(stream);
+    ProfScope prof(PROF_GEMM_TC, 4.0 * M * N * K, st);
+    g_last_path = 3;
+    note_launch(PATH_GEMM_TC_PAIR);
+    return gemm_tc2_swiglu_launch(st, M, N, K, A, lda, Wg, ldg, Wu, ldu, G, U, ldgu, Y, ldy);
 }
 
 int pk_gemm_last_path(void) { return g_last_path; }

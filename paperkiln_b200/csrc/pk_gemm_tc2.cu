@@ -58,6 +58,12 @@ struct T2Params {
     int splits, kb_per_split;
     float* partial;
     int64_t slab, pstride;
+    // SwiGLU pair mode (template parameter SWIGLU): the tile's 256 columns are 128 columns of
+    // G = A Wg (loaded by CTA 0 of the pair) and the SAME 128 columns of U = A Wu (CTA 1, second
+    // tensor map); the epilogue writes y = silu(G) * U [M, N] and, when C / U are given, G and U.
+    void* U;        // nullable, row stride ldc like C
+    void* Y;
+    int64_t ldy;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -140,9 +146,10 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
     Vec<bf16>::load(p, v);
 }
 
-template <typename TC>
+template <typename TC, bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const T2Params p) {
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_b2, const T2Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T2_STAGES * T2_STAGE_BYTES);
@@ -157,7 +164,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t rank = cluster_rank();
     const bool leader = rank == 0;
     const int64_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int64_t tiles_m = (p.M + 2 * T2_BM - 1) / (2 * T2_BM), tiles_n = (p.N + T2_BN - 1) / T2_BN;
+    // columns of the output a tile covers: 256, or 128 of G and of U each in SwiGLU pair mode
+    constexpr int TILE_N = SWIGLU ? T2_BN / 2 : T2_BN;
+    const int64_t tiles_m = (p.M + 2 * T2_BM - 1) / (2 * T2_BM), tiles_n = (p.N + TILE_N - 1) / TILE_N;
     const int64_t n_tiles = tiles_m * tiles_n;
     const int64_t n_work = n_tiles * p.splits;
     const int k_blocks = static_cast<int>((p.K + T2_BK - 1) / T2_BK);
@@ -195,7 +204,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int kb0 = static_cast<int>(w / n_tiles) * p.kb_per_split;
                 const int kb1 = min(k_blocks, kb0 + p.kb_per_split);
                 const int32_t m0 = static_cast<int32_t>((tile / tiles_n) * (2 * T2_BM) + rank * T2_BM);
-                const int32_t n0 = static_cast<int32_t>((tile % tiles_n) * T2_BN + rank * (T2_BN / 2));
+                const int32_t n0 = SWIGLU ? static_cast<int32_t>((tile % tiles_n) * TILE_N)
+                                          : static_cast<int32_t>((tile % tiles_n) * T2_BN + rank * (T2_BN / 2));
+                const CUtensorMap* mb = (SWIGLU && rank == 1) ? &map_b2 : &map_b;
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!wait2(smem_u32(&empty_bar[stage]), phase ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t fb_local = smem_u32(&full_bar[stage]);
@@ -212,11 +223,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             tma_load_2d_pair(sa + c * 8192, &map_a, m0 + c * 64, k0, fb);
                     }
                     if (!p.b_mn_major) {
-                        tma_load_2d_pair(sb, &map_b, k0, n0, fb);                 // box 64(k) x 128(n)
+                        tma_load_2d_pair(sb, mb, k0, n0, fb);                     // box 64(k) x 128(n)
                     } else {
 #pragma unroll
                         for (int c = 0; c < (T2_BN / 2) / 64; ++c)                // boxes 64(n) x 64(k)
-                            tma_load_2d_pair(sb + c * 8192, &map_b, n0 + c * 64, k0, fb);
+                            tma_load_2d_pair(sb + c * 8192, mb, n0 + c * 64, k0, fb);
                     }
                     if (++stage == T2_STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -267,7 +278,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         bool ok = true;
         for (int64_t w = pair; w < n_work && ok; w += n_pairs) {
             const int64_t tile = w % n_tiles;
-            const int64_t m0 = (tile / tiles_n) * (2 * T2_BM) + rank * T2_BM, n0 = (tile % tiles_n) * T2_BN;
+            const int64_t m0 = (tile / tiles_n) * (2 * T2_BM) + rank * T2_BM, n0 = (tile % tiles_n) * TILE_N;
             ok = wait2(smem_u32(&acc_full[acc]), acc_phase, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -275,6 +286,41 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int64_t m = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * T2_BN);
             float* part = p.splits > 1 ? p.partial + (w / n_tiles) * p.slab + m * p.pstride : nullptr;
+            if (SWIGLU) {
+                // columns 0..127 of the accumulator are G, 128..255 the same columns of U. G and U are
+                // rounded to the storage type first and y is formed from the rounded values with the
+                // arithmetic of the stand-alone SwiGLU kernel, so y has the bits the separate
+                // GEMM + GEMM + SwiGLU sequence produces, whether or not G and U are also stored.
+                TC* Gout = static_cast<TC*>(p.C);
+                TC* Uout = static_cast<TC*>(p.U);
+                TC* Yout = static_cast<TC*>(p.Y);
+#pragma unroll 1
+                for (int ch = 0; ch < TILE_N / 32; ++ch) {
+                    const int64_t c0 = n0 + ch * 32;
+                    if (c0 >= p.N) break;  // uniform across the warp
+                    uint32_t rg[32], ru[32];
+                    tmem_ld32(t_row + static_cast<uint32_t>(ch * 32), rg);
+                    tmem_ld32(t_row + static_cast<uint32_t>(TILE_N + ch * 32), ru);
+                    tmem_wait_ld();
+                    if (m < p.M) {
+#pragma unroll
+                        for (int g8 = 0; g8 < 4; ++g8) {
+                            const int64_t c = c0 + g8 * 8;
+                            if (c >= p.N) break;   // N is a multiple of 8 in this mode
+                            float gv[8], uv[8], yv[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                gv[e] = to_f32(from_f32<TC>(__uint_as_float(rg[g8 * 8 + e])));
+                                uv[e] = to_f32(from_f32<TC>(__uint_as_float(ru[g8 * 8 + e])));
+                                yv[e] = (gv[e] / (1.0f + expf(-gv[e]))) * uv[e];
+                            }
+                            if (Gout) store8<TC>(Gout + m * p.ldc + c, gv);
+                            if (Uout) store8<TC>(Uout + m * p.ldc + c, uv);
+                            store8<TC>(Yout + m * p.ldy + c, yv);
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int ch = 0; ch < T2_BN / 32; ++ch) {
                 const int64_t c0 = n0 + ch * 32;
@@ -348,9 +394,9 @@ typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void
                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-template <typename TC>
-int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, T2Params p, int c_dtype) {
-    auto kern = gemm_tc2_kernel<TC>;
+template <typename TC, bool SWIGLU>
+int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, T2Params p, int c_dtype) {
+    auto kern = gemm_tc2_kernel<TC, SWIGLU>;
     static bool attr_set = false;
     if (!attr_set) {
         PK_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES));
@@ -376,7 +422,8 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, T2Par
         PK_REQUIRE(n > 0, "no CTA pair fits on this GPU");
         max_pairs = n;
     }
-    const int64_t tiles = ((p.M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((p.N + T2_BN - 1) / T2_BN);
+    const int64_t tile_n = SWIGLU ? T2_BN / 2 : T2_BN;
+    const int64_t tiles = ((p.M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((p.N + tile_n - 1) / tile_n);
     // Split-K when the last wave of tiles would leave many SM pairs idle and the k loop is long
     // (weight gradients: a few hundred tiles, tens of thousands of rows): the smallest number of
     // k parts whose work items fill the waves to 95 %, if the caller's workspace holds them.
@@ -389,7 +436,7 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, T2Par
     auto fill = [&](int64_t items) {
         return static_cast<double>(items) / static_cast<double>((items + max_pairs - 1) / max_pairs * max_pairs);
     };
-    if (p.partial != nullptr && k_blocks >= 256 && fill(tiles) < 0.9) {
+    if (!SWIGLU && p.partial != nullptr && k_blocks >= 256 && fill(tiles) < 0.9) {
         for (int sp = 2; sp <= 4; ++sp) {
             if (static_cast<size_t>(sp) * p.slab * sizeof(float) > ws_bytes) break;
             if (fill(tiles * sp) >= 0.95) {
@@ -404,7 +451,7 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, T2Par
     gemm_note_splits(p.splits);
     int64_t pairs = max_pairs;
     if (pairs > tiles * p.splits) pairs = tiles * p.splits;
-    kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, p);
+    kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, mb2, p);
     PK_LAUNCH_CHECK();
     if (p.splits > 1)
         return gemm_splitk_reduce(st, c_dtype, p.partial, p.splits, p.slab, p.pstride, p.M, p.N, p.C, p.ldc, p.accumulate,
@@ -433,8 +480,28 @@ int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int
     p.bias = bias; p.residual = residual; p.ldr = ldr;
     p.accumulate = accumulate;
     p.a_mn_major = a_mn; p.b_mn_major = b_mn;
-    if (c_dtype == PK_F32) return launch2<float>(st, ma, mb, p, c_dtype);
-    return launch2<bf16>(st, ma, mb, p, c_dtype);
+    p.U = nullptr; p.Y = nullptr; p.ldy = 0;
+    if (c_dtype == PK_F32) return launch2<float, false>(st, ma, mb, mb, p, c_dtype);
+    return launch2<bf16, false>(st, ma, mb, mb, p, c_dtype);
+}
+
+// y = silu(A Wg) * (A Wu) in one pass over A (SwiGLU pair mode of the kernel above). Wg, Wu are
+// [K, N] row-major (MN-major operands); G / U (nullable, both or neither) receive the two products.
+int gemm_tc2_swiglu_launch(cudaStream_t st, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* Wg,
+                           int64_t ldg, const void* Wu, int64_t ldu, void* G, void* U, int64_t ldgu, void* Y, int64_t ldy) {
+    CUtensorMap ma, mg, mu;
+    int rc = make_tensor_map(&ma, A, K, M, lda, T2_BK, T2_BM);
+    if (rc != PK_OK) return rc;
+    if ((rc = make_tensor_map(&mg, Wg, N, K, ldg, 64, T2_BK)) != PK_OK) return rc;
+    if ((rc = make_tensor_map(&mu, Wu, N, K, ldu, 64, T2_BK)) != PK_OK) return rc;
+    T2Params p;
+    p.M = M; p.N = N; p.K = K;
+    p.C = G; p.ldc = ldgu;
+    p.bias = nullptr; p.residual = nullptr; p.ldr = 0;
+    p.accumulate = 0;
+    p.a_mn_major = 0; p.b_mn_major = 1;
+    p.U = U; p.Y = Y; p.ldy = ldy;
+    return launch2<bf16, true>(st, ma, mg, mu, p, PK_BF16);
 }
 
 

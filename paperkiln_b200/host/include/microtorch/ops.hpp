@@ -72,6 +72,11 @@ Var attention(const Var& q, const Var& k, const Var& v, size_t n_heads, size_t n
 Var rope_(const Var& x, const std::vector<int>& pos, float theta_base, size_t head_dim, size_t n_rot);
 // silu(gate) .* up in one pass (ops::mul(ops::silu(g), u)).
 Var swiglu(const Var& gate, const Var& up);
+// swiglu(x Wg, x Wu) as ONE node: in bf16 mode both projections and the activation run in one
+// GEMM kernel that reads x once (pk_gemm_swiglu); the two products are kept only when a backward
+// pass will need them, and their gradients are written over them. Same values, bit for bit, as
+// swiglu(linear(x, Wg), linear(x, Wu)); falls back to exactly that where the kernel does not apply.
+Var linear_swiglu(const Var& x, const Var& Wg, const Var& Wu);
 
 }  // namespace ops
 }  // namespace microtorch

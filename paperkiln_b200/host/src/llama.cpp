@@ -69,7 +69,8 @@ Var LlamaBlock::forward(const Var& x, const std::vector<int>& pos, size_t seq_le
     Var x1 = o_proj->forward_residual(a, x);  // x + attn
     // ---- SwiGLU FFN sublayer
     Var h2 = ops::rmsnorm(x1, ln2_w);
-    Var f = ops::swiglu(gate_proj->forward(h2), up_proj->forward(h2));
+    Var f = (gate_proj->W && up_proj->W) ? ops::linear_swiglu(h2, gate_proj->W, up_proj->W)
+                                         : ops::swiglu(gate_proj->forward(h2), up_proj->forward(h2));
     return down_proj->forward_residual(f, x1);  // x1 + ffn
 }
 

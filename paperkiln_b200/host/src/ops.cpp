@@ -448,6 +448,41 @@ Var swiglu(const Var& gate, const Var& up) {
     });
 }
 
+Var linear_swiglu(const Var& x, const Var& Wg, const Var& Wu) {
+    if (x->data.cols() != Wg->data.rows() || x->data.cols() != Wu->data.rows())
+        throw std::runtime_error("matmul: inner dimensions disagree");
+    same_shape(Wg, Wu, "swiglu");
+    const size_t R = x->data.rows(), F = Wg->data.cols();
+    const bool want = grad_enabled() && (x->requires_grad || Wg->requires_grad || Wu->requires_grad);
+    if (cdt() != DType::BF16) return swiglu(linear(x, Wg), linear(x, Wu));
+    const Tensor& xt = x->compute();
+    const Tensor& gw = Wg->compute();
+    const Tensor& uw = Wu->compute();
+    Tensor y = new_act(R, F), G, U;
+    if (want) {
+        G = new_act(R, F);
+        U = new_act(R, F);
+    }
+    const int rc = pk_gemm_swiglu(S(), i64(R), i64(F), i64(xt.cols()), xt.ptr(), i64(xt.ld()), gw.ptr(), i64(gw.ld()), uw.ptr(),
+                                  i64(uw.ld()), want ? G.ptr() : nullptr, want ? U.ptr() : nullptr, i64(F), y.ptr(), i64(F));
+    if (rc == PK_ERR_UNSUPPORTED) return swiglu(linear(x, Wg), linear(x, Wu));
+    check(rc, "pk_gemm_swiglu");
+    return record(std::move(y), {x, Wg, Wu}, [G, U](Variable* self) {
+        const Var& x = self->parents[0];
+        const Var& Wg = self->parents[1];
+        const Var& Wu = self->parents[2];
+        Tensor g = grad_of(self);
+        // G and U belong to this node alone: their gradients take their place
+        check(pk_swiglu_bwd(S(), G.dt(), g.ptr(), G.ptr(), U.ptr(), G.ptr(), U.ptr(), i64(G.numel())), "pk_swiglu_bwd");
+        if (Wg->requires_grad) gemm_to_grad(Wg, x->compute(), true, G, false);   // dWg = x^T dG
+        if (Wu->requires_grad) gemm_to_grad(Wu, x->compute(), true, U, false);   // dWu = x^T dU
+        if (x->requires_grad) {
+            gemm_to_grad(x, G, false, Wg->compute(), true, /*reuse_data=*/false);   // dx  = dG Wg^T
+            gemm_to_grad(x, U, false, Wu->compute(), true);                          //     + dU Wu^T
+        }
+    });
+}
+
 Var mean(const Var& x) {
     Tensor xf = x->data.device().cast(DType::F32);
     const size_t n = xf.numel();

@@ -869,3 +869,34 @@ def test_bounded_wait_runs_out_and_the_library_carries_on(pk):
     pkt.check(pk.pk_device_sync())
     pkt.check(pk.pk_kernel_status(ctypes.byref(all_st), 1))
     assert all_st.value == 0
+
+
+@pytest.mark.parametrize("shape", [(300, 128, 64), (1024, 4864, 896), (2048, 8192, 2048), (515, 136, 72)])
+def test_gemm_swiglu_equals_the_three_separate_calls(pk, shape):
+    """y = silu(x Wg) .* (x Wu) from the one-pass kernel has the bits of pk_gemm + pk_gemm +
+    pk_swiglu_fwd, with or without G and U being stored (src/llama.cpp:55-58 of the reference is the
+    composition it replaces)."""
+    M, N, K = shape
+    x = rnd(M, K, seed=1, dtype=torch.bfloat16)
+    Wg = rnd(K, N, seed=2, lo=-0.1, hi=0.1, dtype=torch.bfloat16)
+    Wu = rnd(K, N, seed=3, lo=-0.1, hi=0.1, dtype=torch.bfloat16)
+    G_ref, U_ref = pkt.gemm(x, Wg), pkt.gemm(x, Wu)
+    y_ref = torch.empty_like(G_ref)
+    pkt.check(pk.pk_swiglu_fwd(stream(), BF16, ptr(G_ref), ptr(U_ref), ptr(y_ref), M * N))
+    for keep in (True, False):
+        G = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda") if keep else None
+        U = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda") if keep else None
+        y = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+        pkt.check(pk.pk_gemm_swiglu(stream(), M, N, K, ptr(x), K, ptr(Wg), N, ptr(Wu), N, ptr(G), ptr(U), N, ptr(y), N),
+                  "pk_gemm_swiglu")
+        assert pk.pk_gemm_last_path() == 3
+        assert torch.equal(y, y_ref), f"y differs (keep={keep}): max {(y.float() - y_ref.float()).abs().max().item():.3e}"
+        if keep:
+            assert torch.equal(G, G_ref) and torch.equal(U, U_ref)
+    gf, uf = G_ref.float(), U_ref.float()
+    close(y_ref, gf / (1 + torch.exp(-gf)) * uf, 1e-2, 2 ** -7)
+    st = ctypes.c_int(0)
+    pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
+    assert st.value == 0
+    # shapes the kernel does not take are reported, not mangled
+    assert pk.pk_gemm_swiglu(stream(), 64, N, K, ptr(x), K, ptr(Wg), N, ptr(Wu), N, None, None, N, ptr(y), N) == 3
