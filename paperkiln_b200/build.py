@@ -110,8 +110,8 @@ def build_host(verbose: bool = False, force: bool = False) -> Path:
     for src in sorted((HOST / "examples").glob("*.cpp")):
         exe = PKG / src.stem
         if force or not _newer(exe, [src, lib, *headers]):
-            _run([cxx, "-O2", "-std=c++17", "-I", INCLUDE, src, "-o", exe, "-L", PKG, "-lmicrotorch", "-lpk", "-pthread",
-                  "-Wl,-rpath,$ORIGIN"], verbose)
+            _run([cxx, "-O2", "-std=c++17", "-I", INCLUDE, "-I", HOST / "include", src, "-o", exe, "-L", PKG, "-lmicrotorch",
+                  "-lpk", "-pthread", "-Wl,-rpath,$ORIGIN"], verbose)
     return lib
 
 

@@ -72,6 +72,16 @@ def tensor_stats(stats, prefix, v):
     stats[f"{prefix}.sample"] = strided_sample(v)
 
 
+# Eight optimizer steps on one batch with gradient clipping (the reference's own multi-step device
+# pin, tests/test_step_residency.cpp:142-158, runs 8 steps): per-step losses and the final weights.
+TRAIN_CASES = {
+    "llama_train8": dict(family="llama", vocab=97, d=32, layers=2, heads=4, dff=64, nctx=64, batch=2, seq=16, seed=9,
+                         **{"data-seed": 77}, ckpt=1, steps=8, clip=1.0, lr=0.003),
+    "gpt2_train8": dict(family="gpt2", vocab=97, d=32, layers=2, heads=4, nctx=64, batch=2, seq=16, seed=9,
+                        **{"data-seed": 77}, ckpt=1, steps=8, clip=1.0, lr=0.003),
+}
+
+
 CONFIG1 = dict(family="llama", vocab=4096, d=128, layers=4, heads=4, dff=512, nctx=256, batch=8, seq=256, seed=0,
                **{"data-seed": 0})
 
@@ -131,6 +141,18 @@ def main():
     np.savez_compressed(HERE / "config1_llama_stats.npz", **stats)
     print("config1", f"{(HERE / 'config1_llama_stats.npz').stat().st_size / 1024:.0f} KiB")
     make_reduced()
+    make_train()
+
+
+def make_train():
+    for name, args in TRAIN_CASES.items():
+        with tempfile.TemporaryDirectory() as tmp:
+            info = run_harness("step", args, tmp)
+            arrays = load_dir(Path(tmp))
+            keep = {k: v for k, v in arrays.items() if k in ("ids", "targets", "losses") or k.startswith(("param.", "after."))}
+            keep["meta_json"] = np.frombuffer(json.dumps({"args": args, "result": info}).encode(), dtype=np.uint8)
+            np.savez_compressed(HERE / f"{name}.npz", **keep)
+            print(name, arrays["losses"].ravel(), f"{(HERE / (name + '.npz')).stat().st_size / 1024:.0f} KiB")
 
 
 def make_reduced(only=None):
@@ -150,9 +172,9 @@ def make_reduced(only=None):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) > 1 and sys.argv[1] == "reduced":   # only the reduced bf16-configuration cases
+    if len(sys.argv) > 1 and sys.argv[1] in ("reduced", "train"):   # only one group of cases
         if not HARNESS.exists():
             sys.exit(f"{HARNESS} not found: run `make -C oracle` first")
-        make_reduced(sys.argv[2:])
+        make_reduced(sys.argv[2:]) if sys.argv[1] == "reduced" else make_train()
     else:
         main()
