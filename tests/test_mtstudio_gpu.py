@@ -31,7 +31,11 @@ def test_training_run_emits_the_reference_event_stream(tmp_path, preset, dtype):
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     out = tmp_path / "out"
-    spec = {"name": "r", "arch": {"preset": preset}, "data": {"vocab_cap": 256, "T": 64, "synthetic_tokens": 30000},
+    # a corpus with structure to learn: a cycle of 40 words, so the next word is a function of the current one
+    words = [f"w{i}" for i in range(40)]
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text(" ".join(words[i % 40] for i in range(30000)))
+    spec = {"name": "r", "arch": {"preset": preset}, "data": {"corpus": str(corpus), "vocab_cap": 256, "T": 64},
             "train": {"steps": 12, "lr": 3e-3, "eval_every": 4, "checkpoint_every": 6, "batch": 4, "accum": 2,
                       "checkpoint_activations": True, "dtype": dtype},
             "export": {"formats": ["safetensors", "gguf"]}, "out_dir": str(out)}
@@ -39,12 +43,12 @@ def test_training_run_emits_the_reference_event_stream(tmp_path, preset, dtype):
     kinds = [e["event"] for e in ev]
     assert kinds[0] == "model" and kinds[-1] == "done"
     model = ev[0]
-    assert model["checkpoint_activations"] is True and model["batch"] == 4 and model["accum"] == 2 and model["vocab"] == 256
+    assert model["checkpoint_activations"] is True and model["batch"] == 4 and model["accum"] == 2 and model["vocab"] == 41
     assert model["position"] == ("rope" if preset.startswith("llama") else "learned")
     steps = [e for e in ev if e["event"] == "step"]
     assert [e["step"] for e in steps] == list(range(1, 13))
     assert all(e["loss"] > 0 and e["grad_norm"] > 0 for e in steps)
-    assert steps[-1]["loss"] < steps[0]["loss"]            # a uniform random stream still has a unigram bias to learn
+    assert steps[-1]["loss"] < 0.8 * steps[0]["loss"]
     assert [e["step"] for e in ev if e["event"] == "eval"] == [4, 8, 12]
     exports = {e["format"]: e for e in ev if e["event"] in ("export", "export_skipped")}
     assert Path(exports["safetensors"]["path"]).exists()
