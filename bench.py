@@ -87,6 +87,13 @@ def flops_per_token(w):
     return f_blk, f_attn, f_head
 
 
+def last_projection_flops(w):
+    """FLOPs per token of a block's last projection (down / c_proj). Its value is dead when the
+    block is re-run for the backward pass, so the recompute does not execute it."""
+    d = w["d"]
+    return 2 * d * (4 * d if w["family"] == "gpt2" else w["dff"])
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -158,7 +165,8 @@ def ref_harness_args(w, sample_tokens):
 
 
 def step_flops_per_token(w):
-    """Dense FLOPs one checkpointed training step executes per token (forward + recompute + backward)."""
+    """Dense FLOPs one checkpointed training step of the reference executes per token (forward +
+    full recompute + backward); used to scale the reference's timed sample to the full model."""
     f_blk, f_attn, f_head = flops_per_token(w)
     return w["layers"] * 4 * (f_blk + f_attn) + 3 * f_head
 
@@ -474,10 +482,10 @@ def main():
         # frozen base: the weight-gradient GEMMs of the projections and of the (tied, frozen) head are
         # not executed -- forward + recompute + input gradient for a block, forward + input gradient
         # for the head; attention is as for a dense model. (The rank-16 LoRA products are left out.)
-        step_flops = (L * (3 * f_blk + 4 * f_attn) + 2 * f_head) * tokens_global
+        step_flops = (L * (3 * f_blk + 4 * f_attn - last_projection_flops(w)) + 2 * f_head) * tokens_global
         model_flops = (L * (2 * f_blk + 3 * f_attn) + 2 * f_head) * tokens_global
     else:
-        step_flops = (L * 4 * (f_blk + f_attn) + 3 * f_head) * tokens_global
+        step_flops = (L * (4 * (f_blk + f_attn) - last_projection_flops(w)) + 3 * f_head) * tokens_global
         model_flops = 3 * (L * (f_blk + f_attn) + f_head) * tokens_global
     launches = sum(p["launches"] for p in prof.values())
     # DRAM bytes of one launch of the dominant GEMM shape (the gate / up projection, M x dff x d):
@@ -597,7 +605,7 @@ def run_block(args, w, mt, pk, stream, base, world, rank, torch, np):
     dk = d // H
     f_blk = 2 * (4 * d * d + 3 * d * F)
     f_attn = 4 * (S / 2) * d
-    flops = 3 * (f_blk + f_attn) * R          # recompute (1x) + backward (2x)
+    flops = (3 * (f_blk + f_attn) - 2 * F * d) * R   # recompute (1x, without the dead last projection) + backward (2x)
     g = prof_total["gemm_tc"]
     line = dict(base)
     line["metric"] = "tokens/s through recompute + backward of one checkpointed block"

@@ -44,6 +44,9 @@
 namespace pk {
 
 PK_DEFINE_WAITCTL(gemm_q8)
+#ifdef PK_Q8_DEBUG
+__device__ int g_q8_dbg = 0;
+#endif
 
 namespace {
 
@@ -52,11 +55,18 @@ using namespace tc;
 constexpr int Q8_BM = 128;          // rows per CTA; the pair covers 256
 constexpr int Q8_BN = 256;
 constexpr int Q8_BK = 64;
-constexpr int Q8_THREADS = 448;
+#ifndef Q8_GROUPS_OVERRIDE
+#define Q8_GROUPS_OVERRIDE 1
+#endif
+#ifndef Q8_STAGES_OVERRIDE
+#define Q8_STAGES_OVERRIDE 5
+#endif
 constexpr int Q8_CONV_WARP0 = 6;    // first converter warp
-constexpr int Q8_CONV_WARPS = 8;
+constexpr int Q8_CONV_WARPS = 8;    // converter warps that work on one k slice
+constexpr int Q8_CONV_GROUPS = Q8_GROUPS_OVERRIDE;   // groups of converter warps; group g takes every slice with index % groups == g
+constexpr int Q8_THREADS = (Q8_CONV_WARP0 + Q8_CONV_WARPS * Q8_CONV_GROUPS) * 32;
 constexpr int Q8_CONV_ITERS = 1024 / (Q8_CONV_WARPS * 32);   // 16-byte operand units per thread and k slice (4)
-constexpr int Q8_STAGES = 5;
+constexpr int Q8_STAGES = Q8_STAGES_OVERRIDE;
 constexpr int Q8_A_BYTES = Q8_BM * Q8_BK * 2;          // 16 KiB
 constexpr int Q8_B_BYTES = (Q8_BN / 2) * Q8_BK * 2;    // 16 KiB: this CTA's half of B in bf16
 constexpr int Q8_RAW_BYTES = (Q8_BN / 2) * Q8_BK;      // 8 KiB: the same half as int8
@@ -354,7 +364,12 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp >= Q8_CONV_WARP0) {
         // ------------------------------------------------ converters (both CTAs)
-        const int c = threadIdx.x - Q8_CONV_WARP0 * 32;   // 0..255
+        const int c = (threadIdx.x - Q8_CONV_WARP0 * 32) & (Q8_CONV_WARPS * 32 - 1);   // 0..255
+        const int group = (warp - Q8_CONV_WARP0) / Q8_CONV_WARPS;
+        int turn = 0;   // whose slice this is
+#ifdef PK_Q8_DEBUG
+        const int dbg = g_q8_dbg;
+#endif
         // MN-major (W is [K, N]): thread = (k row r0 + 16 i, 8 columns starting at 8 j), j < 16
         // K-major  (W is [N, K]): thread = (row r0 + 32 i, 8 k values starting at 8 j), j < 8
         const int j = B_MN ? (c & 15) : (c & 7);
@@ -374,8 +389,20 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int64_t w = pair; w < n_tiles && ok; w += n_pairs) {
             const int nb = k_blocks + (lora ? 1 : 0);
             for (int kb = 0; kb < nb; ++kb) {
+                if (Q8_CONV_GROUPS > 1) {
+                    const bool mine = turn == group;
+                    if (++turn == Q8_CONV_GROUPS) turn = 0;
+                    if (!mine) {
+                        if (++stage == Q8_STAGES) { stage = 0; phase ^= 1u; }
+                        continue;
+                    }
+                }
                 if (!waitq(smem_u32(&raw_full[stage]), phase, abort_flag)) { ok = false; break; }
+#ifdef PK_Q8_DEBUG
+                if (kb < k_blocks && dbg != 1) {
+#else
                 if (kb < k_blocks) {
+#endif
                     const uint8_t* raw = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + Q8_B_BYTES + raw_off;
                     uint8_t* dst = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + dst_off;
                     const uint8_t* scl = scale_smem + stage * Q8_SCALE_BYTES + scale_off;
@@ -385,6 +412,9 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const float sc = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(scl + i * row_step * scale_pitch)));
                         *reinterpret_cast<uint4*>(dst + i * row_step * 128) = dequant8(q.x, q.y, sc);
                     }
+#ifdef PK_Q8_DEBUG
+                    if (dbg != 2)
+#endif
                     fence_async_smem();   // generic-proxy writes -> visible to the tensor core's reads
                 }
                 // (the LoRA slice has nothing to convert: the arrival only keeps the barrier's count)
@@ -582,3 +612,10 @@ extern "C" int pk_gemm_q8_lora(void* stream, int c_dtype, int trans_w, int64_t M
     return launch_q8<bf16, false>(st, ma, mw, mxa, ml, p);
 }
 
+#ifdef PK_Q8_DEBUG
+extern "C" int pk_gemm_q8_debug(int mode, int* out) {
+    cudaMemcpyToSymbol(pk::g_q8_dbg, &mode, sizeof(int));
+    if (out) *out = Q8_STAGES * 100 + Q8_CONV_GROUPS;
+    return 0;
+}
+#endif

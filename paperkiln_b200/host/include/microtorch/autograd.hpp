@@ -38,9 +38,15 @@ public:
     Value(const Matrix& m) : host_(m), host_valid_(true) {}              // NOLINT: implicit by design
     Value(Matrix&& m) : host_(std::move(m)), host_valid_(true) {}       // NOLINT
     explicit Value(Tensor t) : dev_(std::move(t)), dev_valid_(true) {}
+    // A [rows, cols] device value whose producer has not run yet: `produce` is called by the first
+    // device() / host() that wants the contents, and never if nobody does. An op uses this for
+    // an output that may turn out to be dead (the last projection of a recomputed segment: its
+    // backward needs the inputs, not the value).
+    static Value deferred(size_t rows, size_t cols, std::function<Tensor()> produce);
+    bool pending() const { return static_cast<bool>(deferred_); }
 
-    size_t rows() const { return dev_valid_ ? dev_.rows() : host_.rows(); }
-    size_t cols() const { return dev_valid_ ? dev_.cols() : host_.cols(); }
+    size_t rows() const { return deferred_ ? def_rows_ : dev_valid_ ? dev_.rows() : host_.rows(); }
+    size_t cols() const { return deferred_ ? def_cols_ : dev_valid_ ? dev_.cols() : host_.cols(); }
     bool empty() const { return rows() == 0; }
 
     // Host view; downloads (and synchronises) when the device copy is newer.
@@ -64,7 +70,7 @@ public:
     void set_device(Tensor t);
     // Call after writing through device() pointers in place.
     void mark_device_modified() { host_valid_ = false; ++version_; }
-    bool on_device() const { return dev_valid_; }
+    bool on_device() const { return dev_valid_ || deferred_; }
     uint64_t version() const { return version_; }
     void reset();
 
@@ -73,7 +79,10 @@ private:
     mutable Matrix host_;
     mutable bool host_valid_ = false;
     mutable bool dev_valid_ = false;
+    mutable std::function<Tensor()> deferred_;
+    size_t def_rows_ = 0, def_cols_ = 0;
     uint64_t version_ = 0;
+    void materialise() const;
 };
 
 class Variable;
@@ -152,6 +161,8 @@ Var checkpoint(const std::function<Var(const Var&)>& fn, const Var& x);
 void backward_from(const Var& root, const Tensor& upstream);
 
 bool grad_enabled();
+// True while a checkpointed segment is being re-run on its private tape during backward.
+bool recomputing();
 class NoGrad {
 public:
     NoGrad();

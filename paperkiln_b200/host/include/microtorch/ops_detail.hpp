@@ -13,6 +13,12 @@ namespace detail {
 // Tape node around `result` unless grad is off or no parent requires it. Null parents
 // are dropped. `bw` reads self->grad and accumulates into self->parents.
 Var record_node(Tensor result, std::vector<Var> parents, std::function<void(Variable*)> bw);
+// Tape node of a projection whose [rows, cols] value `produce` computes. Outside a recomputed
+// segment produce() runs at once; inside one it runs when the first consumer reads the value
+// (Value::deferred), i.e. never for the segment's last projection. `produce` must not depend on
+// buffers that an in-place op rewrites between this call and the first read.
+Var record_projection(size_t rows, size_t cols, std::function<Tensor()> produce, std::vector<Var> parents,
+                      std::function<void(Variable*)> bw);
 // Upstream gradient of a node as a tensor in the compute dtype.
 Tensor upstream(Variable* self);
 // C (+)= op(A).op(B) (+ bias) (+ residual) through pk_gemm.

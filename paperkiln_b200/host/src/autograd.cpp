@@ -17,6 +17,7 @@ size_t live_variables() { return detail::g_live_vars.load(); }
 
 // ---------------------------------------------------------------- Value
 const Matrix& Value::host() const {
+    if (deferred_) materialise();
     if (!host_valid_) {
         if (dev_valid_) {
             host_ = dev_.to_host();
@@ -28,6 +29,22 @@ const Matrix& Value::host() const {
     return host_;
 }
 
+Value Value::deferred(size_t rows, size_t cols, std::function<Tensor()> produce) {
+    Value v;
+    v.deferred_ = std::move(produce);
+    v.def_rows_ = rows;
+    v.def_cols_ = cols;
+    return v;
+}
+
+void Value::materialise() const {
+    std::function<Tensor()> produce = std::move(deferred_);
+    deferred_ = nullptr;
+    dev_ = produce();
+    dev_valid_ = true;
+    host_valid_ = false;
+}
+
 Matrix& Value::mutable_host() {
     (void)host();
     dev_valid_ = false;
@@ -36,6 +53,7 @@ Matrix& Value::mutable_host() {
 }
 
 Value& Value::operator=(const Matrix& m) {
+    deferred_ = nullptr;
     // Keep a device buffer of the same shape as the home of the data (parameters are
     // windows of a flat buffer and must stay there): write through instead of rebinding.
     if (dev_.defined() && dev_.rows() == m.rows() && dev_.cols() == m.cols() && dev_valid_) {
@@ -55,6 +73,7 @@ Value& Value::operator=(const Matrix& m) {
 Value& Value::operator=(Matrix&& m) { return *this = static_cast<const Matrix&>(m); }
 
 void Value::fill(float v) {
+    if (deferred_) materialise();
     if (dev_valid_ && v == 0.0f) {
         dev_.zero_();
         host_valid_ = false;
@@ -66,6 +85,7 @@ void Value::fill(float v) {
 }
 
 const Tensor& Value::device() const {
+    if (deferred_) materialise();
     if (!dev_valid_) {
         if (!host_valid_) throw std::runtime_error("Value::device on an empty value");
         if (dev_.defined() && dev_.rows() == host_.rows() && dev_.cols() == host_.cols()) {
@@ -79,6 +99,7 @@ const Tensor& Value::device() const {
 }
 
 void Value::set_device(Tensor t) {
+    deferred_ = nullptr;
     dev_ = std::move(t);
     dev_valid_ = true;
     host_valid_ = false;
@@ -87,6 +108,7 @@ void Value::set_device(Tensor t) {
 }
 
 void Value::reset() {
+    deferred_ = nullptr;
     dev_ = Tensor();
     host_ = Matrix();
     dev_valid_ = host_valid_ = false;
@@ -195,6 +217,7 @@ void Variable::accumulate(const Matrix& g) {
 namespace {
 
 thread_local bool g_grad_enabled = true;
+thread_local int g_recompute_depth = 0;
 bool g_release_interior = true;
 std::function<void(int)> g_segment_hook;
 int g_segment_counter = 0;
@@ -295,7 +318,15 @@ Var checkpoint(const std::function<Var(const Var&)>& fn, const Var& x) {
         const Var xin = self->parents[0];
         // Recompute on a detached leaf that aliases the stored boundary activation.
         Var x2 = std::make_shared<Variable>(Value(xin->data.device()), true);
-        Var y2 = fn_copy(x2);
+        ++g_recompute_depth;
+        Var y2;
+        try {
+            y2 = fn_copy(x2);
+        } catch (...) {
+            --g_recompute_depth;
+            throw;
+        }
+        --g_recompute_depth;
         if (y2->data.rows() != self->grad.rows() || y2->data.cols() != self->grad.cols())
             throw std::runtime_error("checkpoint: recomputed output shape mismatch");
         y2->accumulate(self->grad.device());
@@ -343,12 +374,13 @@ void zero_grad(const std::vector<Var>& vars) {
 }
 
 bool grad_enabled() { return g_grad_enabled; }
+bool recomputing() { return g_recompute_depth > 0; }
 NoGrad::NoGrad() : prev_(g_grad_enabled) { g_grad_enabled = false; }
 NoGrad::~NoGrad() { g_grad_enabled = prev_; }
 
 namespace autograd {
 bool disposable_input(const Var& v) {
-    return v && v->pending_consumers == 1 && !v->is_leaf() && v->data.on_device() && v->data.device().use_count() == 1 &&
+    return v && v->pending_consumers == 1 && !v->is_leaf() && !v->data.pending() && v->data.on_device() && v->data.device().use_count() == 1 &&
            v->data.device().is_dense() && !v->shadow.defined();
 }
 void set_release_interior(bool on) { g_release_interior = on; }

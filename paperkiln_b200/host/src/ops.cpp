@@ -27,11 +27,11 @@ int64_t i64(size_t v) { return static_cast<int64_t>(v); }
 Tensor new_act(size_t r, size_t c) { return Tensor::empty(r, c, cdt()); }
 
 // Tape node unless grad is off or no input requires it (reference: src/ops.cpp:17-29).
-Var record(Tensor result, std::vector<Var> parents, std::function<void(Variable*)> bw) {
+Var record_value(Value result, std::vector<Var> parents, std::function<void(Variable*)> bw) {
     bool needs = false;
     if (grad_enabled())
         for (const auto& p : parents) needs = needs || (p && p->requires_grad);
-    Var out = std::make_shared<Variable>(Value(std::move(result)), needs);
+    Var out = std::make_shared<Variable>(std::move(result), needs);
     if (needs) {
         parents.erase(std::remove(parents.begin(), parents.end(), nullptr), parents.end());
         out->parents = std::move(parents);
@@ -39,6 +39,10 @@ Var record(Tensor result, std::vector<Var> parents, std::function<void(Variable*
         out->backward_fn = [self, bw]() { bw(self); };
     }
     return out;
+}
+
+Var record(Tensor result, std::vector<Var> parents, std::function<void(Variable*)> bw) {
+    return record_value(Value(std::move(result)), std::move(parents), std::move(bw));
 }
 
 // Upstream gradient of a node in the compute dtype.
@@ -312,6 +316,15 @@ namespace detail {
 Var record_node(Tensor result, std::vector<Var> parents, std::function<void(Variable*)> bw) {
     return record(std::move(result), std::move(parents), std::move(bw));
 }
+Var record_projection(size_t rows, size_t cols, std::function<Tensor()> produce, std::vector<Var> parents,
+                      std::function<void(Variable*)> bw) {
+    // While a checkpointed segment is re-run for its backward pass, a projection's value is
+    // produced when its first consumer asks for it. The segment's last projection has none
+    // (its closure reads x, W and the upstream gradient), so its GEMM is not run a second time.
+    if (grad_enabled() && recomputing())
+        return record_value(Value::deferred(rows, cols, std::move(produce)), std::move(parents), std::move(bw));
+    return record(produce(), std::move(parents), std::move(bw));
+}
 Tensor upstream(Variable* self) { return grad_of(self); }
 void gemm_raw(const Tensor& A, bool ta, const Tensor& B, bool tb, Tensor& C, bool accumulate, const float* bias,
               const Tensor* residual) {
@@ -353,19 +366,22 @@ Var linear(const Var& x, const Var& W, const Var& bias, const Var& residual, boo
         throw std::runtime_error("add_bias: bias must be [1, cols(x)]");
     if (residual && (residual->data.rows() != x->data.rows() || residual->data.cols() != out))
         throw std::runtime_error("linear: residual shape mismatch");
-    const Tensor& xt = x->compute();
-    const Tensor& wt = W->compute();
-    // A row stride that is a multiple of 16 bytes keeps ragged widths (a 50257-wide
-    // vocabulary) on the tensor-core kernel.
-    Tensor y = (cdt() == DType::BF16 && out % 8 != 0) ? Tensor::empty_strided(xt.rows(), out, (out + 7) / 8 * 8, cdt())
-                                                      : new_act(xt.rows(), out);
-    Tensor bt;
-    if (bias) bt = f32_of(bias);
-    Tensor rt;
-    if (residual) rt = residual->compute();
-    gemm(xt, false, wt, transposed_w, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
+    auto produce = [x, W, bias, residual, transposed_w, out]() {
+        const Tensor& xt = x->compute();
+        const Tensor& wt = W->compute();
+        // A row stride that is a multiple of 16 bytes keeps ragged widths (a 50257-wide
+        // vocabulary) on the tensor-core kernel.
+        Tensor y = (cdt() == DType::BF16 && out % 8 != 0) ? Tensor::empty_strided(xt.rows(), out, (out + 7) / 8 * 8, cdt())
+                                                          : new_act(xt.rows(), out);
+        Tensor bt;
+        if (bias) bt = f32_of(bias);
+        Tensor rt;
+        if (residual) rt = residual->compute();
+        gemm(xt, false, wt, transposed_w, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
+        return y;
+    };
     const bool has_bias = bias != nullptr, has_res = residual != nullptr;
-    return record(std::move(y), {x, W, bias, residual}, [transposed_w, has_bias, has_res](Variable* self) {
+    return detail::record_projection(x->data.rows(), out, produce, {x, W, bias, residual}, [transposed_w, has_bias, has_res](Variable* self) {
         const Var& x = self->parents[0];
         const Var& W = self->parents[1];
         Tensor g = grad_of(self);

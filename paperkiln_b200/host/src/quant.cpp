@@ -189,18 +189,21 @@ void check_linear_shapes(const Var& x, const Q8Weight& W, const Var& bias, const
 
 Var q8_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var& bias, const Var& residual) {
     check_linear_shapes(x, *Wq, bias, residual);
-    const DType cd = device::compute_dtype();
-    const Tensor& xt = x->compute();
-    Tensor y = Tensor::empty(xt.rows(), Wq->cols, cd);
-    Tensor bt, rt;
-    if (bias) bt = bias->data.device().cast(DType::F32);
-    if (residual) rt = residual->compute();
-    if (!q8_gemm_fused(xt, *Wq, false, nullptr, nullptr, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr)) {
-        Tensor w = Wq->dequantize(cd);  // expanded for this GEMM only
-        detail::gemm_raw(xt, false, w, false, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
-    }
+    auto produce = [x, Wq, bias, residual]() {
+        const DType cd = device::compute_dtype();
+        const Tensor& xt = x->compute();
+        Tensor y = Tensor::empty(xt.rows(), Wq->cols, cd);
+        Tensor bt, rt;
+        if (bias) bt = bias->data.device().cast(DType::F32);
+        if (residual) rt = residual->compute();
+        if (!q8_gemm_fused(xt, *Wq, false, nullptr, nullptr, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr)) {
+            Tensor w = Wq->dequantize(cd);  // expanded for this GEMM only
+            detail::gemm_raw(xt, false, w, false, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
+        }
+        return y;
+    };
     const bool has_bias = bias != nullptr, has_res = residual != nullptr;
-    return detail::record_node(std::move(y), {x, bias, residual}, [Wq, has_bias, has_res](Variable* self) {
+    return detail::record_projection(x->data.rows(), Wq->cols, produce, {x, bias, residual}, [Wq, has_bias, has_res](Variable* self) {
         const Var& x = self->parents[0];
         Tensor g = detail::upstream(self);
         if (x->requires_grad) q8_dx_into_grad(x, g, *Wq, nullptr, nullptr);
@@ -217,22 +220,27 @@ Var q8_lora_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var&
     const DType cd = device::compute_dtype();
     const Tensor& xt = x->compute();
     const Tensor& at = A->compute();
-    const Tensor& bt_l = B->compute();
     // the rank-r intermediate, scaled: XA = scaling (x A)
     Tensor xa = Tensor::empty(xt.rows(), r, cd);
     detail::gemm_raw(xt, false, at, false, xa, false);
     check(pk_scale(device::stream(), xa.dt(), xa.ptr(), scaling, xa.ptr(), i64(xa.numel())), "pk_scale");
-    Tensor y = Tensor::empty(xt.rows(), Wq->cols, cd);
-    Tensor bt, rt;
-    if (bias) bt = bias->data.device().cast(DType::F32);
-    if (residual) rt = residual->compute();
-    if (!q8_gemm_fused(xt, *Wq, false, &xa, &bt_l, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr)) {
-        Tensor w = Wq->dequantize(cd);
-        detail::gemm_raw(xt, false, w, false, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
-        detail::gemm_raw(xa, false, bt_l, false, y, true);
-    }
+    auto produce = [x, Wq, B, xa, bias, residual]() {
+        const DType cd = device::compute_dtype();
+        const Tensor& xt = x->compute();
+        const Tensor& bt_l = B->compute();
+        Tensor y = Tensor::empty(xt.rows(), Wq->cols, cd);
+        Tensor bt, rt;
+        if (bias) bt = bias->data.device().cast(DType::F32);
+        if (residual) rt = residual->compute();
+        if (!q8_gemm_fused(xt, *Wq, false, &xa, &bt_l, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr)) {
+            Tensor w = Wq->dequantize(cd);
+            detail::gemm_raw(xt, false, w, false, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
+            detail::gemm_raw(xa, false, bt_l, false, y, true);
+        }
+        return y;
+    };
     const bool has_bias = bias != nullptr, has_res = residual != nullptr;
-    return detail::record_node(std::move(y), {x, A, B, bias, residual}, [Wq, xa, scaling, has_bias, has_res](Variable* self) {
+    return detail::record_projection(x->data.rows(), Wq->cols, produce, {x, A, B, bias, residual}, [Wq, xa, scaling, has_bias, has_res](Variable* self) {
         const Var& x = self->parents[0];
         const Var& A = self->parents[1];
         const Var& B = self->parents[2];
