@@ -488,15 +488,15 @@ def main():
         step_flops = (L * (4 * (f_blk + f_attn) - last_projection_flops(w)) + 3 * f_head) * tokens_global
         model_flops = 3 * (L * (f_blk + f_attn) + f_head) * tokens_global
     launches = sum(p["launches"] for p in prof.values())
-    # DRAM bytes of one launch of the dominant GEMM shape (the gate / up projection, M x dff x d):
-    # dram__bytes_read + dram__bytes_write of an ncu capture at M = 16384 (113.1 + 231.1 MB for
+    # DRAM bytes of one launch of the dominant GEMM shape (the down projection, M x d x dff):
+    # dram__bytes_read + dram__bytes_write of an ncu capture at M = 16384 (575.3 + 60.0 MB for
     # d 2048, dff 8192), scaled to this run's rows per GPU -- traffic grows in proportion to M.
-    # Only quoted for the shape that was captured.
     traffic, traffic_note = None, None
     if args.workload == "c4":
-        traffic = 344.2e6 * (n_local / max(1, args.accum) / 16384.0)
-        traffic_note = ("gate/up projection launch (rows x 8192 x 2048): ncu capture at 16384 rows scaled by rows; "
-                        "algorithmic bytes of that launch are 369 MB per 16384 rows")
+        traffic = 635.3e6 * (n_local / max(1, args.accum) / 16384.0)
+        traffic_note = ("down projection launch (rows x 2048 x 8192): ncu capture at 16384 rows scaled by rows; "
+                        "algorithmic bytes of that launch are 369 MB per 16384 rows (the A operand is read about "
+                        "twice: a row block's 8192-deep slab does not stay in L2 between its tiles; tensor pipe 90 % busy)")
     line = dict(base)
     line["value"] = tokens_global / (res_ms / args.steps * 1e-3)
     line["ms_per_step"] = res_ms / args.steps

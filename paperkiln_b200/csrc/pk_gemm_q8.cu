@@ -18,17 +18,21 @@
 //                lanes copy the slice's fp16 scales into shared memory with cp.async, whose
 //                completion is counted on the same "raw" barrier
 //   warp 1       tensor-memory allocation; in the leader one thread issues the MMAs
-//   warps 2..5   epilogue (tcgen05.ld, bias / residual / accumulate, stores)
+//   warps 2..5   epilogue: rows leave through shared-memory boxes and TMA stores, what is added to
+//                them (residual, C) arrives by TMA (pk_gemm_epilogue.cuh); direct stores otherwise
 //   warps 6..13  converters: int8 + scale -> swizzled bf16, fence.proxy.async, then one arrival per
 //                warp on the LEADER's "full" barrier, which therefore completes when the A bytes of
 //                both CTAs have landed and all 16 converter warps of the pair are done: the issuer
 //                waits once per k slice
-// Measured and not kept (16384 x 4864 x 896, TFLOP/s; this form 830, the bf16 pair kernel on an
-// already expanded weight 1125): two converter groups on alternate k slices 830 (the converters'
-// latency is not the limit); converters loading the int8 slice from global memory into registers
-// one slice ahead instead of staging it by TMA 723 (the loads stall the converter warps more than
-// the 16 KB of shared-memory traffic per slice they save); a cluster-scope release on every
-// converter arrival 495; a second barrier for the issuer to wait on 340.
+// Measured (16384 x 4864 x 896, TFLOP/s): with row-per-thread stores in the epilogue 836, with
+// the staged epilogue 952 (the bf16 pair kernel on an already expanded weight: 1201 -> 1413); the
+// k loop of this shape is only 14 slices, so a tile's epilogue is as long as its MMAs. With the
+// converters idle (arrivals only) the old form reached 1005, so converting costs about a sixth.
+// Four or five ring stages, and eight or sixteen converter warps (two groups on alternate k
+// slices), made no difference; eight epilogue warps were slower (781). Not kept earlier:
+// converters loading the int8 slice from global memory into registers instead of staging it by
+// TMA 723; a cluster-scope release on every converter arrival 495; a second barrier for the
+// issuer to wait on 340.
 // Both layouts of W are served: trans_w = 0 (W is [K, N], the operand is MN-major; forward) and
 // trans_w = 1 (W is [N, K], K-major; input gradient). The k order is fixed and the products are
 // the ones a bf16 GEMM over the expanded weight would form, so the result equals
@@ -40,13 +44,11 @@
 
 #include "pk_common.cuh"
 #include "pk_tc.cuh"
+#include "pk_gemm_epilogue.cuh"
 
 namespace pk {
 
 PK_DEFINE_WAITCTL(gemm_q8)
-#ifdef PK_Q8_DEBUG
-__device__ int g_q8_dbg = 0;
-#endif
 
 namespace {
 
@@ -55,24 +57,19 @@ using namespace tc;
 constexpr int Q8_BM = 128;          // rows per CTA; the pair covers 256
 constexpr int Q8_BN = 256;
 constexpr int Q8_BK = 64;
-#ifndef Q8_GROUPS_OVERRIDE
-#define Q8_GROUPS_OVERRIDE 1
-#endif
-#ifndef Q8_STAGES_OVERRIDE
-#define Q8_STAGES_OVERRIDE 5
-#endif
 constexpr int Q8_CONV_WARP0 = 6;    // first converter warp
 constexpr int Q8_CONV_WARPS = 8;    // converter warps that work on one k slice
-constexpr int Q8_CONV_GROUPS = Q8_GROUPS_OVERRIDE;   // groups of converter warps; group g takes every slice with index % groups == g
-constexpr int Q8_THREADS = (Q8_CONV_WARP0 + Q8_CONV_WARPS * Q8_CONV_GROUPS) * 32;
+constexpr int Q8_THREADS = (Q8_CONV_WARP0 + Q8_CONV_WARPS) * 32;
 constexpr int Q8_CONV_ITERS = 1024 / (Q8_CONV_WARPS * 32);   // 16-byte operand units per thread and k slice (4)
-constexpr int Q8_STAGES = Q8_STAGES_OVERRIDE;
+constexpr int Q8_STAGES = 4;
 constexpr int Q8_A_BYTES = Q8_BM * Q8_BK * 2;          // 16 KiB
 constexpr int Q8_B_BYTES = (Q8_BN / 2) * Q8_BK * 2;    // 16 KiB: this CTA's half of B in bf16
 constexpr int Q8_RAW_BYTES = (Q8_BN / 2) * Q8_BK;      // 8 KiB: the same half as int8
 constexpr int Q8_STAGE_BYTES = Q8_A_BYTES + Q8_B_BYTES + Q8_RAW_BYTES;
 constexpr int Q8_SCALE_BYTES = 512;                    // fp16 scales of one half slice: 64 x 4 or 128 x 2
-constexpr int Q8_SMEM_BYTES = Q8_STAGES * (Q8_STAGE_BYTES + Q8_SCALE_BYTES) + 1024 + 512;
+constexpr int Q8_EPI_BOXES = 4;                        // per epilogue warp: boxes of 32 rows x 64 bytes (pk_gemm_epilogue.cuh)
+constexpr int Q8_EPI_BYTES = 4 * Q8_EPI_BOXES * EPI_BOX_BYTES;
+constexpr int Q8_SMEM_BYTES = Q8_STAGES * (Q8_STAGE_BYTES + Q8_SCALE_BYTES) + Q8_EPI_BYTES + 1024 + 512;
 
 struct Q8Params {
     int64_t M, N, K;
@@ -85,6 +82,7 @@ struct Q8Params {
     const __half* scales;   // [rows of W, cols of W / 32]
     int64_t scale_ld;       // cols of W / 32
     int lora_ksteps;        // ceil(r / 16); 0: no LoRA slice
+    int tma_out;            // 1: output through shared-memory staging and TMA stores (map_c, map_r)
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -207,18 +205,21 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w0, uint32_t w1, float s) {
 template <typename TC, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Q8_THREADS, 1)
 gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               const __grid_constant__ CUtensorMap map_xa, const __grid_constant__ CUtensorMap map_l, const Q8Params p) {
+               const __grid_constant__ CUtensorMap map_xa, const __grid_constant__ CUtensorMap map_l,
+               const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_r, const Q8Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* scale_smem = smem + Q8_STAGES * Q8_STAGE_BYTES;   // [STAGES][Q8_SCALE_BYTES]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(scale_smem + Q8_STAGES * Q8_SCALE_BYTES);
+    uint8_t* epi_smem = scale_smem + Q8_STAGES * Q8_SCALE_BYTES;   // [4 warps][EPI_BOXES][2048]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Q8_EPI_BYTES);
     uint64_t* full_bar = bars;                        // [STAGES]  leader: TMA bytes of A (and of the LoRA slice) of both
                                                       //           CTAs + the 16 converter warps of the pair
     uint64_t* empty_bar = bars + Q8_STAGES;           // [STAGES]  per CTA, both signalled by the leader's commits
     uint64_t* raw_full = bars + 2 * Q8_STAGES;        // [STAGES]  per CTA: its int8 half slice and its scales have landed
     uint64_t* acc_full = bars + 3 * Q8_STAGES;        // [2]       per CTA, both signalled by the leader
     uint64_t* acc_empty = bars + 3 * Q8_STAGES + 2;   // [2]       leader: 8 epilogue warps of the pair
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * Q8_STAGES + 4);
+    uint64_t* in_bar = bars + 3 * Q8_STAGES + 4;      // [4 warps][EPI_BOXES] per CTA: residual / C box has landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + 4 * Q8_EPI_BOXES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -240,6 +241,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(smem_u32(&acc_full[a]), 1);
             mbar_init(smem_u32(&acc_empty[a]), 8);
         }
+        for (int b = 0; b < 4 * Q8_EPI_BOXES; ++b) mbar_init(smem_u32(&in_bar[b]), 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -364,12 +366,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     } else if (warp >= Q8_CONV_WARP0) {
         // ------------------------------------------------ converters (both CTAs)
-        const int c = (threadIdx.x - Q8_CONV_WARP0 * 32) & (Q8_CONV_WARPS * 32 - 1);   // 0..255
-        const int group = (warp - Q8_CONV_WARP0) / Q8_CONV_WARPS;
-        int turn = 0;   // whose slice this is
-#ifdef PK_Q8_DEBUG
-        const int dbg = g_q8_dbg;
-#endif
+        const int c = threadIdx.x - Q8_CONV_WARP0 * 32;   // 0..255
         // MN-major (W is [K, N]): thread = (k row r0 + 16 i, 8 columns starting at 8 j), j < 16
         // K-major  (W is [N, K]): thread = (row r0 + 32 i, 8 k values starting at 8 j), j < 8
         const int j = B_MN ? (c & 15) : (c & 7);
@@ -389,20 +386,8 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int64_t w = pair; w < n_tiles && ok; w += n_pairs) {
             const int nb = k_blocks + (lora ? 1 : 0);
             for (int kb = 0; kb < nb; ++kb) {
-                if (Q8_CONV_GROUPS > 1) {
-                    const bool mine = turn == group;
-                    if (++turn == Q8_CONV_GROUPS) turn = 0;
-                    if (!mine) {
-                        if (++stage == Q8_STAGES) { stage = 0; phase ^= 1u; }
-                        continue;
-                    }
-                }
                 if (!waitq(smem_u32(&raw_full[stage]), phase, abort_flag)) { ok = false; break; }
-#ifdef PK_Q8_DEBUG
-                if (kb < k_blocks && dbg != 1) {
-#else
                 if (kb < k_blocks) {
-#endif
                     const uint8_t* raw = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + Q8_B_BYTES + raw_off;
                     uint8_t* dst = smem + stage * Q8_STAGE_BYTES + Q8_A_BYTES + dst_off;
                     const uint8_t* scl = scale_smem + stage * Q8_SCALE_BYTES + scale_off;
@@ -412,9 +397,6 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         const float sc = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(scl + i * row_step * scale_pitch)));
                         *reinterpret_cast<uint4*>(dst + i * row_step * 128) = dequant8(q.x, q.y, sc);
                     }
-#ifdef PK_Q8_DEBUG
-                    if (dbg != 2)
-#endif
                     fence_async_smem();   // generic-proxy writes -> visible to the tensor core's reads
                 }
                 // (the LoRA slice has nothing to convert: the arrival only keeps the barrier's count)
@@ -430,17 +412,32 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t acc_phase = 0;
         TC* C = static_cast<TC*>(p.C);
         const TC* Rsd = static_cast<const TC*>(p.residual);
+        StagedOut out;   // staged form of the output (p.tma_out): boxes, barriers and maps of this warp
+        out.boxes = epi_smem + (warp - 2) * (Q8_EPI_BOXES * EPI_BOX_BYTES);
+        out.in_bar = in_bar + (warp - 2) * Q8_EPI_BOXES;
+        out.out = &map_c;
+        out.in = Rsd != nullptr ? &map_r : (p.accumulate ? &map_c : nullptr);
+        out.bias = p.bias;
+        out.N = p.N;
+        out.slab = -1;
+        out.uc = 0;
         bool ok = true;
         for (int64_t w = pair; w < n_tiles && ok; w += n_pairs) {
             const int64_t m0 = (w / tiles_n) * (2 * Q8_BM) + rank * Q8_BM, n0 = (w % tiles_n) * Q8_BN;
-            ok = waitq(smem_u32(&acc_full[acc]), acc_phase, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            fence_after();
             const int64_t m = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * Q8_BN);
+            if (p.tma_out) {
+                ok = staged_epilogue<TC, Q8_BN, Q8_EPI_BOXES>(out, n0, static_cast<int32_t>(m0 + quad * 32), t_row,
+                                                              smem_u32(&acc_full[acc]), acc_phase, abort_flag, &g_gemm_q8_ctl, lane);
+                if (!ok) break;
+            } else {
+                ok = waitq(smem_u32(&acc_full[acc]), acc_phase, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fence_after();
+            }
 #pragma unroll 1
-            for (int ch = 0; ch < Q8_BN / 32; ++ch) {
+            for (int ch = 0; ch < (p.tma_out ? 0 : Q8_BN / 32); ++ch) {
                 const int64_t c0 = n0 + ch * 32;
                 if (c0 >= p.N) break;  // uniform across the warp
                 uint32_t r[32];
@@ -483,6 +480,7 @@ gemm_q8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (acc == 0) acc_phase ^= 1u;
         }
     }
+    if (warp >= 2 && warp < Q8_CONV_WARP0 && lane == 0) bulk_wait_all();   // this thread's TMA stores are complete
     fence_before();
     __syncthreads();
     cluster_sync_all();   // no CTA leaves while the other may still signal its barriers or read its shared memory
@@ -528,17 +526,31 @@ int max_pairs_of(int* out) {
     return PK_OK;
 }
 
+
 template <typename TC, bool B_MN>
 int launch_q8(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mxa, const CUtensorMap& ml,
-              const Q8Params& p) {
+              Q8Params p) {
     auto kern = gemm_q8_kernel<TC, B_MN>;
+    // staged output (pk_gemm_epilogue.cuh) when C, the residual and the bias can be reached in 16-byte groups
+    constexpr int64_t PER16 = 16 / static_cast<int64_t>(sizeof(TC));
+    const bool reads = p.bias != nullptr || p.residual != nullptr || p.accumulate != 0;
+    p.tma_out = aligned16(p.C) && (p.ldc % PER16) == 0 && !(p.residual != nullptr && p.accumulate != 0) &&
+                (p.residual == nullptr || (aligned16(p.residual) && (p.ldr % PER16) == 0)) &&
+                (p.bias == nullptr || aligned16(p.bias)) && (p.N % PER16 == 0 || !reads);
+    CUtensorMap mc = ma, mr = ma;
+    if (p.tma_out) {
+        int rc = make_tensor_map_out(&mc, p.C, static_cast<int>(sizeof(TC)), p.N, p.M, p.ldc, 32);
+        if (rc == PK_OK && p.residual != nullptr)
+            rc = make_tensor_map_out(&mr, p.residual, static_cast<int>(sizeof(TC)), p.N, p.M, p.ldr, 32);
+        if (rc != PK_OK) return rc;
+    }
     int max_pairs = 0;
     const int rc = max_pairs_of<TC, B_MN>(&max_pairs);
     if (rc != PK_OK) return rc;
     const int64_t tiles = ((p.M + 2 * Q8_BM - 1) / (2 * Q8_BM)) * ((p.N + Q8_BN - 1) / Q8_BN);
     int64_t pairs = max_pairs;
     if (pairs > tiles) pairs = tiles;
-    kern<<<static_cast<unsigned>(2 * pairs), Q8_THREADS, Q8_SMEM_BYTES, st>>>(ma, mw, mxa, ml, p);
+    kern<<<static_cast<unsigned>(2 * pairs), Q8_THREADS, Q8_SMEM_BYTES, st>>>(ma, mw, mxa, ml, mc, mr, p);
     PK_LAUNCH_CHECK();
     return PK_OK;
 }
@@ -611,11 +623,3 @@ extern "C" int pk_gemm_q8_lora(void* stream, int c_dtype, int trans_w, int64_t M
     if (c_dtype == PK_F32) return launch_q8<float, false>(st, ma, mw, mxa, ml, p);
     return launch_q8<bf16, false>(st, ma, mw, mxa, ml, p);
 }
-
-#ifdef PK_Q8_DEBUG
-extern "C" int pk_gemm_q8_debug(int mode, int* out) {
-    cudaMemcpyToSymbol(pk::g_q8_dbg, &mode, sizeof(int));
-    if (out) *out = Q8_STAGES * 100 + Q8_CONV_GROUPS;
-    return 0;
-}
-#endif

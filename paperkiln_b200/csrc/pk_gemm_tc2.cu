@@ -25,6 +25,7 @@
 
 #include "pk_common.cuh"
 #include "pk_tc.cuh"
+#include "pk_gemm_epilogue.cuh"
 
 namespace pk {
 
@@ -42,7 +43,9 @@ constexpr int T2_STAGES = 6;
 constexpr int T2_A_BYTES = T2_BM * T2_BK * 2;          // 16 KiB
 constexpr int T2_B_BYTES = (T2_BN / 2) * T2_BK * 2;    // 16 KiB: this CTA's half of B
 constexpr int T2_STAGE_BYTES = T2_A_BYTES + T2_B_BYTES;
-constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
+constexpr int T2_EPI_BOXES = 4;              // per epilogue warp: boxes of 32 rows x 64 bytes for TMA loads / stores of the output
+constexpr int T2_EPI_BYTES = 4 * T2_EPI_BOXES * 2048;
+constexpr int T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + T2_EPI_BYTES + 1024 + 512;
 
 struct T2Params {
     int64_t M, N, K;
@@ -64,6 +67,10 @@ struct T2Params {
     void* U;        // nullable, row stride ldc like C
     void* Y;
     int64_t ldy;
+    // 1: the output goes through shared-memory staging and TMA stores (map_c; map_u / map_y in
+    // SwiGLU mode), 0: the threads store their rows themselves (unaligned C, ragged N with a
+    // residual or accumulate read)
+    int tma_out;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -149,15 +156,18 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
 template <typename TC, bool SWIGLU>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_b2, const T2Params p) {
+                const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
+                const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_y, const T2Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T2_STAGES * T2_STAGE_BYTES);
+    uint8_t* epi_smem = smem + T2_STAGES * T2_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + T2_EPI_BYTES);
     uint64_t* full_bar = bars;                        // [STAGES]  used in the leader
     uint64_t* empty_bar = bars + T2_STAGES;           // [STAGES]  one per CTA, both signalled by the leader
     uint64_t* acc_full = bars + 2 * T2_STAGES;        // [2]       one per CTA, both signalled by the leader
     uint64_t* acc_empty = bars + 2 * T2_STAGES + 2;   // [2]       used in the leader: 8 epilogue warps of the pair
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * T2_STAGES + 4);
+    uint64_t* in_bar = bars + 2 * T2_STAGES + 4;      // [4 warps][EPI_BOXES] per CTA: residual / C box has landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(in_bar + 4 * T2_EPI_BOXES);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -180,6 +190,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             mbar_init(smem_u32(&acc_full[a]), 1);
             mbar_init(smem_u32(&acc_empty[a]), 8);
         }
+        for (int b = 0; b < 4 * T2_EPI_BOXES; ++b) mbar_init(smem_u32(&in_bar[b]), 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -275,17 +286,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t acc_phase = 0;
         TC* C = static_cast<TC*>(p.C);
         const TC* Rsd = static_cast<const TC*>(p.residual);
+        StagedOut out;   // staged form of the output (p.tma_out): boxes, barriers and maps of this warp
+        out.boxes = epi_smem + (warp - 2) * (T2_EPI_BOXES * EPI_BOX_BYTES);
+        out.in_bar = in_bar + (warp - 2) * T2_EPI_BOXES;
+        out.out = &map_c;
+        out.in = p.splits > 1 ? nullptr : (Rsd != nullptr ? &map_u : (p.accumulate ? &map_c : nullptr));
+        out.bias = p.splits > 1 ? nullptr : p.bias;
+        out.N = p.splits > 1 ? p.pstride : p.N;
+        out.slab = -1;
+        out.uc = 0;
         bool ok = true;
         for (int64_t w = pair; w < n_work && ok; w += n_pairs) {
             const int64_t tile = w % n_tiles;
             const int64_t m0 = (tile / tiles_n) * (2 * T2_BM) + rank * T2_BM, n0 = (tile % tiles_n) * TILE_N;
-            ok = wait2(smem_u32(&acc_full[acc]), acc_phase, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            fence_after();
             const int64_t m = m0 + quad * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * T2_BN);
             float* part = p.splits > 1 ? p.partial + (w / n_tiles) * p.slab + m * p.pstride : nullptr;
+            const bool staged = !SWIGLU && p.tma_out;   // waits for the accumulator after it has requested its inputs
+            if (!staged) {
+                ok = wait2(smem_u32(&acc_full[acc]), acc_phase, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fence_after();
+            }
             if (SWIGLU) {
                 // columns 0..127 of the accumulator are G, 128..255 the same columns of U. G and U are
                 // rounded to the storage type first and y is formed from the rounded values with the
@@ -302,7 +325,34 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tmem_ld32(t_row + static_cast<uint32_t>(ch * 32), rg);
                     tmem_ld32(t_row + static_cast<uint32_t>(TILE_N + ch * 32), ru);
                     tmem_wait_ld();
-                    if (m < p.M) {
+                    if (p.tma_out) {
+                        // staged form: up to three boxes per 32 columns (G, U, y), each handed to a TMA store
+                        float gv[32], uv[32], yv[32];
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            gv[e] = to_f32(from_f32<TC>(__uint_as_float(rg[e])));
+                            uv[e] = to_f32(from_f32<TC>(__uint_as_float(ru[e])));
+                            yv[e] = (gv[e] / (1.0f + expf(-gv[e]))) * uv[e];
+                        }
+                        const int32_t x = static_cast<int32_t>(c0), y0 = static_cast<int32_t>(m0 + quad * 32);
+                        auto emit = [&](const float* vals, const CUtensorMap* map) {
+                            uint8_t* box = out.boxes + (out.uc & (T2_EPI_BOXES - 1)) * EPI_BOX_BYTES;
+                            if (lane == 0) bulk_wait_read<T2_EPI_BOXES - 1>();
+                            __syncwarp();
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(box + box_offset(lane, j)) = pack_out<TC>(vals + j * 8);
+                            fence_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_store_2d(map, smem_u32(box), x, y0);
+                                bulk_commit();
+                            }
+                            ++out.uc;
+                        };
+                        if (Gout) emit(gv, &map_c);
+                        if (Uout) emit(uv, &map_u);
+                        emit(yv, &map_y);
+                    } else if (m < p.M) {
 #pragma unroll
                         for (int g8 = 0; g8 < 4; ++g8) {
                             const int64_t c = c0 + g8 * 8;
@@ -320,6 +370,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                     }
                 }
+            } else if (p.tma_out) {
+                // staged form (pk_gemm_epilogue.cuh); with k parts the fp32 partial tile goes to its slab
+                const int32_t y0 = static_cast<int32_t>(m0 + quad * 32);
+                const uint32_t acc_bar = smem_u32(&acc_full[acc]);
+                if (p.splits > 1) {
+                    out.slab = static_cast<int32_t>(w / n_tiles);
+                    ok = staged_epilogue<float, T2_BN, T2_EPI_BOXES>(out, n0, y0, t_row, acc_bar, acc_phase, abort_flag, &g_gemm_tc2_ctl, lane);
+                } else {
+                    ok = staged_epilogue<TC, T2_BN, T2_EPI_BOXES>(out, n0, y0, t_row, acc_bar, acc_phase, abort_flag, &g_gemm_tc2_ctl, lane);
+                }
+                if (!ok) break;
             } else
 #pragma unroll 1
             for (int ch = 0; ch < T2_BN / 32; ++ch) {
@@ -381,6 +442,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             if (acc == 0) acc_phase ^= 1u;
         }
     }
+    if (warp >= 2 && lane == 0) bulk_wait_all();   // this thread's TMA stores are complete before the CTA's shared memory goes away
     fence_before();
     __syncthreads();
     cluster_sync_all();   // no CTA leaves while the other may still signal its barriers or read its shared memory
@@ -393,6 +455,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
 
 template <typename TC, bool SWIGLU>
 int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, T2Params p, int c_dtype) {
@@ -449,9 +512,44 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const
     if (p.splits > 1 && static_cast<int64_t>(p.kb_per_split) * (p.splits - 1) >= k_blocks)
         p.splits = static_cast<int>((k_blocks + p.kb_per_split - 1) / p.kb_per_split);
     gemm_note_splits(p.splits);
+    // Output through shared-memory staging and TMA stores (pk_gemm_epilogue.cuh) when the outputs can
+    // be described by tensor maps (16-byte aligned base and row stride) and every 16-byte group
+    // the epilogue reads (bias, residual or C) lies inside a row.
+    constexpr int64_t PER16 = 16 / static_cast<int64_t>(sizeof(TC));
+    CUtensorMap mc = ma, mu = ma, my = ma;
+    if (SWIGLU) {
+        const bool keep = p.C != nullptr;
+        p.tma_out = aligned16(p.Y) && (p.ldy % 8) == 0 && (p.N % 8) == 0 &&
+                    (!keep || (aligned16(p.C) && aligned16(p.U) && (p.ldc % 8) == 0));
+        if (p.tma_out) {
+            int rc = make_tensor_map_out(&my, p.Y, 2, p.N, p.M, p.ldy, 32);
+            if (rc == PK_OK && keep) rc = make_tensor_map_out(&mc, p.C, 2, p.N, p.M, p.ldc, 32);
+            if (rc == PK_OK && keep) rc = make_tensor_map_out(&mu, p.U, 2, p.N, p.M, p.ldc, 32);
+            if (rc != PK_OK) return rc;
+        }
+    } else if (p.splits > 1) {
+        p.tma_out = aligned16(p.partial);
+        if (p.tma_out) {   // fp32 partial tiles: columns, rows, k part
+            const int rc = make_tensor_map_out_3d(&mc, p.partial, 4, p.pstride, p.M, p.splits, p.pstride, p.slab, 32);
+            if (rc != PK_OK) return rc;
+        }
+    } else {
+        const bool reads = p.bias != nullptr || p.residual != nullptr || p.accumulate != 0;
+        p.tma_out = aligned16(p.C) && (p.ldc % PER16) == 0 && !(p.residual != nullptr && p.accumulate != 0) &&
+                    (p.residual == nullptr || (aligned16(p.residual) && (p.ldr % PER16) == 0)) &&
+                    (p.bias == nullptr || aligned16(p.bias)) && (p.N % PER16 == 0 || !reads);
+        if (p.tma_out) {
+            int rc = make_tensor_map_out(&mc, p.C, static_cast<int>(sizeof(TC)), p.N, p.M, p.ldc, 32);
+            if (rc != PK_OK) return rc;
+            if (p.residual != nullptr) {   // the kernel's map_u slot: U in SwiGLU mode, else the residual
+                rc = make_tensor_map_out(&mu, p.residual, static_cast<int>(sizeof(TC)), p.N, p.M, p.ldr, 32);
+                if (rc != PK_OK) return rc;
+            }
+        }
+    }
     int64_t pairs = max_pairs;
     if (pairs > tiles * p.splits) pairs = tiles * p.splits;
-    kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, mb2, p);
+    kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, mb2, mc, mu, my, p);
     PK_LAUNCH_CHECK();
     if (p.splits > 1)
         return gemm_splitk_reduce(st, c_dtype, p.partial, p.splits, p.slab, p.pstride, p.M, p.N, p.C, p.ldc, p.accumulate,
@@ -506,3 +604,4 @@ int gemm_tc2_swiglu_launch(cudaStream_t st, int64_t M, int64_t N, int64_t K, con
 
 
 }  // namespace pk
+

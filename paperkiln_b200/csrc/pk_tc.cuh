@@ -139,6 +139,28 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
         : "memory");
 }
+// TMA tile store shared -> global (clipped at the tensor's edges), tracked by the issuing
+// thread's bulk async-group; the shared-memory box must have been written, fenced with
+// fence.proxy.async and made visible to the issuing thread before the call.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int32_t x, int32_t y, int32_t z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until all of this thread's bulk groups are complete (their global writes performed).
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // Makes generic-proxy shared-memory writes visible to the async proxy (UMMA operand reads).
@@ -335,6 +357,11 @@ int make_tensor_map(CUtensorMap* map, const void* base, int64_t inner, int64_t o
 int make_tensor_map_3d(CUtensorMap* map, const void* base, int64_t inner, int64_t rows, int64_t batch, int64_t ld,
                        int box_inner, int box_rows);
 // Byte matrix [outer, inner] with row stride ld bytes, no swizzle (rows of the box are packed).
+// Output tiles (TMA stores): rows of 64 bytes, 64-byte swizzle; elem_bytes 2 (bf16) or 4 (fp32).
+int make_tensor_map_out(CUtensorMap* map, const void* base, int elem_bytes, int64_t inner, int64_t outer, int64_t ld,
+                        int box_outer);
+int make_tensor_map_out_3d(CUtensorMap* map, const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t slabs,
+                           int64_t ld, int64_t slab_elems, int box_outer);
 int make_tensor_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner,
                        int box_outer);
 

@@ -73,6 +73,25 @@ int make_tensor_map_3d(CUtensorMap* map, const void* base, int64_t inner, int64_
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+int make_tensor_map_out(CUtensorMap* map, const void* base, int elem_bytes, int64_t inner, int64_t outer, int64_t ld,
+                        int box_outer) {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * static_cast<cuuint64_t>(elem_bytes)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(64 / elem_bytes), static_cast<cuuint32_t>(box_outer)};
+    return encode(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims,
+                  strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
+int make_tensor_map_out_3d(CUtensorMap* map, const void* base, int elem_bytes, int64_t inner, int64_t rows, int64_t slabs,
+                           int64_t ld, int64_t slab_elems, int box_outer) {
+    const cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(slabs)};
+    const cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * static_cast<cuuint64_t>(elem_bytes),
+                                   static_cast<cuuint64_t>(slab_elems) * static_cast<cuuint64_t>(elem_bytes)};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(64 / elem_bytes), static_cast<cuuint32_t>(box_outer), 1};
+    return encode(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, base, dims,
+                  strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
+}
+
 int make_tensor_map_u8(CUtensorMap* map, const void* base, int64_t inner, int64_t outer, int64_t ld, int box_inner,
                        int box_outer) {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};

@@ -443,11 +443,17 @@ Var silu(const Var& x) { return unary_op(x, pk_silu_fwd, pk_silu_bwd, "pk_silu")
 
 Var swiglu(const Var& gate, const Var& up) {
     same_shape(gate, up, "swiglu");
-    const Tensor& gt = gate->compute();
-    const Tensor& ut = up->compute();
-    Tensor y = new_act(gt.rows(), gt.cols());
-    check(pk_swiglu_fwd(S(), gt.dt(), gt.ptr(), ut.ptr(), y.ptr(), i64(gt.numel())), "pk_swiglu_fwd");
-    return record(std::move(y), {gate, up}, [](Variable* self) {
+    // Produced on first read inside a recomputed segment: when the consumer is a frozen projection
+    // at the end of the segment (QLoRA down_proj: its backward reads neither its input nor its
+    // value), the recompute needs this product no more than the projection's.
+    auto produce = [gate, up]() {
+        const Tensor& gt = gate->compute();
+        const Tensor& ut = up->compute();
+        Tensor y = new_act(gt.rows(), gt.cols());
+        check(pk_swiglu_fwd(S(), gt.dt(), gt.ptr(), ut.ptr(), y.ptr(), i64(gt.numel())), "pk_swiglu_fwd");
+        return y;
+    };
+    return detail::record_projection(gate->data.rows(), gate->data.cols(), produce, {gate, up}, [](Variable* self) {
         const Var& gate = self->parents[0];
         const Var& up = self->parents[1];
         const Tensor& gt = gate->compute();
