@@ -28,8 +28,12 @@
 // the staged epilogue 952 (the bf16 pair kernel on an already expanded weight: 1201 -> 1413); the
 // k loop of this shape is only 14 slices, so a tile's epilogue is as long as its MMAs. With the
 // converters idle (arrivals only) the old form reached 1005, so converting costs about a sixth.
-// Four or five ring stages, and eight or sixteen converter warps (two groups on alternate k
-// slices), made no difference; eight epilogue warps were slower (781). Not kept earlier:
+// Three ring stages cost 6 %, five give nothing over four; half the conversion work per slice
+// changes nothing either, so neither the ring's depth nor the converters' throughput is the
+// bound: what remains against the bf16 kernel is the extra hop of every slice (raw bytes land ->
+// converter warps wake, convert, arrive on the leader's barrier -> the issuer wakes). Sixteen
+// converter warps (two groups on alternate k slices) need more registers than 704 threads
+// leave the epilogue (517); eight epilogue warps were slower (781). Not kept earlier:
 // converters loading the int8 slice from global memory into registers instead of staging it by
 // TMA 723; a cluster-scope release on every converter arrival 495; a second barrier for the
 // issuer to wait on 340.
