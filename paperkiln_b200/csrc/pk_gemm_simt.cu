@@ -17,6 +17,8 @@ int gemm_tc_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int6
                    const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
                    int accumulate, const float* bias, const void* residual, int64_t ldr);
 
+float* gemm_splitk_workspace(size_t* bytes);   // pk_gemm_tc.cu
+
 // CTA-pair kernel (pk_gemm_tc2.cu)
 int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                     const void* B, int64_t ldb, void* C, int64_t ldc, int accumulate, const float* bias, const void* residual,
@@ -167,7 +169,19 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
             const int64_t pairs = sm_count() / 2;
             const int64_t t2 = ((M + 255) / 256) * ((N + 255) / 256);
             const double fill = static_cast<double>(t2) / static_cast<double>((t2 + pairs - 1) / pairs * pairs);
-            if (N >= 256 && M >= 256 && fill >= 0.8) {
+            // ... or when cutting a long k loop into 2-4 parts does (the pair kernel's own split-K rule;
+            // input gradient of a wide vocabulary projection: 48 tiles, k = 151 936)
+            bool split_fills = false;
+            size_t ws_bytes = 0;
+            if (fill < 0.8 && K >= 256 * 64 && gemm_splitk_workspace(&ws_bytes) != nullptr) {
+                const size_t part_bytes = static_cast<size_t>(M) * static_cast<size_t>((N + 255) / 256 * 256) * sizeof(float);
+                for (int sp = 2; sp <= 4 && !split_fills; ++sp) {
+                    const int64_t items = t2 * sp;
+                    const double f = static_cast<double>(items) / static_cast<double>((items + pairs - 1) / pairs * pairs);
+                    split_fills = f >= 0.95 && sp * part_bytes <= ws_bytes;
+                }
+            }
+            if (N >= 256 && M >= 256 && (fill >= 0.8 || split_fills)) {
                 g_last_path = 3;
                 note_launch(PATH_GEMM_TC_PAIR);
                 return gemm_tc2_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate, bias,
