@@ -373,7 +373,8 @@ def test_gemm_cta_pair_kernel(pk, shape, ta, tb):
 @pytest.mark.parametrize("shape,ta,tb", [((2048, 512, 16384), True, False), ((768, 768, 8192), True, False),
                                          ((300, 200, 8192), False, False), ((896, 16, 8192), True, False),
                                          ((256, 264, 4096 + 64), False, True),
-                                         ((2048, 8192, 16384), True, False)])  # the last one: CTA-pair kernel
+                                         ((2048, 8192, 16384), True, False),   # CTA-pair kernel
+                                         ((3072, 896, 16384), False, False)])  # 48 pair tiles: pair kernel because 3 k parts fill it
 def test_gemm_split_k(pk, shape, ta, tb):
     """Few output tiles and a long k extent (weight gradients of narrow projections): with a
     workspace the k range is cut into parts whose fp32 partial tiles are added in a fixed order.
@@ -402,6 +403,8 @@ def test_gemm_split_k(pk, shape, ta, tb):
     assert st.value == 0
     assert outs[0][2] == 1 and outs[0][3] == 1
     assert outs[1][2] > 1 and outs[1][3] > 1, "the k range was not split"
+    if shape == (3072, 896, 16384):
+        assert pk.pk_gemm_last_path() == 3 and outs[1][2] == 3, "few tiles with a long k loop belong on the pair kernel in three parts"
     assert torch.equal(outs[1][0], outs[2][0]) and torch.equal(outs[1][1], outs[2][1])
     ref = (A.t() if ta else A).float() @ (B.t() if tb else B).float()
     tol = 2e-3 * math.sqrt(max(K, 64) / 64)
