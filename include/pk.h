@@ -199,6 +199,16 @@ int pk_rope(void* stream, int dtype, void* x, int64_t ld, int64_t col0, int n_he
             int head_dim, const int32_t* pos, const float* cos_sin, int64_t n_pos,
             int64_t R, int inverse);
 
+/* C = rope(A . op(B) + bias) for bf16 operands and output: pk_gemm followed by pk_rope on columns
+ * [0, n_heads * head_dim) of C, in one launch -- the rotation happens in the GEMM's epilogue on the
+ * value rounded to bf16, so the result is bit-identical to the two calls (the q and k
+ * projections of src/llama.cpp:30-36, which concatenates q, k, v and calls ops::apply_rope). trans_b as in pk_gemm. Takes
+ * head_dim 64 or 128 and the shapes the CTA-pair kernel takes (M, N >= 256, enough 256 x 256
+ * tiles, 16-byte aligned operands); otherwise PK_ERR_UNSUPPORTED and the caller makes the two calls. */
+int pk_gemm_rope(void* stream, int trans_b, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
+                 const void* B, int64_t ldb, void* C, int64_t ldc, const float* bias, const int32_t* pos,
+                 const float* cos_sin, int64_t n_pos, int n_heads, int head_dim, int inverse);
+
 /* ---- activations / elementwise ---------------------------------------------
  * SwiGLU y = silu(g) * u and its backward: ops::silu + ops::mul
  * (src/ops.cpp:404-424, 76-83). GELU (tanh form, correct derivative):

@@ -134,6 +134,24 @@ template <> struct Vec<bf16> {
     }
 };
 
+// Rotary embedding applied by a GEMM epilogue to columns [0, cols) of its output.
+struct RopeEpilogue {
+    const float* cos_sin;   // (cos, sin) per [position, pair]
+    const int32_t* pos;     // position of every output row
+    int64_t n_pos;
+    int half;               // pairs per head
+    int64_t cols;           // rotated columns: heads * 2 * half
+    float sign;             // +1, or -1 for the inverse rotation
+};
+
+// One rotary pair: (x0, x1) turned by the angle whose (cos, sin) is (c, s). Shared by the RoPE
+// kernels and by the GEMM epilogue that rotates q / k on their way out, so that all three
+// form the same products and sums.
+__device__ __forceinline__ void rope_rotate(float x0, float x1, float c, float s, float& o0, float& o1) {
+    o0 = x0 * c - x1 * s;
+    o1 = x0 * s + x1 * c;
+}
+
 __host__ __device__ inline bool aligned16(const void* p) {
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }

@@ -74,6 +74,16 @@ struct StagedOut {
     int64_t N;                 // columns of C
     int32_t slab;              // >= 0: `out` is 3-D and this is the slab
     uint32_t uc;               // units staged so far by this warp: box index and barrier phase rotate with it
+    // Rotary embedding on the way out (bf16 outputs; q and k projections): columns [0, rope_cols)
+    // are heads of 2 * rope_half columns whose adjacent pairs are turned by the angle of the row's
+    // position, after the value has been rounded to bf16 as a separate GEMM would have stored it.
+    const float* rope_cs = nullptr;    // (cos, sin) per [position, pair]; null: no rotation
+    const int32_t* rope_pos = nullptr; // position of every row of C
+    int rope_half = 0;                 // 32 or 64: a 32-column unit lies inside one head
+    int64_t rope_cols = 0;
+    int64_t rope_npos = 0;
+    float rope_sign = 1.0f;            // -1: inverse rotation
+    int64_t M = 0;                     // rows of C (only read when rotating)
 };
 
 // Writes the 32 x BN block of one warp: accumulator columns [0, BN) at tensor-memory address
@@ -118,6 +128,21 @@ __device__ __forceinline__ bool staged_epilogue(StagedOut& s, int64_t n0, int32_
                         const float4 b = *reinterpret_cast<const float4*>(s.bias + c);
                         v[g * 4] += b.x; v[g * 4 + 1] += b.y; v[g * 4 + 2] += b.z; v[g * 4 + 3] += b.w;
                     }
+                }
+            }
+            if (sizeof(TC) == 2 && s.rope_cs != nullptr && n0 + u * UC < s.rope_cols && y0 + lane < s.M) {
+                int64_t pp = s.rope_pos[y0 + lane];
+                pp = pp < 0 ? 0 : (pp >= s.rope_npos ? s.rope_npos - 1 : pp);
+                const int j0 = static_cast<int>((n0 + u * UC) % (2 * s.rope_half)) / 2;   // first pair of this unit in its head
+                const float4* cs4 = reinterpret_cast<const float4*>(s.rope_cs + (pp * s.rope_half + j0) * 2);
+#pragma unroll
+                for (int g = 0; g < UC / 4; ++g) {
+                    const float4 c2 = __ldg(cs4 + g);   // (cos, sin) of two pairs
+                    float a[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) a[e] = to_f32(from_f32<bf16>(v[g * 4 + e]));
+                    rope_rotate(a[0], a[1], c2.x, c2.y * s.rope_sign, v[g * 4], v[g * 4 + 1]);
+                    rope_rotate(a[2], a[3], c2.z, c2.w * s.rope_sign, v[g * 4 + 2], v[g * 4 + 3]);
                 }
             }
             const uint32_t bx = s.uc & (BOXES - 1);

@@ -22,7 +22,7 @@ float* gemm_splitk_workspace(size_t* bytes);   // pk_gemm_tc.cu
 // CTA-pair kernel (pk_gemm_tc2.cu)
 int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                     const void* B, int64_t ldb, void* C, int64_t ldc, int accumulate, const float* bias, const void* residual,
-                    int64_t ldr);
+                    int64_t ldr, const RopeEpilogue* rope);
 
 static thread_local int g_last_path = -1;
 static int g_force_simt = 0;
@@ -185,7 +185,7 @@ int pk_gemm(void* stream, int ab_dtype, int c_dtype, int trans_a, int trans_b, i
                 g_last_path = 3;
                 note_launch(PATH_GEMM_TC_PAIR);
                 return gemm_tc2_launch(st, c_dtype, trans_a, trans_b, M, N, K, A, lda, B, ldb, C, ldc, accumulate, bias,
-                                       residual, ldr);
+                                       residual, ldr, nullptr);
             }
         }
         g_last_path = 2;
@@ -230,6 +230,40 @@ int pk_gemm_swiglu(void* stream, int64_t M, int64_t N, int64_t K, const void* A,
     g_last_path = 3;
     note_launch(PATH_GEMM_TC_PAIR);
     return gemm_tc2_swiglu_launch(st, M, N, K, A, lda, Wg, ldg, Wu, ldu, G, U, ldgu, Y, ldy);
+}
+
+int pk_gemm_rope(void* stream, int trans_b, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda, const void* B,
+                 int64_t ldb, void* C, int64_t ldc, const float* bias, const int32_t* pos, const float* cos_sin, int64_t n_pos,
+                 int n_heads, int head_dim, int inverse) {
+    PK_REQUIRE(M >= 0 && N >= 0 && K > 0 && n_heads >= 0 && n_pos > 0, "bad shape");
+    if (M == 0 || N == 0) return PK_OK;
+    PK_REQUIRE(A && B && C && pos && cos_sin, "null pointer");
+    PK_REQUIRE(lda >= K && ldb >= (trans_b ? K : N) && ldc >= N, "leading dimension too small");
+    PK_REQUIRE(static_cast<int64_t>(n_heads) * head_dim <= N, "more rotated columns than C has");
+    // the pair kernel's staged epilogue, a 32-column unit inside one head, the same fill rule as pk_gemm
+    const int64_t pairs = sm_count() / 2;
+    const int64_t t2 = ((M + 255) / 256) * ((N + 255) / 256);
+    const double fill = static_cast<double>(t2) / static_cast<double>((t2 + pairs - 1) / pairs * pairs);
+    const bool ok = !g_force_simt && g_pair_mode && (head_dim == 64 || head_dim == 128) && M >= 256 && N >= 256 && fill >= 0.8 &&
+                    N % 8 == 0 && aligned16(cos_sin) && (bias == nullptr || aligned16(bias)) &&
+                    gemm_tc_supported(PK_BF16, 0, trans_b, M, N, K, A, lda, B, ldb, C, ldc, nullptr, 0, bias);
+    if (!ok) {
+        set_error("pk_gemm_rope: shape or alignment outside what the kernel takes (M %lld N %lld K %lld head_dim %d)",
+                  static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K), head_dim);
+        return PK_ERR_UNSUPPORTED;
+    }
+    RopeEpilogue rope;
+    rope.cos_sin = cos_sin;
+    rope.pos = pos;
+    rope.n_pos = n_pos;
+    rope.half = head_dim / 2;
+    rope.cols = static_cast<int64_t>(n_heads) * head_dim;
+    rope.sign = inverse ? -1.0f : 1.0f;
+    cudaStream_t st = as_stream(stream);
+    ProfScope prof(PROF_GEMM_TC, 2.0 * M * N * K, st);
+    g_last_path = 3;
+    note_launch(PATH_GEMM_TC_PAIR);
+    return gemm_tc2_launch(st, PK_BF16, 0, trans_b, M, N, K, A, lda, B, ldb, C, ldc, 0, bias, nullptr, 0, &rope);
 }
 
 int pk_gemm_last_path(void) { return g_last_path; }

@@ -71,6 +71,12 @@ struct T2Params {
     // SwiGLU mode), 0: the threads store their rows themselves (unaligned C, ragged N with a
     // residual or accumulate read)
     int tma_out;
+    // rotary embedding in the epilogue (StagedOut in pk_gemm_epilogue.cuh); rope_cs == nullptr: none
+    const float* rope_cs;
+    const int32_t* rope_pos;
+    int rope_half;
+    int64_t rope_cols, rope_npos;
+    float rope_sign;
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -295,6 +301,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         out.N = p.splits > 1 ? p.pstride : p.N;
         out.slab = -1;
         out.uc = 0;
+        out.rope_cs = p.rope_cs;
+        out.rope_pos = p.rope_pos;
+        out.rope_half = p.rope_half;
+        out.rope_cols = p.rope_cols;
+        out.rope_npos = p.rope_npos;
+        out.rope_sign = p.rope_sign;
+        out.M = p.M;
         bool ok = true;
         for (int64_t w = pair; w < n_work && ok; w += n_pairs) {
             const int64_t tile = w % n_tiles;
@@ -499,7 +512,7 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const
     auto fill = [&](int64_t items) {
         return static_cast<double>(items) / static_cast<double>((items + max_pairs - 1) / max_pairs * max_pairs);
     };
-    if (!SWIGLU && p.partial != nullptr && k_blocks >= 256 && fill(tiles) < 0.9) {
+    if (!SWIGLU && p.rope_cs == nullptr && p.partial != nullptr && k_blocks >= 256 && fill(tiles) < 0.9) {
         for (int sp = 2; sp <= 4; ++sp) {
             if (static_cast<size_t>(sp) * p.slab * sizeof(float) > ws_bytes) break;
             if (fill(tiles * sp) >= 0.95) {
@@ -547,6 +560,10 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const
             }
         }
     }
+    if (p.rope_cs != nullptr && !p.tma_out) {
+        set_error("pk_gemm_rope: the output cannot go through the staged epilogue");
+        return PK_ERR_UNSUPPORTED;
+    }
     int64_t pairs = max_pairs;
     if (pairs > tiles * p.splits) pairs = tiles * p.splits;
     kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, mb2, mc, mu, my, p);
@@ -561,7 +578,7 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const
 
 int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int64_t N, int64_t K, const void* A, int64_t lda,
                     const void* B, int64_t ldb, void* C, int64_t ldc, int accumulate, const float* bias, const void* residual,
-                    int64_t ldr) {
+                    int64_t ldr, const RopeEpilogue* rope) {
     const int a_mn = ta ? 1 : 0, b_mn = tb ? 0 : 1;
     CUtensorMap ma, mb;
     int rc;
@@ -579,6 +596,11 @@ int gemm_tc2_launch(cudaStream_t st, int c_dtype, int ta, int tb, int64_t M, int
     p.accumulate = accumulate;
     p.a_mn_major = a_mn; p.b_mn_major = b_mn;
     p.U = nullptr; p.Y = nullptr; p.ldy = 0;
+    p.rope_cs = nullptr; p.rope_pos = nullptr; p.rope_half = 0; p.rope_cols = 0; p.rope_npos = 0; p.rope_sign = 1.0f;
+    if (rope != nullptr) {
+        p.rope_cs = rope->cos_sin; p.rope_pos = rope->pos; p.rope_half = rope->half;
+        p.rope_cols = rope->cols; p.rope_npos = rope->n_pos; p.rope_sign = rope->sign;
+    }
     if (c_dtype == PK_F32) return launch2<float, false>(st, ma, mb, mb, p, c_dtype);
     return launch2<bf16, false>(st, ma, mb, mb, p, c_dtype);
 }
@@ -599,6 +621,7 @@ int gemm_tc2_swiglu_launch(cudaStream_t st, int64_t M, int64_t N, int64_t K, con
     p.accumulate = 0;
     p.a_mn_major = 0; p.b_mn_major = 1;
     p.U = U; p.Y = Y; p.ldy = ldy;
+    p.rope_cs = nullptr; p.rope_pos = nullptr; p.rope_half = 0; p.rope_cols = 0; p.rope_npos = 0; p.rope_sign = 1.0f;
     return launch2<bf16, true>(st, ma, mg, mu, p, PK_BF16);
 }
 

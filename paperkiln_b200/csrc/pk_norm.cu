@@ -499,8 +499,10 @@ rope_kernel(T* __restrict__ x, int64_t ld, int64_t col0, int n_heads, int half, 
         T* px = x + row * ld + col0 + static_cast<int64_t>(h) * (2 * half) + 2 * j;
         const float x0 = to_f32(px[0]), x1 = to_f32(px[1]);
         const float sn = c.y * sin_sign;
-        px[0] = from_f32<T>(x0 * c.x - x1 * sn);
-        px[1] = from_f32<T>(x0 * sn + x1 * c.x);
+        float o0, o1;
+        rope_rotate(x0, x1, c.x, sn, o0, o1);
+        px[0] = from_f32<T>(o0);
+        px[1] = from_f32<T>(o1);
     }
 }
 
@@ -530,9 +532,7 @@ rope_vec8_kernel(bf16* __restrict__ x, int64_t ld, int64_t col0, int n_heads, in
         float o[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float x0 = v[2 * e], x1 = v[2 * e + 1];
-            o[2 * e] = x0 * cc[e] - x1 * ss[e];
-            o[2 * e + 1] = x0 * ss[e] + x1 * cc[e];
+            rope_rotate(v[2 * e], v[2 * e + 1], cc[e], ss[e], o[2 * e], o[2 * e + 1]);
         }
         Vec<bf16>::store(px, o);
     }

@@ -77,6 +77,9 @@ Var swiglu(const Var& gate, const Var& up);
 // pass will need them, and their gradients are written over them. Same values, bit for bit, as
 // swiglu(linear(x, Wg), linear(x, Wu)); falls back to exactly that where the kernel does not apply.
 Var linear_swiglu(const Var& x, const Var& Wg, const Var& Wu);
+// rope_(linear(x, W), pos, theta_base, head_dim, n_rot) with the rotation in the GEMM's epilogue
+// where the kernel takes the shape (bf16, head_dim 64 or 128); the same bits either way.
+Var linear_rope(const Var& x, const Var& W, const std::vector<int>& pos, float theta_base, size_t head_dim, size_t n_rot);
 
 }  // namespace ops
 }  // namespace microtorch

@@ -60,11 +60,12 @@ LlamaBlock::LlamaBlock(const LlamaConfig& cfg, unsigned seed)
 Var LlamaBlock::forward(const Var& x, const std::vector<int>& pos, size_t seq_len) const {
     // ---- attention sublayer (pre-RMSNorm)
     Var h = ops::rmsnorm(x, ln1_w);
-    Var q = q_proj->forward(h);
-    Var k = k_proj->forward(h);
+    // dense projections rotate q and k on their way out of the GEMM; quantised ones in a second pass
+    Var q = q_proj->W ? ops::linear_rope(h, q_proj->W, pos, rope_theta_, dk, rope_all_ ? H : 1)
+                      : ops::rope_(q_proj->forward(h), pos, rope_theta_, dk, rope_all_ ? H : 1);
+    Var k = k_proj->W ? ops::linear_rope(h, k_proj->W, pos, rope_theta_, dk, rope_all_ ? Hkv : 1)
+                      : ops::rope_(k_proj->forward(h), pos, rope_theta_, dk, rope_all_ ? Hkv : 1);
     Var v = v_proj->forward(h);
-    q = ops::rope_(q, pos, rope_theta_, dk, rope_all_ ? H : 1);
-    k = ops::rope_(k, pos, rope_theta_, dk, rope_all_ ? Hkv : 1);
     Var a = ops::attention(q, k, v, H, Hkv, seq_len, /*causal=*/true);
     Var x1 = o_proj->forward_residual(a, x);  // x + attn
     // ---- SwiGLU FFN sublayer

@@ -358,6 +358,33 @@ Var matmul(const Var& a, const Var& b) {
     });
 }
 
+// Backward of y = x W (+ bias) (+ residual) given the upstream gradient g (reference: src/ops.cpp:50-55, 96-103).
+static void linear_backward(Variable* self, const Tensor& g, bool transposed_w, bool has_bias, bool has_res) {
+        const Var& x = self->parents[0];
+        const Var& W = self->parents[1];
+        if (W->requires_grad) {
+            if (!transposed_w) gemm_to_grad(W, x->compute(), true, g, false);  // [in,out] = X^T G
+            else gemm_to_grad(W, g, true, x->compute(), false);               // [out,in] = G^T X
+        }
+        // last use of x by this node is behind us: dX may take x's place when x is dead otherwise
+        if (x->requires_grad) gemm_to_grad(x, g, false, W->compute(), !transposed_w, /*reuse_data=*/true);
+        size_t idx = 2;
+        if (has_bias) {
+            const Var& b = self->parents[idx++];
+            if (b->requires_grad) {
+                const Tensor gd = g.dense();
+                Tensor scratch = Tensor::bytes(pk_colsum_scratch_bytes(i64(gd.rows()), i64(gd.cols())));
+                into_f32_grad(b, [&](float* dst) {
+                    check(pk_colsum(S(), gd.dt(), gd.ptr(), dst, scratch.ptr(), i64(gd.rows()), i64(gd.cols())), "pk_colsum");
+                });
+            }
+        }
+        if (has_res) {
+            const Var& r = self->parents[idx++];
+            if (r->requires_grad) r->accumulate(g.dense());
+        }
+    }
+
 Var linear(const Var& x, const Var& W, const Var& bias, const Var& residual, bool transposed_w) {
     const size_t in = transposed_w ? W->data.cols() : W->data.rows();
     const size_t out = transposed_w ? W->data.rows() : W->data.cols();
@@ -382,30 +409,44 @@ Var linear(const Var& x, const Var& W, const Var& bias, const Var& residual, boo
     };
     const bool has_bias = bias != nullptr, has_res = residual != nullptr;
     return detail::record_projection(x->data.rows(), out, produce, {x, W, bias, residual}, [transposed_w, has_bias, has_res](Variable* self) {
-        const Var& x = self->parents[0];
-        const Var& W = self->parents[1];
+        linear_backward(self, grad_of(self), transposed_w, has_bias, has_res);
+    });
+}
+
+// y = rope(x W): the q / k projection with the rotary embedding applied in the GEMM's epilogue
+// (pk_gemm_rope), bit-identical to rope_(linear(x, W), ...) and falling back to exactly that when
+// the kernel does not take the shape. Backward: the gradient is rotated back in place, then the
+// projection's backward runs on it.
+Var linear_rope(const Var& x, const Var& W, const std::vector<int>& pos, float theta_base, size_t head_dim, size_t n_rot) {
+    const size_t in = W->data.rows(), out = W->data.cols();
+    if (x->data.cols() != in) throw std::runtime_error("matmul: inner dimensions disagree");
+    if (head_dim % 2 != 0 || n_rot * head_dim > out) throw std::runtime_error("apply_rope: head_dim must be even and <= d");
+    if (pos.size() != x->data.rows()) throw std::runtime_error("apply_rope: one position per row");
+    if (cdt() != DType::BF16 || (head_dim != 64 && head_dim != 128) || n_rot == 0)
+        return rope_(linear(x, W), pos, theta_base, head_dim, n_rot);
+    auto produce = [x, W, pos, theta_base, head_dim, n_rot, out]() {
+        const Tensor& xt = x->compute();
+        const Tensor& wt = W->compute();
+        Tensor y = new_act(xt.rows(), out);
+        Tensor table = rope_table(theta_base, head_dim, max_pos(pos));
+        Tensor dpos = device_ints(pos);
+        const int rc = pk_gemm_rope(S(), 0, i64(xt.rows()), i64(out), i64(xt.cols()), xt.ptr(), i64(xt.ld()), wt.ptr(), i64(wt.ld()),
+                                    y.ptr(), i64(y.ld()), nullptr, static_cast<const int32_t*>(dpos.ptr()), table.f32(),
+                                    i64(table.rows()), static_cast<int>(n_rot), static_cast<int>(head_dim), 0);
+        if (rc == PK_ERR_UNSUPPORTED) {
+            gemm(xt, false, wt, false, y, false);
+            rope_apply(y, 0, n_rot, head_dim, pos, theta_base, false);
+        } else {
+            check(rc, "pk_gemm_rope");
+        }
+        return y;
+    };
+    return detail::record_projection(x->data.rows(), out, produce, {x, W}, [pos, theta_base, head_dim, n_rot](Variable* self) {
         Tensor g = grad_of(self);
-        if (W->requires_grad) {
-            if (!transposed_w) gemm_to_grad(W, x->compute(), true, g, false);  // [in,out] = X^T G
-            else gemm_to_grad(W, g, true, x->compute(), false);               // [out,in] = G^T X
-        }
-        // last use of x by this node is behind us: dX may take x's place when x is dead otherwise
-        if (x->requires_grad) gemm_to_grad(x, g, false, W->compute(), !transposed_w, /*reuse_data=*/true);
-        size_t idx = 2;
-        if (has_bias) {
-            const Var& b = self->parents[idx++];
-            if (b->requires_grad) {
-                const Tensor gd = g.dense();
-                Tensor scratch = Tensor::bytes(pk_colsum_scratch_bytes(i64(gd.rows()), i64(gd.cols())));
-                into_f32_grad(b, [&](float* dst) {
-                    check(pk_colsum(S(), gd.dt(), gd.ptr(), dst, scratch.ptr(), i64(gd.rows()), i64(gd.cols())), "pk_colsum");
-                });
-            }
-        }
-        if (has_res) {
-            const Var& r = self->parents[idx++];
-            if (r->requires_grad) r->accumulate(g.dense());
-        }
+        self->grad.reset();
+        if (g.use_count() > 1) g = g.clone();  // someone else still reads the unrotated gradient
+        rope_apply(g, 0, n_rot, head_dim, pos, theta_base, true);
+        linear_backward(self, g, false, false, false);
     });
 }
 

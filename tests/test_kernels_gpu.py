@@ -903,3 +903,41 @@ def test_gemm_swiglu_equals_the_three_separate_calls(pk, shape):
     assert st.value == 0
     # shapes the kernel does not take are reported, not mangled
     assert pk.pk_gemm_swiglu(stream(), 64, N, K, ptr(x), K, ptr(Wg), N, ptr(Wu), N, None, None, N, ptr(y), N) == 3
+
+
+@pytest.mark.parametrize("shape", [(4096, 2048, 512, 64, 32, False, False), (16384, 512, 264, 64, 1, True, False),
+                                   (2048, 4096, 384, 128, 16, False, True), (4099, 2048, 512, 64, 12, False, True)])
+def test_gemm_rope_equals_gemm_then_rope(pk, shape):
+    """pk_gemm_rope (the q / k projection with the rotary embedding applied in the GEMM's epilogue)
+    gives pk_gemm followed by pk_rope bit for bit: all heads or only the first, both layouts of
+    the weight, with a bias, ragged rows, forward and inverse rotation. Shapes the kernel does not
+    take are refused with PK_ERR_UNSUPPORTED."""
+    M, N, K, hd, nh, tb, with_bias = shape
+    A = rnd(M, K, seed=1, lo=-1, hi=1, dtype=torch.bfloat16)
+    B = rnd(N, K, seed=2, lo=-1, hi=1, dtype=torch.bfloat16) if tb else rnd(K, N, seed=2, lo=-1, hi=1, dtype=torch.bfloat16)
+    bias = rnd(1, N, seed=3).reshape(N) if with_bias else None
+    n_pos = 777
+    pos = torch.tensor([(7 * i) % n_pos for i in range(M)], dtype=torch.int32, device="cuda")
+    j = np.arange(hd // 2, dtype=np.float32)
+    inv = (np.float32(1.0) / np.power(np.float32(10000.0), (2 * j) / np.float32(hd))).astype(np.float32)
+    th = np.arange(n_pos, dtype=np.float32)[:, None] * inv[None, :]
+    tab = torch.from_numpy(np.stack([np.cos(th), np.sin(th)], axis=-1).astype(np.float32)).cuda().contiguous()
+    for inverse in (0, 1):
+        two = pkt.gemm(A, B, tb=tb, bias=bias)
+        pkt.check(pk.pk_rope(stream(), dt(two), ptr(two), N, 0, nh, hd, ptr(pos), ptr(tab), n_pos, M, inverse))
+        one = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        pkt.check(pk.pk_gemm_rope(stream(), int(tb), M, N, K, ptr(A), K, ptr(B), B.stride(0), ptr(one), N, ptr(bias),
+                                  ptr(pos), ptr(tab), n_pos, nh, hd, inverse))
+        assert pk.pk_gemm_last_path() == 3
+        assert torch.equal(one, two), (one.float() - two.float()).abs().max()
+    st = ctypes.c_int(0)
+    pkt.check(pk.pk_gemm_tc_status(ctypes.byref(st), 1))
+    assert st.value == 0
+    # head_dim 32: a 32-column unit would span two heads
+    rc = pk.pk_gemm_rope(stream(), int(tb), M, N, K, ptr(A), K, ptr(B), B.stride(0), ptr(one), N, None, ptr(pos), ptr(tab),
+                         n_pos, 1, 32, 0)
+    assert rc == 3  # PK_ERR_UNSUPPORTED
+    # too few rows for the pair kernel
+    rc = pk.pk_gemm_rope(stream(), int(tb), 64, N, K, ptr(A), K, ptr(B), B.stride(0), ptr(one), N, None, ptr(pos), ptr(tab),
+                         n_pos, nh, hd, 0)
+    assert rc == 3
