@@ -373,6 +373,7 @@ int pk_gemm_q8_lora(void* stream, int c_dtype, int trans_w, int64_t M, int64_t N
                     const void* XA, int64_t ldxa, const void* L, int64_t ldl, int r,
                     void* C, int64_t ldc, int accumulate, const float* bias, const void* residual, int64_t ldr);
 
+
 /* ---- collectives -------------------------------------------------------------
  * Sum all-reduce of fp32 gradient ranges between the ranks of a data-parallel job (one process
  * per GPU), asynchronous behind the compute stream so that the exchange of one block's gradients

@@ -147,9 +147,11 @@ struct RopeEpilogue {
 // One rotary pair: (x0, x1) turned by the angle whose (cos, sin) is (c, s). Shared by the RoPE
 // kernels and by the GEMM epilogue that rotates q / k on their way out, so that all three
 // form the same products and sums.
+// Every product and sum is rounded on its own (no fused multiply-add), as the reference's CPU loop
+// does (src/ops.cpp:495-511), so the three sites cannot contract differently.
 __device__ __forceinline__ void rope_rotate(float x0, float x1, float c, float s, float& o0, float& o1) {
-    o0 = x0 * c - x1 * s;
-    o1 = x0 * s + x1 * c;
+    o0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    o1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
 }
 
 __host__ __device__ inline bool aligned16(const void* p) {

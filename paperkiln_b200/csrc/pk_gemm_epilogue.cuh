@@ -89,7 +89,7 @@ struct StagedOut {
 // Writes the 32 x BN block of one warp: accumulator columns [0, BN) at tensor-memory address
 // t_row -> C columns n0.., rows y0 .. y0 + 31. Waits for the accumulator (acc_bar / acc_parity)
 // after it has requested the first inputs. Returns false when a bounded wait gave up.
-template <typename TC, int BN, int BOXES>
+template <typename TC, int BN, int BOXES, bool ROPE = false>
 __device__ __forceinline__ bool staged_epilogue(StagedOut& s, int64_t n0, int32_t y0, uint32_t t_row, uint32_t acc_bar,
                                                 uint32_t acc_parity, volatile int* abort_flag, WaitCtl* ctl, int lane) {
     constexpr int UC = 64 / static_cast<int>(sizeof(TC));   // output columns in 64 bytes
@@ -106,6 +106,25 @@ __device__ __forceinline__ bool staged_epilogue(StagedOut& s, int64_t n0, int32_
             tma_load_2d(smem_u32(s.boxes + bx * EPI_BOX_BYTES), s.in, static_cast<int32_t>(n0 + u * UC), y0, bar);
         }
     }
+    // rotary embedding: this row's (cos, sin) table row; the 16 pairs of a unit are fetched one unit
+    // ahead (the first before the accumulator is complete) so that their latency is not in the loop
+    const bool rot = ROPE && sizeof(TC) == 2 && s.rope_cs != nullptr && y0 + lane < s.M;
+    const float4* cs_row = nullptr;
+    float4 cs_cur[UC / 4], cs_nxt[UC / 4];
+#pragma unroll
+    for (int g = 0; g < UC / 4; ++g) cs_cur[g] = cs_nxt[g] = make_float4(1.0f, 0.0f, 1.0f, 0.0f);
+    auto rope_fetch = [&](int u, float4 (&dst)[UC / 4]) {
+        // float4 index of the unit's first pair inside the table row: pair j0 -> floats 2 j0
+        const int f4 = static_cast<int>((n0 + static_cast<int64_t>(u) * UC) % (2 * s.rope_half)) / 4;
+#pragma unroll
+        for (int g = 0; g < UC / 4; ++g) dst[g] = __ldg(cs_row + f4 + g);
+    };
+    if (rot) {
+        int64_t pp = s.rope_pos[y0 + lane];
+        pp = pp < 0 ? 0 : (pp >= s.rope_npos ? s.rope_npos - 1 : pp);
+        cs_row = reinterpret_cast<const float4*>(s.rope_cs + pp * s.rope_half * 2);
+        if (n0 < s.rope_cols) rope_fetch(0, cs_cur);
+    }
     bool ok = mbar_wait(acc_bar, acc_parity, abort_flag, ctl);
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) return false;
@@ -115,6 +134,7 @@ __device__ __forceinline__ bool staged_epilogue(StagedOut& s, int64_t n0, int32_
 #pragma unroll
     for (int u = 0; u < UNITS; ++u) {
         if (u < n_units && ok) {
+            if (rot && u + 1 < n_units && n0 + (u + 1) * UC < s.rope_cols) rope_fetch(u + 1, cs_nxt);
             tmem_wait_ld();
             if (u + 1 < n_units) tmem_ld_cols<UC>(t_row + static_cast<uint32_t>((u + 1) * UC), r[(u + 1) & 1]);
             float v[UC];
@@ -130,14 +150,10 @@ __device__ __forceinline__ bool staged_epilogue(StagedOut& s, int64_t n0, int32_
                     }
                 }
             }
-            if (sizeof(TC) == 2 && s.rope_cs != nullptr && n0 + u * UC < s.rope_cols && y0 + lane < s.M) {
-                int64_t pp = s.rope_pos[y0 + lane];
-                pp = pp < 0 ? 0 : (pp >= s.rope_npos ? s.rope_npos - 1 : pp);
-                const int j0 = static_cast<int>((n0 + u * UC) % (2 * s.rope_half)) / 2;   // first pair of this unit in its head
-                const float4* cs4 = reinterpret_cast<const float4*>(s.rope_cs + (pp * s.rope_half + j0) * 2);
+            if (rot && n0 + u * UC < s.rope_cols) {
 #pragma unroll
                 for (int g = 0; g < UC / 4; ++g) {
-                    const float4 c2 = __ldg(cs4 + g);   // (cos, sin) of two pairs
+                    const float4 c2 = cs_cur[g];   // (cos, sin) of two pairs
                     float a[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) a[e] = to_f32(from_f32<bf16>(v[g * 4 + e]));
@@ -145,6 +161,8 @@ __device__ __forceinline__ bool staged_epilogue(StagedOut& s, int64_t n0, int32_
                     rope_rotate(a[2], a[3], c2.z, c2.w * s.rope_sign, v[g * 4 + 2], v[g * 4 + 3]);
                 }
             }
+#pragma unroll
+            for (int g = 0; g < UC / 4; ++g) cs_cur[g] = cs_nxt[g];
             const uint32_t bx = s.uc & (BOXES - 1);
             uint8_t* box = s.boxes + bx * EPI_BOX_BYTES;
             if (reads) {

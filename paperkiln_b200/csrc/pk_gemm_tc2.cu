@@ -390,6 +390,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (p.splits > 1) {
                     out.slab = static_cast<int32_t>(w / n_tiles);
                     ok = staged_epilogue<float, T2_BN, T2_EPI_BOXES>(out, n0, y0, t_row, acc_bar, acc_phase, abort_flag, &g_gemm_tc2_ctl, lane);
+                } else if (sizeof(TC) == 2 && p.rope_cs != nullptr) {
+                    ok = staged_epilogue<TC, T2_BN, T2_EPI_BOXES, true>(out, n0, y0, t_row, acc_bar, acc_phase, abort_flag, &g_gemm_tc2_ctl, lane);
                 } else {
                     ok = staged_epilogue<TC, T2_BN, T2_EPI_BOXES>(out, n0, y0, t_row, acc_bar, acc_phase, abort_flag, &g_gemm_tc2_ctl, lane);
                 }

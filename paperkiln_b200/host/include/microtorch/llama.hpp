@@ -39,6 +39,8 @@ public:
     Projection(size_t in, size_t out, unsigned seed, bool quantized, bool lora, size_t rank, float alpha);
     Var forward(const Var& x) const;
     Var forward_residual(const Var& x, const Var& residual) const;
+    // forward(x) with the rotary embedding applied to the first n_rot heads of the result
+    Var forward_rope(const Var& x, const std::vector<int>& pos, float theta_base, size_t head_dim, size_t n_rot) const;
     Var W;     // dense mode
     Var A, B;  // LoRA (QLoRA mode, q/v projections)
     std::shared_ptr<Q8Weight> Wq;

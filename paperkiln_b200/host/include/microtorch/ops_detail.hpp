@@ -28,6 +28,13 @@ void gemm_raw(const Tensor& A, bool ta, const Tensor& B, bool tb, Tensor& C, boo
 void gemm_into_grad(const Var& target, const Tensor& A, bool ta, const Tensor& B, bool tb);
 // grad(b) += column sums of g
 void colsum_into_grad(const Var& b, const Tensor& g);
+// Rotary embedding: the (cos, sin) table [positions, head_dim] for theta_base and the positions on
+// the device; rotation of the first n_rot heads of t in place (inverse: by the negative angle).
+void rope_operands(const std::vector<int>& pos, float theta_base, size_t head_dim, Tensor& table, Tensor& dpos);
+// False when MICROTORCH_ROPE_IN_GEMM=0: the projections then rotate in a second pass (for
+// measuring what the fusion is worth; the results are the same bits).
+bool rope_in_gemm();
+void rope_inplace(Tensor& t, size_t n_rot, size_t head_dim, const std::vector<int>& pos, float theta_base, bool inverse);
 
 }  // namespace detail
 }  // namespace ops

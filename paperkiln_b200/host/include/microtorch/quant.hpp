@@ -48,14 +48,23 @@ QuantizedTensor quantize_int8(const Matrix& m, size_t block = 64);
 Matrix dequantize(const QuantizedTensor& t);
 
 namespace ops {
+// Rotary embedding to apply to the first n_rot heads of a quantised projection's output, as one
+// tape node with the projection (what rope_(y, pos, theta_base, head_dim, n_rot) would do; a second
+// pass over y: the Q8_0 kernel's epilogue has no registers to spare for it).
+struct Rotary {
+    std::vector<int> pos;
+    float theta_base;
+    size_t head_dim;
+    size_t n_rot;
+};
 // y = x deq(Wq) (+ bias) (+ residual); no gradient flows to the quantized weight.
 Var q8_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var& bias = nullptr,
-              const Var& residual = nullptr);
+              const Var& residual = nullptr, const Rotary* rot = nullptr);
 // y = x deq(Wq) + scaling (x A) B (+ bias) (+ residual): the QLoRA projection as one tape node.
 // Gradients reach x, A and B (and bias / residual). In bf16 mode with a Q8_0 weight the base
 // product and the rank-r product share one accumulator in one kernel, forward and backward.
 Var q8_lora_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var& A, const Var& B, float scaling,
-                   const Var& bias = nullptr, const Var& residual = nullptr);
+                   const Var& bias = nullptr, const Var& residual = nullptr, const Rotary* rot = nullptr);
 }  // namespace ops
 
 namespace nn {

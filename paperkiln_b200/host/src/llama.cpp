@@ -33,6 +33,13 @@ Var Projection::forward_residual(const Var& x, const Var& residual) const {
     return ops::q8_lora_linear(x, Wq, A, B, scaling, nullptr, residual);
 }
 
+Var Projection::forward_rope(const Var& x, const std::vector<int>& pos, float theta_base, size_t head_dim, size_t n_rot) const {
+    if (W) return ops::linear_rope(x, W, pos, theta_base, head_dim, n_rot);
+    const ops::Rotary rot{pos, theta_base, head_dim, n_rot};
+    if (!A) return ops::q8_linear(x, Wq, nullptr, nullptr, &rot);
+    return ops::q8_lora_linear(x, Wq, A, B, scaling, nullptr, nullptr, &rot);
+}
+
 LlamaBlock::LlamaBlock(const LlamaConfig& cfg, unsigned seed)
     : H(cfg.n_heads), Hkv(cfg.n_kv_heads ? cfg.n_kv_heads : cfg.n_heads), dk(cfg.d / cfg.n_heads),
       rope_theta_(cfg.rope_theta), rms_eps_(cfg.rms_eps), rope_all_(cfg.rope_all_heads) {
@@ -60,11 +67,9 @@ LlamaBlock::LlamaBlock(const LlamaConfig& cfg, unsigned seed)
 Var LlamaBlock::forward(const Var& x, const std::vector<int>& pos, size_t seq_len) const {
     // ---- attention sublayer (pre-RMSNorm)
     Var h = ops::rmsnorm(x, ln1_w);
-    // dense projections rotate q and k on their way out of the GEMM; quantised ones in a second pass
-    Var q = q_proj->W ? ops::linear_rope(h, q_proj->W, pos, rope_theta_, dk, rope_all_ ? H : 1)
-                      : ops::rope_(q_proj->forward(h), pos, rope_theta_, dk, rope_all_ ? H : 1);
-    Var k = k_proj->W ? ops::linear_rope(h, k_proj->W, pos, rope_theta_, dk, rope_all_ ? Hkv : 1)
-                      : ops::rope_(k_proj->forward(h), pos, rope_theta_, dk, rope_all_ ? Hkv : 1);
+    // q and k are rotated on their way out of the projection's GEMM
+    Var q = q_proj->forward_rope(h, pos, rope_theta_, dk, rope_all_ ? H : 1);
+    Var k = k_proj->forward_rope(h, pos, rope_theta_, dk, rope_all_ ? Hkv : 1);
     Var v = v_proj->forward(h);
     Var a = ops::attention(q, k, v, H, Hkv, seq_len, /*causal=*/true);
     Var x1 = o_proj->forward_residual(a, x);  // x + attn

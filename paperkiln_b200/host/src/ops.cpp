@@ -4,6 +4,7 @@
 #include "microtorch/ops.hpp"
 #include "microtorch/ops_detail.hpp"
 
+#include <cstdlib>
 #include <algorithm>
 #include <cmath>
 #include <cstring>
@@ -333,6 +334,20 @@ void gemm_raw(const Tensor& A, bool ta, const Tensor& B, bool tb, Tensor& C, boo
 void gemm_into_grad(const Var& target, const Tensor& A, bool ta, const Tensor& B, bool tb) {
     gemm_to_grad(target, A, ta, B, tb);
 }
+void rope_operands(const std::vector<int>& pos, float theta_base, size_t head_dim, Tensor& table, Tensor& dpos) {
+    table = rope_table(theta_base, head_dim, max_pos(pos));
+    dpos = device_ints(pos);
+}
+bool rope_in_gemm() {
+    static const bool on = [] {
+        const char* e = std::getenv("MICROTORCH_ROPE_IN_GEMM");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+void rope_inplace(Tensor& t, size_t n_rot, size_t head_dim, const std::vector<int>& pos, float theta_base, bool inverse) {
+    rope_apply(t, 0, n_rot, head_dim, pos, theta_base, inverse);
+}
 void colsum_into_grad(const Var& b, const Tensor& g) {
     Tensor scratch = Tensor::bytes(pk_colsum_scratch_bytes(i64(g.rows()), i64(g.cols())));
     into_f32_grad(b, [&](float* dst) {
@@ -422,7 +437,7 @@ Var linear_rope(const Var& x, const Var& W, const std::vector<int>& pos, float t
     if (x->data.cols() != in) throw std::runtime_error("matmul: inner dimensions disagree");
     if (head_dim % 2 != 0 || n_rot * head_dim > out) throw std::runtime_error("apply_rope: head_dim must be even and <= d");
     if (pos.size() != x->data.rows()) throw std::runtime_error("apply_rope: one position per row");
-    if (cdt() != DType::BF16 || (head_dim != 64 && head_dim != 128) || n_rot == 0)
+    if (cdt() != DType::BF16 || (head_dim != 64 && head_dim != 128) || n_rot == 0 || !detail::rope_in_gemm())
         return rope_(linear(x, W), pos, theta_base, head_dim, n_rot);
     auto produce = [x, W, pos, theta_base, head_dim, n_rot, out]() {
         const Tensor& xt = x->compute();

@@ -185,11 +185,31 @@ void check_linear_shapes(const Var& x, const Q8Weight& W, const Var& bias, const
     if (residual && (residual->data.rows() != x->data.rows() || residual->data.cols() != W.cols))
         throw std::runtime_error("linear: residual shape mismatch");
 }
+void check_rotary(const Rotary* rot, const Var& x, const Q8Weight& W, const Var& residual) {
+    if (!rot) return;
+    if (residual) throw std::runtime_error("apply_rope: a rotated projection takes no residual");
+    if (rot->head_dim % 2 != 0 || rot->n_rot * rot->head_dim > W.cols)
+        throw std::runtime_error("apply_rope: head_dim must be even and <= d");
+    if (rot->pos.size() != x->data.rows()) throw std::runtime_error("apply_rope: one position per row");
+}
+
+// Upstream gradient of a (possibly rotated) projection: rotated back in place first.
+Tensor upstream_unrotated(Variable* self, const std::shared_ptr<Rotary>& rot) {
+    Tensor g = detail::upstream(self);
+    if (rot) {
+        self->grad.reset();
+        if (g.use_count() > 1) g = g.clone();  // someone else still reads the rotated gradient
+        detail::rope_inplace(g, rot->n_rot, rot->head_dim, rot->pos, rot->theta_base, true);
+    }
+    return g;
+}
 }  // namespace
 
-Var q8_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var& bias, const Var& residual) {
+Var q8_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var& bias, const Var& residual, const Rotary* rot_in) {
     check_linear_shapes(x, *Wq, bias, residual);
-    auto produce = [x, Wq, bias, residual]() {
+    check_rotary(rot_in, x, *Wq, residual);
+    const std::shared_ptr<Rotary> rot = rot_in ? std::make_shared<Rotary>(*rot_in) : nullptr;
+    auto produce = [x, Wq, bias, residual, rot]() {
         const DType cd = device::compute_dtype();
         const Tensor& xt = x->compute();
         Tensor y = Tensor::empty(xt.rows(), Wq->cols, cd);
@@ -200,20 +220,23 @@ Var q8_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var& bias
             Tensor w = Wq->dequantize(cd);  // expanded for this GEMM only
             detail::gemm_raw(xt, false, w, false, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
         }
+        if (rot) detail::rope_inplace(y, rot->n_rot, rot->head_dim, rot->pos, rot->theta_base, false);
         return y;
     };
     const bool has_bias = bias != nullptr, has_res = residual != nullptr;
-    return detail::record_projection(x->data.rows(), Wq->cols, produce, {x, bias, residual}, [Wq, has_bias, has_res](Variable* self) {
+    return detail::record_projection(x->data.rows(), Wq->cols, produce, {x, bias, residual}, [Wq, has_bias, has_res, rot](Variable* self) {
         const Var& x = self->parents[0];
-        Tensor g = detail::upstream(self);
+        Tensor g = upstream_unrotated(self, rot);
         if (x->requires_grad) q8_dx_into_grad(x, g, *Wq, nullptr, nullptr);
         bias_residual_grads(self, 1, has_bias, has_res, g);
     });
 }
 
 Var q8_lora_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var& A, const Var& B, float scaling,
-                   const Var& bias, const Var& residual) {
+                   const Var& bias, const Var& residual, const Rotary* rot_in) {
     check_linear_shapes(x, *Wq, bias, residual);
+    check_rotary(rot_in, x, *Wq, residual);
+    const std::shared_ptr<Rotary> rot = rot_in ? std::make_shared<Rotary>(*rot_in) : nullptr;
     const size_t r = A->data.cols();
     if (A->data.rows() != Wq->rows || B->data.rows() != r || B->data.cols() != Wq->cols)
         throw std::runtime_error("matmul: inner dimensions disagree");
@@ -224,7 +247,7 @@ Var q8_lora_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var&
     Tensor xa = Tensor::empty(xt.rows(), r, cd);
     detail::gemm_raw(xt, false, at, false, xa, false);
     check(pk_scale(device::stream(), xa.dt(), xa.ptr(), scaling, xa.ptr(), i64(xa.numel())), "pk_scale");
-    auto produce = [x, Wq, B, xa, bias, residual]() {
+    auto produce = [x, Wq, B, xa, bias, residual, rot]() {
         const DType cd = device::compute_dtype();
         const Tensor& xt = x->compute();
         const Tensor& bt_l = B->compute();
@@ -237,15 +260,16 @@ Var q8_lora_linear(const Var& x, const std::shared_ptr<Q8Weight>& Wq, const Var&
             detail::gemm_raw(xt, false, w, false, y, false, bias ? bt.f32() : nullptr, residual ? &rt : nullptr);
             detail::gemm_raw(xa, false, bt_l, false, y, true);
         }
+        if (rot) detail::rope_inplace(y, rot->n_rot, rot->head_dim, rot->pos, rot->theta_base, false);
         return y;
     };
     const bool has_bias = bias != nullptr, has_res = residual != nullptr;
-    return detail::record_projection(x->data.rows(), Wq->cols, produce, {x, A, B, bias, residual}, [Wq, xa, scaling, has_bias, has_res](Variable* self) {
+    return detail::record_projection(x->data.rows(), Wq->cols, produce, {x, A, B, bias, residual}, [Wq, xa, scaling, has_bias, has_res, rot](Variable* self) {
         const Var& x = self->parents[0];
         const Var& A = self->parents[1];
         const Var& B = self->parents[2];
         const DType cd = device::compute_dtype();
-        Tensor g = detail::upstream(self);
+        Tensor g = upstream_unrotated(self, rot);
         const bool need_dxa = x->requires_grad || A->requires_grad;
         Tensor dxa;  // scaling (dY B^T): the gradient that reaches x A
         if (need_dxa) {

@@ -941,3 +941,4 @@ def test_gemm_rope_equals_gemm_then_rope(pk, shape):
     rc = pk.pk_gemm_rope(stream(), int(tb), 64, N, K, ptr(A), K, ptr(B), B.stride(0), ptr(one), N, None, ptr(pos), ptr(tab),
                          n_pos, nh, hd, 0)
     assert rc == 3
+
