@@ -38,7 +38,10 @@ using namespace tc;
 constexpr int T2_BM = 128;         // rows per CTA; the pair covers 256
 constexpr int T2_BN = 256;
 constexpr int T2_BK = 64;
-constexpr int T2_THREADS = 192;
+constexpr int T2_THREADS = 192;          // producer warp, MMA warp, four epilogue warps
+constexpr int T2_THREADS_SWIGLU = 320;   // SwiGLU mode: eight epilogue warps (two per tensor-memory lane quadrant, 64 of
+                                         // the tile's 128 G / U columns each): its epilogue has an exponential and a
+                                         // division per element and was the bound with four
 constexpr int T2_STAGES = 6;
 constexpr int T2_A_BYTES = T2_BM * T2_BK * 2;          // 16 KiB
 constexpr int T2_B_BYTES = (T2_BN / 2) * T2_BK * 2;    // 16 KiB: this CTA's half of B
@@ -160,7 +163,7 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
 }
 
 template <typename TC, bool SWIGLU>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T2_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SWIGLU ? T2_THREADS_SWIGLU : T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
                 const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_y, const T2Params p) {
@@ -194,7 +197,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&acc_full[a]), 1);
-            mbar_init(smem_u32(&acc_empty[a]), 8);
+            mbar_init(smem_u32(&acc_empty[a]), SWIGLU ? 16 : 8);   // epilogue warps of the pair
         }
         for (int b = 0; b < 4 * T2_EPI_BOXES; ++b) mbar_init(smem_u32(&in_bar[b]), 1);
         *abort_flag = 0;
@@ -293,8 +296,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         TC* C = static_cast<TC*>(p.C);
         const TC* Rsd = static_cast<const TC*>(p.residual);
         StagedOut out;   // staged form of the output (p.tma_out): boxes, barriers and maps of this warp
-        out.boxes = epi_smem + (warp - 2) * (T2_EPI_BOXES * EPI_BOX_BYTES);
-        out.in_bar = in_bar + (warp - 2) * T2_EPI_BOXES;
+        // boxes per warp: four, or two in SwiGLU mode (eight warps, stores only)
+        constexpr int WARP_BOXES = SWIGLU ? T2_EPI_BOXES / 2 : T2_EPI_BOXES;
+        out.boxes = epi_smem + (warp - 2) * (WARP_BOXES * EPI_BOX_BYTES);
+        out.in_bar = in_bar + ((warp - 2) & 3) * T2_EPI_BOXES;
         out.out = &map_c;
         out.in = p.splits > 1 ? nullptr : (Rsd != nullptr ? &map_u : (p.accumulate ? &map_c : nullptr));
         out.bias = p.splits > 1 ? nullptr : p.bias;
@@ -330,8 +335,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 TC* Gout = static_cast<TC*>(p.C);
                 TC* Uout = static_cast<TC*>(p.U);
                 TC* Yout = static_cast<TC*>(p.Y);
+                // warps 2..5 take the tile's first 64 columns of G / U, warps 6..9 the other 64
+                const int ch0 = ((warp - 2) >> 2) * (TILE_N / 64), ch1 = ch0 + TILE_N / 64;
 #pragma unroll 1
-                for (int ch = 0; ch < TILE_N / 32; ++ch) {
+                for (int ch = ch0; ch < ch1; ++ch) {
                     const int64_t c0 = n0 + ch * 32;
                     if (c0 >= p.N) break;  // uniform across the warp
                     uint32_t rg[32], ru[32];
@@ -349,8 +356,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                         const int32_t x = static_cast<int32_t>(c0), y0 = static_cast<int32_t>(m0 + quad * 32);
                         auto emit = [&](const float* vals, const CUtensorMap* map) {
-                            uint8_t* box = out.boxes + (out.uc & (T2_EPI_BOXES - 1)) * EPI_BOX_BYTES;
-                            if (lane == 0) bulk_wait_read<T2_EPI_BOXES - 1>();
+                            uint8_t* box = out.boxes + (out.uc & (WARP_BOXES - 1)) * EPI_BOX_BYTES;
+                            if (lane == 0) bulk_wait_read<WARP_BOXES - 1>();
                             __syncwarp();
 #pragma unroll
                             for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(box + box_offset(lane, j)) = pack_out<TC>(vals + j * 8);
@@ -486,7 +493,7 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const
     if (max_pairs == 0) {
         cudaLaunchConfig_t probe = {};
         probe.gridDim = dim3(static_cast<unsigned>(sm_count() / 2 * 2));
-        probe.blockDim = dim3(T2_THREADS);
+        probe.blockDim = dim3(SWIGLU ? T2_THREADS_SWIGLU : T2_THREADS);
         probe.dynamicSmemBytes = T2_SMEM_BYTES;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -568,7 +575,7 @@ int launch2(cudaStream_t st, const CUtensorMap& ma, const CUtensorMap& mb, const
     }
     int64_t pairs = max_pairs;
     if (pairs > tiles * p.splits) pairs = tiles * p.splits;
-    kern<<<static_cast<unsigned>(2 * pairs), T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, mb2, mc, mu, my, p);
+    kern<<<static_cast<unsigned>(2 * pairs), SWIGLU ? T2_THREADS_SWIGLU : T2_THREADS, T2_SMEM_BYTES, st>>>(ma, mb, mb2, mc, mu, my, p);
     PK_LAUNCH_CHECK();
     if (p.splits > 1)
         return gemm_splitk_reduce(st, c_dtype, p.partial, p.splits, p.slab, p.pstride, p.M, p.N, p.C, p.ldc, p.accumulate,
