@@ -231,31 +231,79 @@ add_bias_kernel(const T* x, const float* b, T* y, int64_t R, int64_t C, bool vec
 }
 
 // ---- column sums, two deterministic stages ---------------------------------------------
-// Stage 1: block b sums rows b, b+G, b+2G, ... for every column into partial[b, C].
-// Stage 2: out[c] += sum_b partial[b, c] in ascending b.
-constexpr int COLSUM_THREADS = 256;
-inline int colsum_blocks(int64_t R) {
-    int64_t g = static_cast<int64_t>(sm_count()) * 2;
-    if (g > R) g = R;
-    if (g < 1) g = 1;
-    return static_cast<int>(g);
+// Stage 1: a block owns a group of columns (COLSUM_THREADS x 16 bytes of a row) and the rows
+// b, b+G, b+2G, ... of stripe b; a thread keeps the sums of its 16 bytes of columns in
+// registers and has four rows in flight. partial[b, c] is the stripe's sum of column c.
+// Stage 2: out[c] += sum_b partial[b, c], four interleaved running sums combined in a fixed order.
+// (The previous form read one element per thread and row: 63 us for 16384 x 3072 bf16, a
+// tenth of a GPT-2 step went into bias gradients.)
+constexpr int COLSUM_THREADS = 128;
+struct ColsumGrid {
+    int col_groups;   // gridDim.y
+    int stripes;      // gridDim.x = G
+};
+inline ColsumGrid colsum_grid(int64_t R, int64_t C, int per_thread) {
+    ColsumGrid g;
+    const int64_t cols_per_block = static_cast<int64_t>(COLSUM_THREADS) * per_thread;
+    g.col_groups = static_cast<int>((C + cols_per_block - 1) / cols_per_block);
+    int64_t st = (static_cast<int64_t>(sm_count()) * 4 + g.col_groups - 1) / g.col_groups;
+    if (st > R) st = R;
+    if (st < 1) st = 1;
+    g.stripes = static_cast<int>(st);
+    return g;
 }
-template <typename T>
+// the scratch is sized for the larger of the two layouts (scalar fallback: one column per thread)
+inline int colsum_stripes_max(int64_t R, int64_t C) {
+    const int a = colsum_grid(R, C, 8).stripes, b = colsum_grid(R, C, 1).stripes;
+    return a > b ? a : b;
+}
+template <typename T, int N>
+__device__ __forceinline__ void colsum_load(const T* p, float (&v)[N]) {
+    if constexpr (N == 1) v[0] = to_f32(p[0]);
+    else Vec<T>::load(p, v);
+}
+template <typename T, int N>   // N columns (16 bytes) per thread when the rows are 16-byte aligned, else 1
 __global__ void __launch_bounds__(COLSUM_THREADS)
-colsum_stage1(const T* x, float* partial, int64_t R, int64_t C) {
-    for (int64_t c = threadIdx.x; c < C; c += COLSUM_THREADS) {
-        float acc = 0.0f;
-        for (int64_t r = blockIdx.x; r < R; r += gridDim.x) acc += to_f32(x[r * C + c]);
-        partial[static_cast<int64_t>(blockIdx.x) * C + c] = acc;
+colsum_stage1(const T* __restrict__ x, float* __restrict__ partial, int64_t R, int64_t C) {
+    const int64_t c0 = (static_cast<int64_t>(blockIdx.y) * COLSUM_THREADS + threadIdx.x) * N;
+    if (c0 >= C) return;
+    float acc[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) acc[e] = 0.0f;
+    const int64_t G = gridDim.x;
+    int64_t r = blockIdx.x;
+    for (; r + 3 * G < R; r += 4 * G) {   // four rows in flight, added in row order
+        float v[4][N];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) colsum_load<T, N>(x + (r + k * G) * C + c0, v[k]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int e = 0; e < N; ++e) acc[e] += v[k][e];
     }
+    for (; r < R; r += G) {
+        float v[N];
+        colsum_load<T, N>(x + r * C + c0, v);
+#pragma unroll
+        for (int e = 0; e < N; ++e) acc[e] += v[e];
+    }
+#pragma unroll
+    for (int e = 0; e < N; ++e) partial[static_cast<int64_t>(blockIdx.x) * C + c0 + e] = acc[e];
 }
 __global__ void __launch_bounds__(256)
-colsum_stage2(const float* partial, float* out, int nparts, int64_t C) {
+colsum_stage2(const float* __restrict__ partial, float* out, int nparts, int64_t C) {
     const int64_t c = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (c >= C) return;
-    float acc = 0.0f;
-    for (int b = 0; b < nparts; ++b) acc += partial[static_cast<int64_t>(b) * C + c];
-    out[c] += acc;
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    int b = 0;
+    for (; b + 3 < nparts; b += 4) {
+        a0 += partial[static_cast<int64_t>(b) * C + c];
+        a1 += partial[static_cast<int64_t>(b + 1) * C + c];
+        a2 += partial[static_cast<int64_t>(b + 2) * C + c];
+        a3 += partial[static_cast<int64_t>(b + 3) * C + c];
+    }
+    for (; b < nparts; ++b) a0 += partial[static_cast<int64_t>(b) * C + c];
+    out[c] += (a0 + a1) + (a2 + a3);
 }
 
 // ---- column-range copy -----------------------------------------------------------
@@ -413,18 +461,26 @@ int pk_add_bias(void* stream, int dtype, const void* x, const float* b, void* y,
 }
 size_t pk_colsum_scratch_bytes(int64_t R, int64_t C) {
     if (R <= 0 || C <= 0) return 0;
-    return static_cast<size_t>(colsum_blocks(R)) * static_cast<size_t>(C) * sizeof(float);
+    return static_cast<size_t>(colsum_stripes_max(R, C)) * static_cast<size_t>(C) * sizeof(float);
 }
 int pk_colsum(void* stream, int dtype, const void* x, float* out, void* scratch, int64_t R, int64_t C) {
     PK_REQUIRE(valid_dtype(dtype), "bad dtype");
     if (R <= 0 || C <= 0) return PK_OK;
     PK_REQUIRE(x && out && scratch, "null pointer");
-    const int g = colsum_blocks(R);
     float* partial = static_cast<float*>(scratch);
-    if (dtype == PK_F32)
-        colsum_stage1<float><<<g, COLSUM_THREADS, 0, as_stream(stream)>>>(static_cast<const float*>(x), partial, R, C);
-    else
-        colsum_stage1<bf16><<<g, COLSUM_THREADS, 0, as_stream(stream)>>>(static_cast<const bf16*>(x), partial, R, C);
+    cudaStream_t st = as_stream(stream);
+    constexpr int NB = Vec<bf16>::N, NF = Vec<float>::N;
+    const bool vec = aligned16(x) && C % (dtype == PK_F32 ? NF : NB) == 0;
+    const ColsumGrid cg = colsum_grid(R, C, vec ? (dtype == PK_F32 ? NF : NB) : 1);
+    const dim3 grid(static_cast<unsigned>(cg.stripes), static_cast<unsigned>(cg.col_groups));
+    const int g = cg.stripes;
+    if (dtype == PK_F32) {
+        if (vec) colsum_stage1<float, NF><<<grid, COLSUM_THREADS, 0, st>>>(static_cast<const float*>(x), partial, R, C);
+        else colsum_stage1<float, 1><<<grid, COLSUM_THREADS, 0, st>>>(static_cast<const float*>(x), partial, R, C);
+    } else {
+        if (vec) colsum_stage1<bf16, NB><<<grid, COLSUM_THREADS, 0, st>>>(static_cast<const bf16*>(x), partial, R, C);
+        else colsum_stage1<bf16, 1><<<grid, COLSUM_THREADS, 0, st>>>(static_cast<const bf16*>(x), partial, R, C);
+    }
     PK_LAUNCH_CHECK();
     colsum_stage2<<<static_cast<unsigned>((C + 255) / 256), 256, 0, as_stream(stream)>>>(partial, out, g, C);
     PK_LAUNCH_CHECK();
