@@ -66,6 +66,9 @@ Var linear(const Var& x, const Var& W, const Var& bias = nullptr, const Var& res
 // reference's blocks (src/llama.cpp:44-52, src/nn.cpp:144-150).
 Var attention(const Var& q, const Var& k, const Var& v, size_t n_heads, size_t n_kv_heads, size_t seq_len,
               bool causal);
+// attention(slice_cols(qkv, 0, d), slice_cols(qkv, d, 2 d), slice_cols(qkv, 2 d, 3 d), n_heads, n_heads, ...)
+// for a packed [T, 3 d] projection, without the slices: the same values, read and written in place.
+Var attention_packed(const Var& qkv, size_t n_heads, size_t seq_len, bool causal);
 // Rotates the first `n_rot` heads (width head_dim) of x [T, H*head_dim] IN PLACE and
 // returns a node that shares x's buffer. x must have no other consumer and must be the
 // output of an op whose backward does not read its own output (a linear / matmul).

@@ -154,12 +154,8 @@ CausalSelfAttention::CausalSelfAttention(size_t d, size_t n_heads, unsigned seed
 }
 
 Var CausalSelfAttention::heads(const Var& x, size_t seq_len) const {
-    const size_t d = H * dk;
-    Var qkv = c_attn->forward(x);  // [T, 3d]: q | k | v, heads contiguous inside each
-    Var q = ops::slice_cols(qkv, 0, d);
-    Var k = ops::slice_cols(qkv, d, 2 * d);
-    Var v = ops::slice_cols(qkv, 2 * d, 3 * d);
-    return ops::attention(q, k, v, H, H, seq_len, causal);
+    Var qkv = c_attn->forward(x);  // [T, 3d]: q | k | v, heads contiguous inside each, read in place
+    return ops::attention_packed(qkv, H, seq_len, causal);
 }
 Var CausalSelfAttention::forward(const Var& x, size_t seq_len) const { return c_proj->forward(heads(x, seq_len)); }
 Var CausalSelfAttention::forward_residual(const Var& x, const Var& residual, size_t seq_len) const {

@@ -311,6 +311,44 @@ Var attention_impl(const Var& q, const Var& k, const Var& v, size_t Hq, size_t H
     });
 }
 
+// Attention over a packed [T, 3 d] projection (q | k | v, heads contiguous inside each, as GPT-2's
+// c_attn produces it): the kernels read the three column ranges in place through the row stride
+// and write dq | dk | dv into one [T, 3 d] gradient, so nothing is sliced or concatenated.
+Var attention_packed_impl(const Var& qkv, size_t H, size_t seq_len, bool causal) {
+    const size_t T = qkv->data.rows();
+    if (H == 0 || qkv->data.cols() % (3 * H) != 0) throw std::runtime_error("fused_attention: shape mismatch");
+    const size_t d = qkv->data.cols() / 3, dk = d / H;
+    const size_t sl = seq_len == 0 ? T : seq_len;
+    if (sl == 0 || T % sl != 0) throw std::runtime_error("fused_attention: rows not a multiple of seq_len");
+    const size_t B = T / sl;
+    const float scale = 1.0f / std::sqrt(static_cast<float>(dk));
+    const Tensor& pt = qkv->compute();
+    const size_t es = dtype_bytes(pt.dtype());
+    auto col = [es](const Tensor& t, size_t c) { return static_cast<void*>(static_cast<char*>(t.ptr()) + c * es); };
+    Tensor out = new_act(T, d);
+    Tensor lse = Tensor::empty(T, H, DType::F32);
+    check(pk_attn_fwd(S(), pt.dt(), col(pt, 0), i64(pt.ld()), col(pt, d), i64(pt.ld()), col(pt, 2 * d), i64(pt.ld()), out.ptr(),
+                      i64(out.cols()), lse.f32(), i64(B), i64(sl), static_cast<int>(H), static_cast<int>(H),
+                      static_cast<int>(dk), scale, causal ? 1 : 0),
+          "pk_attn_fwd");
+    Tensor out_saved = out;
+    return record(std::move(out), {qkv}, [out_saved, lse, B, sl, H, d, dk, scale, causal, es](Variable* self) {
+        const Var& qkv = self->parents[0];
+        if (!qkv->requires_grad) return;
+        const Tensor& pt = qkv->compute();
+        auto col = [es](const Tensor& t, size_t c) { return static_cast<void*>(static_cast<char*>(t.ptr()) + c * es); };
+        Tensor g = grad_of(self);
+        Tensor dp = new_act(pt.rows(), pt.cols());
+        Tensor scratch = Tensor::bytes(pk_attn_bwd_scratch_bytes(i64(B), i64(sl), static_cast<int>(H)));
+        check(pk_attn_bwd(S(), pt.dt(), col(pt, 0), i64(pt.ld()), col(pt, d), i64(pt.ld()), col(pt, 2 * d), i64(pt.ld()),
+                          out_saved.ptr(), i64(out_saved.cols()), lse.f32(), g.ptr(), i64(g.cols()), col(dp, 0), i64(dp.ld()),
+                          col(dp, d), i64(dp.ld()), col(dp, 2 * d), i64(dp.ld()), scratch.ptr(), i64(B), i64(sl),
+                          static_cast<int>(H), static_cast<int>(H), static_cast<int>(dk), scale, causal ? 1 : 0),
+              "pk_attn_bwd");
+        qkv->accumulate(dp);
+    });
+}
+
 }  // namespace
 
 namespace detail {
@@ -907,6 +945,10 @@ Var rope_(const Var& x, const std::vector<int>& pos, float theta_base, size_t he
 Var fused_attention(const Var& q, const Var& k, const Var& v, float scale, size_t seq_len, bool causal) {
     if (q->data.cols() != k->data.cols()) throw std::runtime_error("fused_attention: shape mismatch");
     return attention_impl(q, k, v, 1, 1, scale, seq_len, causal, true);
+}
+
+Var attention_packed(const Var& qkv, size_t n_heads, size_t seq_len, bool causal) {
+    return attention_packed_impl(qkv, n_heads, seq_len, causal);
 }
 
 Var attention(const Var& q, const Var& k, const Var& v, size_t n_heads, size_t n_kv_heads, size_t seq_len,
